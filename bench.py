@@ -1,0 +1,414 @@
+"""Benchmark of the kernel suite (one JSON line on stdout from rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--headline NAME] [--only NAME[,NAME]] [--no-cpu]
+
+A "step" is one call of the headline workload's hot path on one batch of seeded
+synthetic input.  `value` is timed on the device with inputs resident in HBM;
+`e2e` times the same call from pinned host buffers (H2D + kernel + D2H).  The
+other workloads of the suite are reported under "kernels" (N=1 only).  With
+--impl reference the CPU restatement of the reference's own CPU path (numpy
+float32, OpenBLAS contractions) is timed on the host cores instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "cutile.jl_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], tensor=d["bf16_tflops"], tensor_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        rows = [r for t, r in self.rows if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 9] or \
+               [r for _, r in self.rows if len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        sm = sorted(float(r[1]) for r in rows)
+        reasons = set()
+        for r in rows:
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
+                "samples": len(rows)}
+
+
+# --------------------------------------------------------------------------- workloads
+class Workload:
+    """One benchmark configuration.  Subclasses fill in the members below."""
+    name = ""
+    metric = ""
+    unit = ""            # "GB/s" or "TFLOP/s"
+    bound = "hbm"        # roofline that binds
+    dtype = "f32"
+    launches_per_step = 1
+    kernel = ""          # name of the dominant kernel
+
+    def work(self):      # algorithmic bytes (hbm) or flops (tensor) per step
+        raise NotImplementedError
+
+    def host_inputs(self):  # dict of numpy arrays (seeded)
+        raise NotImplementedError
+
+    def to_device(self, host, torch):  # -> state (device tensors incl. outputs)
+        raise NotImplementedError
+
+    def step(self, ctb, st):  # enqueue one step on the current stream
+        raise NotImplementedError
+
+    def e2e_io(self, st):  # (list of (device, pinned host) input pairs, list of (device, pinned host) outputs)
+        raise NotImplementedError
+
+    def cpu_step(self, host, ref, np):  # -> (callable doing one bounded sample, fraction of a step, description)
+        raise NotImplementedError
+
+    def check(self, host, st, ref, np):  # parity spot check, returns error figure
+        return None
+
+
+class Softmax(Workload):
+    metric = "softmax_gbps"
+    unit = "GB/s"
+    M = N = 4096
+
+    def __init__(self, variant):
+        self.variant = variant
+        self.name = "softmax_tma" if variant == 0 else "softmax_chunked"
+        self.kernel = "softmax_staged_kernel" if variant == 0 else "softmax_online_kernel"
+
+    def describe(self):
+        return f"row softmax f32 {self.M}x{self.N} N(0,4) seed 1, variant={'single-tile' if self.variant == 0 else 'chunked-online'}"
+
+    def work(self):
+        return 2 * self.M * self.N * 4
+
+    def host_inputs(self):
+        from oracle import inputs
+        return inputs.softmax(self.M, self.N, seed=1)
+
+    def to_device(self, host, torch):
+        x = torch.from_numpy(host["input"]).cuda()
+        return dict(x=x, out=torch.empty_like(x))
+
+    def step(self, ctb, st):
+        if self.variant == 0:
+            ctb.softmax.softmax_tma_kernel(st["out"], st["x"], 4096)
+        else:
+            ctb.softmax.softmax_chunked_kernel(st["out"], st["x"], self.N, 1024)
+
+    def e2e_io(self, st):
+        return [("x",)], [("out",)]
+
+    def cpu_step(self, host, ref, np):
+        x = host["input"]
+        return (lambda: ref.softmax(x, dtype=np.float32)), 1.0, "full 4096x4096 rows, numpy float32"
+
+    def check(self, host, st, ref, np):
+        rows = slice(0, 256)
+        return ref.max_abs_over_max(st["out"][rows].cpu().numpy(), ref.softmax(host["input"][rows]))
+
+
+class LayerNormFwd(Workload):
+    name = "layernorm_fwd"
+    metric = "layernorm_fwd_gbps"
+    unit = "GB/s"
+    kernel = "ln_fwd_kernel"
+    M = N = 4096
+
+    def describe(self):
+        return "LayerNorm fwd f32 4096x4096, X~N(0,1) W~U(.5,1.5) B~N(0,.1) eps 1e-5 seed 0"
+
+    def work(self):
+        return 2 * self.M * self.N * 4 + 2 * self.N * 4 + 2 * self.M * 4
+
+    def host_inputs(self):
+        from oracle import inputs
+        return inputs.layernorm(self.M, self.N, seed=0)
+
+    def to_device(self, host, torch):
+        st = {k: torch.from_numpy(host[k]).cuda() for k in ("X", "W", "B", "DY")}
+        st.update(Y=torch.empty_like(st["X"]), DX=torch.empty_like(st["X"]),
+                  Mean=torch.empty(self.M, device="cuda"), Rstd=torch.empty(self.M, device="cuda"),
+                  DWp=torch.empty(64, self.N, device="cuda"), DBp=torch.empty(64, self.N, device="cuda"),
+                  FDW=torch.empty(self.N, device="cuda"), FDB=torch.empty(self.N, device="cuda"))
+        return st
+
+    def step(self, ctb, st):
+        ctb.layernorm.layer_norm_fwd(st["X"], st["W"], st["B"], st["Y"], st["Mean"], st["Rstd"], 1e-5, 1024)
+
+    def e2e_io(self, st):
+        return [("X",), ("W",), ("B",)], [("Y",), ("Mean",), ("Rstd",)]
+
+    def cpu_step(self, host, ref, np):
+        return (lambda: ref.layernorm_fwd(host["X"], host["W"], host["B"], host["eps"], dtype=np.float32)), 1.0, \
+            "full 4096x4096, numpy float32"
+
+    def check(self, host, st, ref, np):
+        r = slice(0, 256)
+        return ref.max_abs_over_max(st["Y"][r].cpu().numpy(),
+                                    ref.layernorm_fwd(host["X"][r], host["W"], host["B"], host["eps"])[0])
+
+
+class LayerNormBwd(LayerNormFwd):
+    name = "layernorm_bwd"
+    metric = "layernorm_bwd_gbps"
+    kernel = "ln_bwd_kernel"
+    launches_per_step = 2
+
+    def describe(self):
+        return "LayerNorm bwd f32 4096x4096, dY~N(0,1) seed 0, GROUP_SIZE_M=64 (dX kernel + partial reduce)"
+
+    def work(self):
+        return 3 * self.M * self.N * 4 + 3 * self.N * 4 + 2 * self.M * 4
+
+    def to_device(self, host, torch):
+        import cutile_b200 as ctb
+        st = super().to_device(host, torch)
+        LayerNormFwd.step(self, ctb, st)  # Mean/Rstd are inputs of the backward pass
+        return st
+
+    def step(self, ctb, st):
+        ctb.layernorm.layer_norm_bwd_dx_partial_dwdb(st["DX"], st["DY"], st["DWp"], st["DBp"], st["X"], st["W"],
+                                                     st["Mean"], st["Rstd"], None, 64, 1024)
+        ctb.layernorm.layer_norm_bwd_dwdb(st["DWp"], st["DBp"], st["FDW"], st["FDB"], 32, 1024)
+
+    def e2e_io(self, st):
+        return [("X",), ("DY",), ("W",), ("Mean",), ("Rstd",)], [("DX",), ("FDW",), ("FDB",)]
+
+    def cpu_step(self, host, ref, np):
+        y, m, r = ref.layernorm_fwd(host["X"], host["W"], host["B"], host["eps"], dtype=np.float32)
+        return (lambda: ref.layernorm_bwd(host["X"], host["W"], host["DY"], m, r, dtype=np.float32)), 1.0, \
+            "full 4096x4096, numpy float32"
+
+    def check(self, host, st, ref, np):
+        _, m, r = ref.layernorm_fwd(host["X"], host["W"], host["B"], host["eps"])
+        dx, dw, db = ref.layernorm_bwd(host["X"], host["W"], host["DY"], m, r)
+        return max(ref.max_abs_over_max(st["DX"].cpu().numpy(), dx), ref.max_abs_over_max(st["FDW"].cpu().numpy(), dw),
+                   ref.max_abs_over_max(st["FDB"].cpu().numpy(), db))
+
+
+def registry():
+    w = [Softmax(0), Softmax(1), LayerNormFwd(), LayerNormBwd()]
+    try:
+        import bench_dense  # tensor-core workloads live beside this file once built
+        w = bench_dense.workloads(Workload) + w
+    except ImportError:
+        pass
+    return {x.name: x for x in w}
+
+
+# --------------------------------------------------------------------------- timing
+def device_time(torch, dist, fn_steps, steps, warmup):
+    """warmup untimed steps, then `steps` steps between two events; max over ranks."""
+    for i in range(warmup):
+        fn_steps(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for i in range(steps):
+        fn_steps(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    if dist is not None:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, t0, t1
+
+
+def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu, sampler=None):
+    import numpy as np
+    from oracle import ref
+    host = w.host_inputs()
+    base = w.to_device(host, torch)
+    nbytes = sum(t.numel() * t.element_size() for t in base.values() if hasattr(t, "numel"))
+    nsets = max(2, min(8, -(-2 * L2_BYTES // max(nbytes, 1)) + 1))
+    sets = [base] + [{k: (v.clone() if hasattr(v, "clone") else v) for k, v in base.items()} for _ in range(nsets - 1)]
+    ms, t0, t1 = device_time(torch, dist, lambda i: w.step(ctb, sets[i % nsets]), steps, warmup)
+    ctb.check_device_status(torch.cuda.current_device())
+    per = ms / steps
+    scale = 1e9 if w.unit == "GB/s" else 1e12
+    value = w.work() * world / (per * 1e-3) / scale
+    res = dict(name=w.name, metric=w.metric, unit=w.unit, value=value, ms_per_step=per, work_per_step=w.work(),
+               workload=w.describe(), l2="rotating %d input/output sets (%.0f MB total, L2 is 126 MB)" %
+               (nsets, nsets * nbytes / 1e6), t0=t0, t1=t1, launches=w.launches_per_step * steps)
+    res["parity_err"] = w.check(host, sets[(warmup + steps - 1) % nsets], ref, np)
+    if do_e2e:
+        ins, outs = w.e2e_io(base)
+        pin_in = {k[0]: torch.from_numpy(host[k[0]] if k[0] in host else base[k[0]].cpu().numpy()).pin_memory() for k in ins}
+        pin_out = {k[0]: torch.empty(base[k[0]].shape, dtype=base[k[0]].dtype).pin_memory() for k in outs}
+
+        def e2e_step(i):
+            for k, h in pin_in.items():
+                base[k].copy_(h, non_blocking=True)
+            w.step(ctb, base)
+            for k, h in pin_out.items():
+                h.copy_(base[k], non_blocking=True)
+        ems, _, _ = device_time(torch, dist, e2e_step, max(3, steps // 4), 3)
+        eper = ems / max(3, steps // 4)
+        res["e2e"] = dict(value=w.work() * world / (eper * 1e-3) / scale, unit=w.unit, ms_per_step=eper,
+                          h2d_bytes_per_step=sum(h.numel() * h.element_size() for h in pin_in.values()),
+                          d2h_bytes_per_step=sum(h.numel() * h.element_size() for h in pin_out.values()))
+    if do_cpu and rank == 0:
+        res["cpu_baseline"] = cpu_time(w, host)
+    return res
+
+
+def cpu_time(w, host, repeats=3):
+    import numpy as np
+    from oracle import ref
+    fn, frac, sample = w.cpu_step(host, ref, np)
+    fn()  # warm-up
+    best = 1e30
+    for _ in range(repeats):
+        t = time.perf_counter()
+        fn()
+        best = min(best, time.perf_counter() - t)
+    scale = 1e9 if w.unit == "GB/s" else 1e12
+    threads = int(os.environ.get("OPENBLAS_NUM_THREADS", os.cpu_count() or 1)) if w.bound == "tensor" else 1
+    return dict(value=w.work() * frac / best / scale, unit=w.unit, cores=threads, kind="port",
+                sample=sample + f"; best of {repeats}; {best * 1e3:.1f} ms", host_cpus=os.cpu_count())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--headline", default=None)
+    ap.add_argument("--only", default=None, help="comma-separated workload names (default: all at N=1)")
+    ap.add_argument("--no-cpu", action="store_true")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    reg = registry()
+    headline = a.headline or ("fmha_causal" if "fmha_causal" in reg else "softmax_tma")
+    hw = reg[headline]
+    pk = peaks()
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        host = hw.host_inputs()
+        cb = cpu_time(hw, host, repeats=max(1, min(a.steps, 3)))
+        line = dict(impl="reference", metric=hw.metric, value=cb["value"], unit=hw.unit, n_gpus=a.gpus, steps=a.steps,
+                    warmup=a.warmup, ms_per_step=None, higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype=hw.dtype, data="synthetic", config={"workload": hw.describe()}, cpu_baseline=cb,
+                    e2e=dict(value=cb["value"], unit=hw.unit, h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                    gpu_launches=0,
+                    note="CPU restatement of the reference's own CPU check path (numpy float32 + OpenBLAS); the "
+                         "reference's GPU path needs Julia and tileiras, which are unavailable on this box")
+        print(json.dumps(line))
+        return
+
+    import torch
+    import cutile_b200 as ctb  # raises if the CUDA library is missing: there is no fallback
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    head = run_workload(hw, torch, ctb, dist, a.steps, a.warmup, rank, world, True, not a.no_cpu and world == 1)
+    clocks = sampler.summary(head["t0"], head["t1"])
+    others = {}
+    if world == 1:
+        names = [n for n in reg if n != headline]
+        if a.only is not None:
+            names = [n for n in a.only.split(",") if n and n != headline]
+        for n in names:
+            r = run_workload(reg[n], torch, ctb, None, a.steps, a.warmup, rank, 1, True, not a.no_cpu)
+            r["clocks"] = sampler.summary(r["t0"], r["t1"])
+            others[n] = r
+    sampler.stop()
+
+    def roof(r, w):
+        peak = pk["hbm"] if w.bound == "hbm" else pk["tensor"]
+        ach = r["work_per_step"] / (r["ms_per_step"] * 1e-3) / (1e9 if w.bound == "hbm" else 1e12)
+        return dict(bound=w.bound, achieved=ach, peak=peak, unit="GB/s" if w.bound == "hbm" else "TFLOP/s",
+                    frac=ach / peak, traffic=getattr(w, "ncu_traffic", None), kernel=w.kernel,
+                    peak_source=pk["source"])
+
+    if rank == 0:
+        line = dict(metric=hw.metric, value=head["value"], unit=hw.unit, n_gpus=world, steps=a.steps, warmup=a.warmup,
+                    ms_per_step=head["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype=hw.dtype, data="synthetic",
+                    config={"workload": hw.describe(), "l2": head["l2"], "per_gpu": "same workload on every rank"},
+                    clocks=clocks, e2e=head.get("e2e"), gpu_launches=head["launches"], roofline=roof(head, hw),
+                    cpu_baseline=head.get("cpu_baseline"), parity_err=head["parity_err"])
+        if others:
+            line["kernels"] = {n: dict(metric=r["metric"], value=r["value"], unit=r["unit"],
+                                       ms_per_step=r["ms_per_step"], roofline=roof(r, reg[n]), e2e=r.get("e2e"),
+                                       cpu_baseline=r.get("cpu_baseline"), parity_err=r["parity_err"],
+                                       workload=r["workload"], clocks=r["clocks"]) for n, r in others.items()}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

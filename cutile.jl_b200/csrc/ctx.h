@@ -1,0 +1,61 @@
+// Library-internal context, error reporting and argument checks shared by the
+// per-kernel translation units.  Nothing here is part of the C ABI.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/cutile_b200.h"
+
+struct ctb_ctx {
+  int device;
+  int sm_count;
+  int cc_major, cc_minor;
+  int* dev_status;        // one int in device memory; kernels atomicMax error codes into it
+  void* workspace;        // grown on demand (ctb_internal::workspace)
+  size_t workspace_bytes;
+  void* nccl;             // ctb_internal::Comm* when a communicator is attached
+};
+
+namespace ctb_internal {
+
+int fail(int status, const char* fmt, ...);  // sets the thread-local message, returns status
+int cuda_fail(cudaError_t e, const char* what);
+bool is_pow2(long long v);
+// True when p looks like device (or managed) memory of the current context.
+bool is_device_ptr(const void* p);
+// Returns ctx scratch of at least `bytes` (may reallocate => synchronises the device).
+int workspace(ctb_ctx* ctx, size_t bytes, void** out);
+
+// cuTensorMapEncodeTiled, resolved through the runtime so that the library has
+// no link-time dependency on libcuda and loads on machines without a driver.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled();
+
+// rank-`rank` tiled map, 128-byte swizzle, zero fill.  dims/box in elements
+// (innermost first), strides in bytes for dims 1..rank-1.
+int make_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128 = true);
+
+#define CTB_CHECK_CTX(ctx)                                                              \
+  do {                                                                                  \
+    if (!(ctx)) return ctb_internal::fail(CTB_BAD_ARG, "%s: null context", __func__);   \
+  } while (0)
+
+#define CTB_CHECK_DEV(p)                                                                          \
+  do {                                                                                            \
+    if (!ctb_internal::is_device_ptr(p))                                                          \
+      return ctb_internal::fail(CTB_BAD_ARG, "%s: argument %s is not a device pointer", __func__, #p); \
+  } while (0)
+
+#define CTB_CHECK_LAUNCH(what)                                     \
+  do {                                                             \
+    cudaError_t e__ = cudaGetLastError();                          \
+    if (e__ != cudaSuccess) return ctb_internal::cuda_fail(e__, what); \
+  } while (0)
+
+}  // namespace ctb_internal

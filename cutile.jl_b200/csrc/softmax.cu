@@ -1,0 +1,297 @@
+// Row softmax for sm_100a.
+//
+// variant 0 ("single tile per row", the counterpart of softmax_tma_kernel,
+//   examples/softmax.jl:18-42): persistent CTAs; each row is staged into shared
+//   memory by one bulk async copy (cp.async.bulk + mbarrier) through a ring of
+//   stages, normalised in registers, written back into the stage and stored
+//   with a bulk copy shared->global, so loads and stores of neighbouring rows
+//   overlap the arithmetic of the current one.
+// variant 1 ("chunked", the counterpart of softmax_chunked_kernel, :48-100):
+//   one pass of 128-bit loads keeps a running (max, sum) per thread; the row
+//   is kept in registers when it fits (one HBM read), else re-read once.
+//
+// Both compute in f32 with exp() and an exact divide, like the reference
+// (examples/softmax.jl:32-35,92).  HBM-bound: 2*M*N*sizeof(T) bytes per call.
+#include <float.h>
+
+#include "ctx.h"
+#include "ptx.cuh"
+
+using namespace ctb;
+using namespace ctb_internal;
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+struct __align__(8) Vec4h {
+  __half2 a, b;
+};
+
+template <typename T>
+struct Pack;  // 4 consecutive elements moved as one 16-byte (f32) or 8-byte (f16) access
+template <>
+struct Pack<float> {
+  using type = float4;
+  static __device__ __forceinline__ void unpack(const float4& v, float* f) {
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  static __device__ __forceinline__ float4 pack(const float* f) { return make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <>
+struct Pack<__half> {
+  using type = Vec4h;
+  static __device__ __forceinline__ void unpack(const Vec4h& v, float* f) {
+    float2 x = __half22float2(v.a), y = __half22float2(v.b);
+    f[0] = x.x; f[1] = x.y; f[2] = y.x; f[3] = y.y;
+  }
+  static __device__ __forceinline__ Vec4h pack(const float* f) {
+    Vec4h v;
+    v.a = __floats2half2_rn(f[0], f[1]);
+    v.b = __floats2half2_rn(f[2], f[3]);
+    return v;
+  }
+};
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = red[0];
+#pragma unroll
+  for (int i = 1; i < kWarps; ++i) r = fmaxf(r, red[i]);
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.f;
+#pragma unroll
+  for (int i = 0; i < kWarps; ++i) r += red[i];  // fixed order: deterministic
+  __syncthreads();
+  return r;
+}
+
+// ------------------------------------------------------------------ variant 0
+// MAXV: packs of 4 elements kept in registers per thread (N <= 4*kThreads*MAXV).
+template <typename T, int MAXV, int STAGES>
+__global__ void __launch_bounds__(kThreads) softmax_staged_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                                  int N, int M, long long ld_out, long long ld_in,
+                                                                  int stage_bytes, int* status) {
+  using P = typename Pack<T>::type;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full[STAGES];
+  __shared__ float red[kWarps];
+  const int tid = threadIdx.x;
+  const uint32_t row_bytes = (uint32_t)N * sizeof(T);
+  const int npack = N / 4;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  const int first = blockIdx.x, step = gridDim.x;
+  const int nrows = first < M ? (M - first + step - 1) / step : 0;
+
+  // prologue: fill the ring
+  if (tid == 0) {
+    for (int i = 0; i < STAGES && i < nrows; ++i) {
+      mbar_expect_tx(&full[i], row_bytes);
+      bulk_g2s(smem + (size_t)i * stage_bytes, in + (long long)(first + i * step) * ld_in, row_bytes, &full[i]);
+    }
+  }
+
+  bool alive = true;
+  for (int i = 0; i < nrows && alive; ++i) {
+    const int s = i % STAGES;
+    const uint32_t parity = (i / STAGES) & 1;
+    P* buf = reinterpret_cast<P*>(smem + (size_t)s * stage_bytes);
+    if (!mbar_wait(&full[s], parity, status, DEV_TIMEOUT_TMA)) alive = false;
+    alive = __syncthreads_and(alive);
+    if (!alive) break;
+
+    float x[MAXV][4];
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int p = tid + v * kThreads;
+      if (p < npack) {
+        Pack<T>::unpack(buf[p], x[v]);
+        mx = fmaxf(mx, fmaxf(fmaxf(x[v][0], x[v][1]), fmaxf(x[v][2], x[v][3])));
+      }
+    }
+    mx = block_max(mx, red);
+    float sum = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      if (tid + v * kThreads < npack) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          x[v][k] = expf(x[v][k] - mx);
+          sum += x[v][k];
+        }
+      }
+    }
+    sum = block_sum(sum, red);
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int p = tid + v * kThreads;
+      if (p < npack) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) x[v][k] = x[v][k] / sum;
+        buf[p] = Pack<T>::pack(x[v]);
+      }
+    }
+    fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk store
+    __syncthreads();
+    if (tid == 0) {
+      bulk_s2g(out + (long long)(first + i * step) * ld_out, buf, row_bytes);
+      bulk_commit();
+      // Refill the stage used by the PREVIOUS row: its store was committed one
+      // iteration ago, so waiting for "all but the newest group" has read it.
+      const int nxt = i - 1 + STAGES;
+      if (i >= 1 && nxt < nrows) {
+        bulk_wait_read<1>();
+        const int ps = (i - 1) % STAGES;
+        mbar_expect_tx(&full[ps], row_bytes);
+        bulk_g2s(smem + (size_t)ps * stage_bytes, in + (long long)(first + nxt * step) * ld_in, row_bytes, &full[ps]);
+      }
+    }
+  }
+  if (tid == 0) bulk_wait<0>();  // stores complete before the CTA (and its smem) goes away
+}
+
+// ------------------------------------------------------------------ variant 1
+// VEC = elements per load (4 => Pack<T>, 1 => scalar).  CACHE = register-resident
+// packs per thread; rows with more are re-read from global for the final pass.
+template <typename T, int VEC, int CACHE>
+__global__ void __launch_bounds__(kThreads) softmax_online_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                                  int N, int M, long long ld_out, long long ld_in) {
+  __shared__ float red[kWarps];
+  const int tid = threadIdx.x;
+  const int nvec = (N + VEC - 1) / VEC;  // VEC==4 only when N % 4 == 0
+  const int nstep = (nvec + kThreads - 1) / kThreads;
+
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const T* src = in + (long long)row * ld_in;
+    T* dst = out + (long long)row * ld_out;
+    float cache[CACHE][VEC];
+    float m = -FLT_MAX, l = 0.f;
+
+    auto load = [&](int i, float* f) -> bool {
+      const int p = tid + i * kThreads;
+      if (p >= nvec) return false;
+      if constexpr (VEC == 4) {
+        Pack<T>::unpack(reinterpret_cast<const typename Pack<T>::type*>(src)[p], f);
+      } else {
+        f[0] = (float)src[p];
+      }
+      return true;
+    };
+    auto update = [&](const float* f) {
+      float cm = f[0];
+#pragma unroll
+      for (int k = 1; k < VEC; ++k) cm = fmaxf(cm, f[k]);
+      if (cm > m) {
+        l *= expf(m - cm);
+        m = cm;
+      }
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) l += expf(f[k] - m);
+    };
+
+#pragma unroll
+    for (int i = 0; i < CACHE; ++i)
+      if (i < nstep && load(i, cache[i])) update(cache[i]);
+    for (int i = CACHE; i < nstep; ++i) {
+      float f[VEC];
+      if (load(i, f)) update(f);
+    }
+    const float mg = block_max(m, red);
+    const float lg = block_sum(l * expf(m - mg), red);  // threads with no data: l = 0
+
+    auto store = [&](int i, float* f) {
+      const int p = tid + i * kThreads;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) f[k] = expf(f[k] - mg) / lg;
+      if constexpr (VEC == 4) {
+        reinterpret_cast<typename Pack<T>::type*>(dst)[p] = Pack<T>::pack(f);
+      } else {
+        dst[p] = (T)f[0];
+      }
+    };
+#pragma unroll
+    for (int i = 0; i < CACHE; ++i)
+      if (i < nstep && tid + i * kThreads < nvec) store(i, cache[i]);
+    for (int i = CACHE; i < nstep; ++i) {
+      float f[VEC];
+      if (load(i, f)) store(i, f);
+    }
+  }
+}
+
+template <typename T>
+int launch(ctb_ctx* ctx, cudaStream_t st, T* out, const T* in, int N, int M, long long ldo, long long ldi,
+           int variant) {
+  const bool vec_ok = (N % 4 == 0) && (ldo % 4 == 0) && (ldi % 4 == 0) &&
+                      ((uintptr_t)out % (4 * sizeof(T)) == 0) && ((uintptr_t)in % (4 * sizeof(T)) == 0);
+  if (variant == 0) {
+    const size_t row_bytes = (size_t)N * sizeof(T);
+    if (row_bytes % 16 || (uintptr_t)out % 16 || (uintptr_t)in % 16 || (ldo * sizeof(T)) % 16 ||
+        (ldi * sizeof(T)) % 16)
+      return fail(CTB_BAD_ALIGN,
+                  "ctb_softmax variant 0: rows must start on 16-byte boundaries and N*elemsize be a multiple of 16");
+    constexpr int STAGES = 3, MAXV = 8;
+    if (N > 4 * kThreads * MAXV)
+      return fail(CTB_UNSUPPORTED, "ctb_softmax variant 0: N=%d exceeds the single-tile limit %d; use variant 1", N,
+                  4 * kThreads * MAXV);
+    const int stage_bytes = (int)((row_bytes + 127) & ~size_t(127));
+    const size_t smem = (size_t)STAGES * stage_bytes;
+    auto k = softmax_staged_kernel<T, MAXV, STAGES>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e, "ctb_softmax: shared memory opt-in");
+    int per_sm = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, kThreads, smem);
+    if (per_sm < 1) per_sm = 1;
+    const int grid = min(M, ctx->sm_count * per_sm);
+    k<<<grid, kThreads, smem, st>>>(out, in, N, M, ldo, ldi, stage_bytes, ctx->dev_status);
+  } else {
+    int per_sm = 8;
+    const int grid = min(M, ctx->sm_count * per_sm);
+    if (vec_ok)
+      softmax_online_kernel<T, 4, 8><<<grid, kThreads, 0, st>>>(out, in, N, M, ldo, ldi);
+    else
+      softmax_online_kernel<T, 1, 8><<<grid, kThreads, 0, st>>>(out, in, N, M, ldo, ldi);
+  }
+  CTB_CHECK_LAUNCH("ctb_softmax launch");
+  return CTB_OK;
+}
+
+}  // namespace
+
+extern "C" int ctb_softmax(ctb_ctx* ctx, void* stream, void* output, const void* input, int64_t N, int64_t M,
+                           int64_t ld_out, int64_t ld_in, int variant, int tile_size, int dtype) {
+  CTB_CHECK_CTX(ctx);
+  if (N <= 0 || M < 0 || N > INT32_MAX || M > INT32_MAX)
+    return fail(CTB_BAD_ARG, "ctb_softmax: bad shape N=%lld M=%lld", (long long)N, (long long)M);
+  if (ld_out < N || ld_in < N) return fail(CTB_BAD_ARG, "ctb_softmax: leading dimension smaller than N");
+  if (variant != 0 && variant != 1) return fail(CTB_BAD_ARG, "ctb_softmax: variant must be 0 or 1");
+  if (!is_pow2(tile_size)) return fail(CTB_UNSUPPORTED_TILE, "ctb_softmax: tile_size %d is not a power of two", tile_size);
+  if (variant == 0 && tile_size < N)
+    return fail(CTB_UNSUPPORTED_TILE, "ctb_softmax variant 0: tile_size %d must cover the row (N=%lld)", tile_size,
+                (long long)N);
+  if (M == 0) return CTB_OK;
+  CTB_CHECK_DEV(output);
+  CTB_CHECK_DEV(input);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CTB_F32)
+    return launch<float>(ctx, st, (float*)output, (const float*)input, (int)N, (int)M, ld_out, ld_in, variant);
+  if (dtype == CTB_F16)
+    return launch<__half>(ctx, st, (__half*)output, (const __half*)input, (int)N, (int)M, ld_out, ld_in, variant);
+  return fail(CTB_BAD_ARG, "ctb_softmax: dtype must be CTB_F32 or CTB_F16");
+}

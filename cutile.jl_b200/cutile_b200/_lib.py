@@ -1,0 +1,93 @@
+"""ctypes binding of libcutile_b200.so (the C ABI in include/cutile_b200.h).
+
+The library is the product; this module only loads it and declares the
+signatures.  There is no fallback: if the shared object is missing the import
+fails with instructions to build it, and on a machine without an sm_100 GPU
+every compute call fails with CtbError(NO_DEVICE).
+"""
+import ctypes as C
+import os
+import threading
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libcutile_b200.so")
+
+OK, BAD_ARG, BAD_ALIGN, UNSUPPORTED_TILE, UNSUPPORTED, CUDA_ERROR, NCCL_ERROR, TIMEOUT, NO_DEVICE = range(9)
+F32, F16, BF16 = 0, 1, 2
+
+
+class CtbError(RuntimeError):
+    """Raised for every non-zero status; `.status` is the ctb_status code."""
+
+    def __init__(self, status, message):
+        super().__init__(f"{status_string(status)}: {message}")
+        self.status = status
+
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing. Build it with `python cutile.jl_b200/csrc/build.py` "
+        "(needs nvcc with sm_100a support); there is no CPU fallback.")
+
+lib = C.CDLL(LIB_PATH)
+
+_p, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+# name -> argument types (return type is int unless listed in _RESTYPES)
+SIGNATURES = {
+    "ctb_create": [C.POINTER(_p), _i],
+    "ctb_destroy": [_p],
+    "ctb_last_error": [],
+    "ctb_status_string": [_i],
+    "ctb_version_info": [C.c_char_p, C.c_size_t],
+    "ctb_check_device_status": [_p, _p],
+    "ctb_softmax": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
+    "ctb_layernorm_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i],
+    "ctb_layernorm_bwd_dx_partial_dwdb": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64,
+                                          _i, _i],
+    "ctb_layernorm_bwd_dwdb": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i],
+}
+_RESTYPES = {"ctb_destroy": None, "ctb_last_error": C.c_char_p, "ctb_status_string": C.c_char_p}
+
+for _name, _args in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError here = header and library disagree
+    _fn.argtypes = _args
+    _fn.restype = _RESTYPES.get(_name, _i)
+
+
+def status_string(status):
+    return lib.ctb_status_string(int(status)).decode()
+
+
+def last_error():
+    return lib.ctb_last_error().decode()
+
+
+def check(status):
+    if status != OK:
+        raise CtbError(status, last_error())
+
+
+def version_info():
+    buf = C.create_string_buffer(256)
+    check(lib.ctb_version_info(buf, 256))
+    return buf.value.decode()
+
+
+_ctx_lock = threading.Lock()
+_ctxs = {}
+
+
+def context(device):
+    """The per-device context of this process (created on first use)."""
+    with _ctx_lock:
+        h = _ctxs.get(device)
+        if h is None:
+            out = _p()
+            check(lib.ctb_create(C.byref(out), int(device)))
+            h = _ctxs[device] = out
+        return h
+
+
+def check_device_status(device, stream=0):
+    check(lib.ctb_check_device_status(context(device), _p(stream)))

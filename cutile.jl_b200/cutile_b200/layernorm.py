@@ -1,0 +1,44 @@
+"""LayerNorm forward/backward: the call surface of examples/layernorm.jl.
+
+Memory order of the Julia arrays: X, Y, DX, DY (N, M) are torch [M, N];
+W, B, FINAL_DW, FINAL_DB are [N]; Mean, Rstd are [M]; the partial buffers
+DW, DB (N, GROUP_SIZE_M) are torch [GROUP_SIZE_M, N].
+"""
+from . import _lib
+from ._util import handles, ptr, rows
+
+
+def layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N):
+    """layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N), examples/layernorm.jl:27-68."""
+    ctx, stream = handles(X)
+    ldx, M, N = rows(X, "X")
+    ldy, My, Ny = rows(Y, "Y")
+    if (My, Ny) != (M, N) or W.numel() != N or B.numel() != N or Mean.numel() != M or Rstd.numel() != M:
+        raise _lib.CtbError(_lib.BAD_ARG, "layer_norm_fwd: inconsistent shapes")
+    _lib.check(_lib.lib.ctb_layernorm_fwd(ctx, stream, ptr(X), ptr(W), ptr(B), ptr(Y), ptr(Mean), ptr(Rstd), N, M,
+                                          ldx, ldy, float(eps), int(TILE_N)))
+
+
+def layer_norm_bwd_dx_partial_dwdb(DX, DY, DW, DB, X, W, Mean, Rstd, Locks, GROUP_SIZE_M, TILE_N):
+    """layer_norm_bwd_dx_partial_dwdb(...), examples/layernorm.jl:118-171.
+    `Locks` is accepted for signature compatibility and never touched; DW/DB
+    need no zero-fill."""
+    ctx, stream = handles(X)
+    ldx, M, N = rows(X, "X")
+    lddy, _, _ = rows(DY, "DY")
+    lddx, _, _ = rows(DX, "DX")
+    if DW.shape != (GROUP_SIZE_M, N) or DB.shape != (GROUP_SIZE_M, N) or not DW.is_contiguous() or not DB.is_contiguous():
+        raise _lib.CtbError(_lib.BAD_ARG, "layer_norm_bwd_dx_partial_dwdb: DW/DB must be contiguous (N, GROUP_SIZE_M)")
+    if DY.shape != X.shape or DX.shape != X.shape:
+        raise _lib.CtbError(_lib.BAD_ARG, "layer_norm_bwd_dx_partial_dwdb: DX/DY must have the shape of X")
+    _lib.check(_lib.lib.ctb_layernorm_bwd_dx_partial_dwdb(
+        ctx, stream, ptr(DX), ptr(DY), ptr(DW), ptr(DB), ptr(X), ptr(W), ptr(Mean), ptr(Rstd),
+        ptr(Locks), N, M, ldx, lddy, lddx, int(GROUP_SIZE_M), int(TILE_N)))
+
+
+def layer_norm_bwd_dwdb(DW, DB, FINAL_DW, FINAL_DB, TILE_M, TILE_N):
+    """layer_norm_bwd_dwdb(DW, DB, FINAL_DW, FINAL_DB, TILE_M, TILE_N), examples/layernorm.jl:186-205."""
+    ctx, stream = handles(DW)
+    G, N = DW.shape
+    _lib.check(_lib.lib.ctb_layernorm_bwd_dwdb(ctx, stream, ptr(DW), ptr(DB), ptr(FINAL_DW), ptr(FINAL_DB), N, G,
+                                               int(TILE_M), int(TILE_N)))

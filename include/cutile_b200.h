@@ -1,0 +1,100 @@
+/* libcutile_b200: C ABI of the sm_100a kernel suite that stands in for the
+ * kernels of cuTile.jl's examples (LayerNorm, softmax, GEMM, FMHA, MoE).
+ *
+ * Each entry point replaces one `@cuda backend=cuTile ... kernel(args...)`
+ * launch (reference: src/launch.jl:788-814, the TileKernel call) or one host
+ * wrapper of examples/*.jl; the comment above each declaration names it.
+ *
+ * Conventions
+ *  - Arrays are Julia column-major: the first listed dimension is contiguous.
+ *    Leading dimensions (ld*) and strides are in ELEMENTS, like TileArray
+ *    strides (src/language/types.jl:326-357).
+ *  - All array arguments are DEVICE pointers owned by the caller; a host pointer
+ *    is rejected with CTB_BAD_ARG (the reference raises ArgumentError,
+ *    src/language/types.jl:371-376).
+ *  - `stream` is the raw CUstream/cudaStream_t handle (NULL = default stream).
+ *    Calls only enqueue work; they never synchronise unless stated.
+ *  - Tile-size constants keep the reference's rule: powers of two
+ *    (src/compiler/intrinsics/core.jl:10-19).  They are validated and otherwise
+ *    advisory: the hand-written kernels choose their own blocking.
+ *  - Index arrays (MoE) are 1-based, as in the reference.
+ *  - Every function returns CTB_OK (0) or a positive ctb_status;
+ *    ctb_last_error() gives the message of the calling thread's last failure.
+ *  - There is no CPU fallback: without a usable sm_100 device ctb_create fails.
+ */
+#ifndef CUTILE_B200_H
+#define CUTILE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum ctb_status {
+  CTB_OK = 0,
+  CTB_BAD_ARG = 1,          /* null/host pointer, non-positive size, bad enum      */
+  CTB_BAD_ALIGN = 2,        /* pointer or leading dimension not aligned as needed  */
+  CTB_UNSUPPORTED_TILE = 3, /* tile constant not a power of two / out of range     */
+  CTB_UNSUPPORTED = 4,      /* shape or option outside what the kernels implement  */
+  CTB_CUDA_ERROR = 5,
+  CTB_NCCL_ERROR = 6,
+  CTB_TIMEOUT = 7,          /* a bounded device-side wait ran out                  */
+  CTB_NO_DEVICE = 8         /* no sm_100 device / driver                           */
+} ctb_status;
+
+typedef enum ctb_dtype { CTB_F32 = 0, CTB_F16 = 1, CTB_BF16 = 2 } ctb_dtype;
+
+typedef struct ctb_ctx ctb_ctx;
+
+/* Context = one device + its scratch + its device status word.  Replaces the
+ * per-process state of the reference launch layer (compile cache and module
+ * loading, src/launch.jl:616-625,663-687): kernels are built ahead of time. */
+int ctb_create(ctb_ctx** out, int device);
+void ctb_destroy(ctb_ctx* ctx);
+const char* ctb_last_error(void);
+const char* ctb_status_string(int status);
+/* Counterpart of cuTile.versioninfo() (src/launch.jl:891-903). */
+int ctb_version_info(char* buf, size_t n);
+/* Synchronises `stream`, then reads and clears the device status word.  Returns
+ * CTB_OK, or CTB_TIMEOUT / CTB_BAD_ARG if a kernel recorded a bounded-wait
+ * expiry or a bad index since the last call. */
+int ctb_check_device_status(ctb_ctx* ctx, void* stream);
+
+/* ---- Row softmax -------------------------------------------------------- */
+/* softmax_tma_kernel(output, input, TILE_SIZE)      examples/softmax.jl:18-42
+ * softmax_chunked_kernel(output, input, n_elems, TILE_SIZE)   :48-100
+ * input/output (N, M): M rows of N contiguous elements, row stride ld.
+ * variant 0: whole row staged in shared memory by bulk async copies (needs
+ *            tile_size >= N, N*elemsize % 16 == 0, 16-byte aligned rows);
+ * variant 1: chunks of tile_size with running max/sum (any N).
+ * dtype: CTB_F32 or CTB_F16 (computes in f32, like the reference). */
+int ctb_softmax(ctb_ctx* ctx, void* stream, void* output, const void* input, int64_t N, int64_t M, int64_t ld_out,
+                int64_t ld_in, int variant, int tile_size, int dtype);
+
+/* ---- LayerNorm ---------------------------------------------------------- */
+/* layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N)   examples/layernorm.jl:27-68
+ * X, Y (N, M) f32; W, B (N); Mean, Rstd (M). */
+int ctb_layernorm_fwd(ctb_ctx* ctx, void* stream, const float* X, const float* W, const float* B, float* Y,
+                      float* Mean, float* Rstd, int64_t N, int64_t M, int64_t ldx, int64_t ldy, float eps,
+                      int tile_n);
+/* layer_norm_bwd_dx_partial_dwdb(DX, DY, DW, DB, X, W, Mean, Rstd, Locks,
+ *                                GROUP_SIZE_M, TILE_N)   examples/layernorm.jl:118-171
+ * DW, DB are the (N, group_size_m) partial buffers (scratch owned by the caller);
+ * on return column g holds the sum of dy*xhat (resp. dy) over the rows assigned
+ * to group g.  They need no zero-fill and `locks` is unused (may be NULL): each
+ * partial column is written once by the thread-block cluster that owns it. */
+int ctb_layernorm_bwd_dx_partial_dwdb(ctb_ctx* ctx, void* stream, float* DX, const float* DY, float* DW, float* DB,
+                                      const float* X, const float* W, const float* Mean, const float* Rstd,
+                                      void* locks, int64_t N, int64_t M, int64_t ldx, int64_t lddy, int64_t lddx,
+                                      int group_size_m, int tile_n);
+/* layer_norm_bwd_dwdb(DW, DB, FINAL_DW, FINAL_DB, TILE_M, TILE_N)   examples/layernorm.jl:186-205
+ * Column sums of the (N, group_size_m) partials, in fixed order (deterministic). */
+int ctb_layernorm_bwd_dwdb(ctb_ctx* ctx, void* stream, const float* DW, const float* DB, float* FINAL_DW,
+                           float* FINAL_DB, int64_t N, int group_size_m, int tile_m, int tile_n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUTILE_B200_H */

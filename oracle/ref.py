@@ -1,0 +1,218 @@
+"""numpy restatement of the CPU references in the reference's examples.
+
+TEST INFRASTRUCTURE ONLY (see the package docstring).  Arrays are in the memory
+order of the Julia column-major originals, i.e. numpy shapes are the Julia
+shapes reversed.  ``dtype=np.float64`` is the parity oracle; ``np.float32`` is
+the timed CPU baseline (numpy's OpenBLAS does every contraction, as Julia's
+``mul!`` would).
+"""
+import numpy as np
+
+
+# --------------------------------------------------------------------------- TF32
+def f32_to_tf32_bits(x):
+    """19-bit TF32 pattern sign(1)|exp(8)|mant(10): the float32 pattern with the
+    low 13 mantissa bits dropped, round-to-nearest-even.  Known answers:
+    ``test/types.jl:203-245``; conversion rule:
+    ``src/compiler/intrinsics/conversions.jl:188-197``."""
+    u = np.asarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    isnan = ((u >> 23) & 0xFF == 0xFF) & ((u & 0x7FFFFF) != 0)
+    r = (u + 0xFFF + ((u >> 13) & 1)) >> 13
+    r = np.where(isnan, (u >> 13) | 1, r)
+    return (r & 0x7FFFF).astype(np.uint32)
+
+
+def tf32_round(x):
+    """float32 values rounded (RNE) to TF32 precision, returned as float32."""
+    return (f32_to_tf32_bits(x).astype(np.uint32) << 13).view(np.float32).reshape(np.shape(x))
+
+
+def tf32_trunc(x):
+    """float32 values with the low 13 mantissa bits cleared (what a tensor core
+    that reads raw float32 from shared memory sees)."""
+    u = np.asarray(x, dtype=np.float32).view(np.uint32) & np.uint32(0xFFFFE000)
+    return u.view(np.float32)
+
+
+# ---------------------------------------------------------------------- LayerNorm
+def layernorm_fwd(X, W, B, eps, dtype=np.float64):
+    """``examples/layernorm.jl:284-298``: population variance, rstd = 1/sqrt(var+eps).
+    X[M, N] (rows normalised over N).  Returns Y[M,N], mean[M], rstd[M]."""
+    X = X.astype(dtype)
+    N = X.shape[1]
+    mean = X.sum(axis=1, keepdims=True) / N
+    var = ((X - mean) ** 2).sum(axis=1, keepdims=True) / N
+    rstd = 1.0 / np.sqrt(var + dtype(eps))
+    Y = (X - mean) * rstd * W.astype(dtype) + B.astype(dtype)
+    return Y, mean[:, 0], rstd[:, 0]
+
+
+def layernorm_bwd(X, W, DY, mean, rstd, dtype=np.float64):
+    """``examples/layernorm.jl:302-313``.  Returns DX[M,N], DW[N], DB[N]."""
+    X = X.astype(dtype); DY = DY.astype(dtype); W = W.astype(dtype)
+    N = X.shape[1]
+    xhat = (X - mean.astype(dtype)[:, None]) * rstd.astype(dtype)[:, None]
+    wdy = W * DY
+    c1 = (xhat * wdy).sum(axis=1, keepdims=True) / N
+    c2 = wdy.sum(axis=1, keepdims=True) / N
+    DX = (wdy - (xhat * c1 + c2)) * rstd.astype(dtype)[:, None]
+    return DX, (DY * xhat).sum(axis=0), DY.sum(axis=0)
+
+
+# ------------------------------------------------------------------------ softmax
+def softmax(x, dtype=np.float64):
+    """``examples/softmax.jl:175-188``: per row subtract max, exp, normalise."""
+    x = x.astype(dtype)
+    e = np.exp(x - x.max(axis=1, keepdims=True))
+    return e / e.sum(axis=1, keepdims=True)
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm(A, B, dtype=np.float64):
+    """``examples/matmul.jl:98-101``: C = A*B with Julia A(M,K), B(K,N).
+    Memory-order inputs A[K,M], B[N,K]; returns C[N,M]."""
+    return B.astype(dtype) @ A.astype(dtype)
+
+
+def batched_gemm(A, B, dtype=np.float64):
+    """``examples/batchmatmul.jl:97-106``; A[b,K,M], B[b,N,K] -> C[b,N,M]."""
+    return np.matmul(B.astype(dtype), A.astype(dtype))
+
+
+def swizzle_2d(M, N, tm, tn, group_size_m, bid):
+    """``examples/matmul.jl:13-24``: 1-based block id -> 1-based (bid_m, bid_n)."""
+    cld = lambda a, b: -(-a // b)
+    num_bid_m, num_bid_n = cld(M, tm), cld(N, tn)
+    in_group = group_size_m * num_bid_n
+    bid0 = bid - 1
+    first = (bid0 // in_group) * group_size_m
+    gsz = min(num_bid_m - first, group_size_m)
+    return first + bid0 % gsz + 1, (bid0 % in_group) // gsz + 1
+
+
+# --------------------------------------------------------------------------- FMHA
+def fmha(Q, K, V, qk_scale=None, causal=False, input_pos=0, dtype=np.float64):
+    """``examples/fmha.jl:175-220``.  Q[B,H,Sq,D], K/V[B,KVH,Skv,D] -> Out[B,H,Sq,Dv].
+    KV head of query head h (1-based) is cld(h, H/KVH).  The causal rule with a
+    query offset is the kernel's (``examples/fmha.jl:45-47,99-101``): key j is
+    visible to query i when i + input_pos >= j; ``ref_fmha`` is the
+    input_pos = 0 case."""
+    Bn, H, Sq, D = Q.shape
+    KVH, Skv = K.shape[1], K.shape[2]
+    scale = dtype(1.0 / np.sqrt(D)) if qk_scale is None else dtype(qk_scale)
+    out = np.zeros((Bn, H, Sq, V.shape[3]), dtype=dtype)
+    group = H // KVH
+    if causal:
+        hidden = np.arange(Skv)[None, :] > (np.arange(Sq)[:, None] + input_pos)
+    for b in range(Bn):
+        for h in range(H):
+            kh = h // group
+            s = (Q[b, h].astype(dtype) @ K[b, kh].astype(dtype).T) * scale
+            if causal:
+                s = np.where(hidden, -np.inf, s)
+            m = s.max(axis=1, keepdims=True)
+            m = np.where(np.isinf(m), 0.0, m)
+            p = np.exp(s - m)
+            out[b, h] = (p / p.sum(axis=1, keepdims=True)) @ V[b, kh].astype(dtype)
+    return out
+
+
+# ---------------------------------------------------------------------------- MoE
+def moe_router(X, Wr, topk):
+    """Router of the benchmark configuration (the reference draws ids with
+    ``randperm``, ``examples/moe.jl:323-332``, so this step is specified here):
+    logits[t,e] = sum_k X[t,k]*Wr[e,k] accumulated in float32 in ascending k (each
+    f16*f16 product is exact in float32, so a fused multiply-add and
+    multiply-then-add agree); top-k by value, ties to the smallest expert index
+    (the reference's arg-reduction rule, ``src/language/operations.jl:1675-1677``);
+    gates = softmax over the k chosen logits in float32, stored as f16.
+    X[T,H] f16, Wr[E,H] f16 -> ids[topk,T] int32 (1-based), gates[topk,T] f16,
+    logits[T,E] float32."""
+    T, H = X.shape
+    Xf = X.astype(np.float32); Wf = Wr.astype(np.float32)
+    acc = np.zeros((T, Wr.shape[0]), dtype=np.float32)
+    for k in range(H):
+        acc = acc + Xf[:, k:k + 1] * Wf[None, :, k]
+    work = acc.copy()
+    ids = np.empty((topk, T), dtype=np.int32)
+    sel = np.empty((topk, T), dtype=np.float32)
+    rows = np.arange(T)
+    for s in range(topk):
+        j = np.argmax(work, axis=1)  # first maximum -> smallest index on ties
+        ids[s] = j + 1
+        sel[s] = work[rows, j]
+        work[rows, j] = -np.inf
+    e = np.exp(sel - sel[0:1])
+    gates = (e / e.sum(axis=0, keepdims=True)).astype(np.float32).astype(np.float16)
+    return ids, gates, acc
+
+
+def moe_align_tile_size(topk_ids, tile_m, num_experts):
+    """``examples/moe.jl:142-183``.  topk_ids[topk,T] (memory of Julia (T,topk)),
+    1-based.  Flat slot id = token*topk + slot (slot fastest), stable sort by
+    expert, each expert padded to a multiple of tile_m with the sentinel
+    T*topk+1.  Returns sorted_token_ids int32[blocks*tile_m] (1-based),
+    sorted_expert_ids int32[blocks] (1-based)."""
+    topk, T = topk_ids.shape
+    total = T * topk
+    flat = np.ascontiguousarray(topk_ids.T).reshape(-1).astype(np.int64)
+    perm = np.argsort(flat, kind="stable") + 1
+    counts = np.bincount(flat - 1, minlength=num_experts)
+    blocks = -(-counts // tile_m)
+    nblk = int(blocks.sum())
+    tok = np.full(nblk * tile_m, total + 1, dtype=np.int32)
+    exp = np.zeros(nblk, dtype=np.int32)
+    cb = ct = 0
+    for e in range(num_experts):
+        exp[cb:cb + blocks[e]] = e + 1
+        tok[cb * tile_m: cb * tile_m + counts[e]] = perm[ct:ct + counts[e]]
+        ct += counts[e]; cb += blocks[e]
+    return tok, exp
+
+
+def silu_and_mul(gate, up, dtype=np.float64):
+    """``examples/moe.jl:110-128``: gate/(1+exp(-gate)) * up."""
+    g = gate.astype(dtype)
+    return g / (1.0 + np.exp(-g)) * up.astype(dtype)
+
+
+def moe_ffn(X, w1, w2, topk_weights, topk_ids, dtype=np.float64):
+    """``examples/moe.jl:264-304``.  X[T,H], w1[E,2I,H] (gate rows then up rows),
+    w2[E,H,I], topk_weights/topk_ids[topk,T] -> out[T,H]."""
+    T, H = X.shape
+    E, I = w2.shape[0], w2.shape[2]
+    out = np.zeros((T, H), dtype=dtype)
+    Xd = X.astype(dtype)
+    tw = topk_weights.astype(dtype)
+    for e in range(E):
+        slot, tok = np.nonzero(topk_ids == e + 1)
+        if tok.size == 0:
+            continue
+        w1e = w1[e].astype(dtype)
+        x = Xd[tok]
+        act = silu_and_mul(x @ w1e[:I].T, x @ w1e[I:].T, dtype)
+        y = act @ w2[e].astype(dtype).T
+        np.add.at(out, tok, y * tw[slot, tok][:, None])
+    return out
+
+
+# ------------------------------------------------------------------- error norms
+def rel_fro(out, ref):
+    """||out-ref||_F / ||ref||_F, the norm-wise measure Julia's ``isapprox`` uses
+    on arrays (``examples/matmul.jl:100``)."""
+    out = np.asarray(out, dtype=np.float64); ref = np.asarray(ref, dtype=np.float64)
+    return float(np.linalg.norm(out - ref) / max(np.linalg.norm(ref), 1e-300))
+
+
+def max_rel(out, ref, floor=1e-3):
+    """max |out-ref| / max(|ref|, floor*max|ref|): element-wise relative error
+    with a floor, so that entries that cancel to ~0 do not dominate."""
+    out = np.asarray(out, dtype=np.float64); ref = np.asarray(ref, dtype=np.float64)
+    den = np.maximum(np.abs(ref), floor * np.abs(ref).max())
+    return float((np.abs(out - ref) / den).max())
+
+
+def max_abs_over_max(out, ref):
+    """max |out-ref| / max |ref|."""
+    out = np.asarray(out, dtype=np.float64); ref = np.asarray(ref, dtype=np.float64)
+    return float(np.abs(out - ref).max() / np.abs(ref).max())

@@ -1,0 +1,55 @@
+"""CPU tests of the drop-in boundary: the shared library loads without a GPU
+driver, exports every symbol the public header declares, and its host-side
+argument validation behaves like the reference's (no compute calls here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "cutile_b200.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ctb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from cutile_b200 import _lib
+    names = declared_symbols()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(_lib.lib, n), f"{n} declared in the header but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes signatures and header disagree"
+
+
+def test_version_and_status_strings():
+    import cutile_b200
+    assert "sm_100a" in cutile_b200.version_info()
+    assert cutile_b200._lib.status_string(0) == "OK"
+    assert cutile_b200._lib.status_string(7) == "TIMEOUT"
+
+
+def test_no_cpu_fallback():
+    """Without a device the context cannot be created: the product never computes on the host."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from cutile_b200 import _lib
+    out = ctypes.c_void_p()
+    st = _lib.lib.ctb_create(ctypes.byref(out), 0)
+    assert st == _lib.NO_DEVICE and "no CPU path" in _lib.last_error()
+
+
+def test_null_context_and_host_arrays_rejected():
+    import numpy as np
+    import cutile_b200
+    from cutile_b200 import _lib
+    st = _lib.lib.ctb_softmax(None, None, None, None, 4, 1, 4, 4, 0, 4, 0)
+    assert st == _lib.BAD_ARG and "null context" in _lib.last_error()
+    with pytest.raises(cutile_b200.CtbError) as e:  # host array, like the reference's ArgumentError
+        cutile_b200.softmax.softmax_tma_kernel(np.zeros((2, 4), np.float32), np.zeros((2, 4), np.float32), 4)
+    assert e.value.status == _lib.BAD_ARG

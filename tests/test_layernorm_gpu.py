@@ -1,0 +1,81 @@
+"""GPU parity of the LayerNorm kernels against the float64 oracle.
+
+Tolerance (f32): max|out-ref| / max|ref| <= 1e-5 for Y, dX, Mean, Rstd, dW, dB
+(the reference's own check is norm-wise rtol=1e-2, examples/layernorm.jl:300-312)."""
+import numpy as np
+import pytest
+
+from oracle import inputs, ref
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+
+
+def run_fwd_bwd(cuda, d, G=64, ld=None):
+    import torch
+    ln = cuda.layernorm
+    M, N = d["M"], d["N"]
+    ld = ld or N
+    def dev2d(a):
+        t = torch.zeros(M, ld, device="cuda")
+        t[:, :N] = torch.from_numpy(a).cuda()
+        return t[:, :N]
+    X, DY = dev2d(d["X"]), dev2d(d["DY"])
+    W, B = torch.from_numpy(d["W"]).cuda(), torch.from_numpy(d["B"]).cuda()
+    Y = torch.zeros(M, ld, device="cuda")[:, :N]
+    DX = torch.zeros(M, ld, device="cuda")[:, :N]
+    Mean, Rstd = torch.empty(M, device="cuda"), torch.empty(M, device="cuda")
+    DWp = torch.full((G, N), float("nan"), device="cuda")  # never zero-filled: must be fully overwritten
+    DBp = torch.full((G, N), float("nan"), device="cuda")
+    FDW, FDB = torch.empty(N, device="cuda"), torch.empty(N, device="cuda")
+    ln.layer_norm_fwd(X, W, B, Y, Mean, Rstd, float(d["eps"]), 1024)
+    ln.layer_norm_bwd_dx_partial_dwdb(DX, DY, DWp, DBp, X, W, Mean, Rstd, None, G, 1024)
+    ln.layer_norm_bwd_dwdb(DWp, DBp, FDW, FDB, 32, 1024)
+    torch.cuda.synchronize()
+    return [t.cpu().numpy() for t in (Y, Mean, Rstd, DX, FDW, FDB)]
+
+
+# the reference's main() cases (examples/layernorm.jl:340-348), the benchmark
+# shape, ragged/odd shapes (generic path), wide rows, fewer rows than groups.
+@pytest.mark.parametrize("M,N,G", [(256, 256, 64), (512, 512, 64), (1024, 1024, 64), (4096, 4096, 64),
+                                   (37, 1000, 64), (5, 333, 8), (130, 8192, 16), (3, 2048, 64), (300, 4096, 1)])
+def test_layernorm_parity(cuda, M, N, G):
+    d = inputs.layernorm(M=M, N=N, seed=0)
+    Y, Mean, Rstd, DX, DW, DB = run_fwd_bwd(cuda, d, G)
+    rY, rMean, rRstd = ref.layernorm_fwd(d["X"], d["W"], d["B"], d["eps"])
+    rDX, rDW, rDB = ref.layernorm_bwd(d["X"], d["W"], d["DY"], rMean, rRstd)
+    for name, got, want in (("Y", Y, rY), ("Mean", Mean, rMean), ("Rstd", Rstd, rRstd), ("dX", DX, rDX),
+                            ("dW", DW, rDW), ("dB", DB, rDB)):
+        err = ref.max_abs_over_max(got, want)
+        assert err <= TOL, (name, err)
+        assert ref.rel_fro(got, want) <= 1e-2  # the reference's own criterion
+
+
+def test_layernorm_strided(cuda):
+    d = inputs.layernorm(M=64, N=512, seed=5)
+    Y, Mean, Rstd, DX, DW, DB = run_fwd_bwd(cuda, d, 64, ld=640)
+    rY, rMean, rRstd = ref.layernorm_fwd(d["X"], d["W"], d["B"], d["eps"])
+    rDX, rDW, rDB = ref.layernorm_bwd(d["X"], d["W"], d["DY"], rMean, rRstd)
+    assert ref.max_abs_over_max(Y, rY) <= TOL and ref.max_abs_over_max(DX, rDX) <= TOL
+    assert ref.max_abs_over_max(DW, rDW) <= TOL and ref.max_abs_over_max(DB, rDB) <= TOL
+
+
+def test_layernorm_bwd_is_deterministic(cuda):
+    d = inputs.layernorm(M=2048, N=4096, seed=3)
+    a = run_fwd_bwd(cuda, d)
+    b = run_fwd_bwd(cuda, d)
+    for x, y in zip(a, b):
+        assert np.array_equal(x, y)  # lock-free fixed-order reduction: bitwise repeatable
+
+
+def test_layernorm_rejections(cuda):
+    import torch
+    lib = cuda._lib
+    X = torch.zeros(4, 256, device="cuda")
+    v = torch.zeros(256, device="cuda"); m = torch.zeros(4, device="cuda")
+    with pytest.raises(cuda.CtbError) as e:
+        cuda.layernorm.layer_norm_fwd(X, v, v, torch.empty_like(X), m, m.clone(), 1e-5, 1000)
+    assert e.value.status == lib.UNSUPPORTED_TILE
+    with pytest.raises(cuda.CtbError) as e:
+        cuda.layernorm.layer_norm_fwd(X, v[:100], v, torch.empty_like(X), m, m.clone(), 1e-5, 1024)
+    assert e.value.status == lib.BAD_ARG
