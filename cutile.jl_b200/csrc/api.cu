@@ -69,7 +69,7 @@ EncodeTiledFn encode_tiled() {
 }
 
 int make_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
-              const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+              const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return fail(CTB_CUDA_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t gdim[5], gstr[5];
@@ -81,7 +81,7 @@ int make_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* ba
     if (i > 0) gstr[i - 1] = strides_bytes[i - 1];
   }
   CUresult r = enc(out, dt, rank, const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   swizzle,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(CTB_BAD_ALIGN,

@@ -36,10 +36,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn encode_tiled();
 
-// rank-`rank` tiled map, 128-byte swizzle, zero fill.  dims/box in elements
-// (innermost first), strides in bytes for dims 1..rank-1.
+// rank-`rank` tiled map, zero fill.  dims/box in elements (innermost first),
+// strides in bytes for dims 1..rank-1.
 int make_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
-              const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128 = true);
+              const uint64_t* strides_bytes, const uint32_t* box,
+              CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
 
 #define CTB_CHECK_CTX(ctx)                                                              \
   do {                                                                                  \

@@ -1,0 +1,297 @@
+// Dense and batched GEMM for sm_100a: C(M,N[,b]) = A(M,K[,b]) * B(K,N[,b]),
+// Julia column-major (counterparts of matmul_kernel, examples/matmul.jl:28-60,
+// and batch_matmul_kernel, examples/batchmatmul.jl:15-56).
+//
+// f32 inputs run as TF32 tensor-core MMAs with f32 accumulation (the reference
+// converts f32 -> tf32, examples/matmul.jl:49-52; the tensor core here reads the
+// raw f32 bits from shared memory and ignores the low 13 mantissa bits, i.e.
+// truncation instead of the reference's round-to-nearest-even); f16 inputs run
+// as f16 MMAs with f32 accumulation and an f16 result.
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0     TMA producer: per k-block, A as 128-byte-wide boxes (M contiguous,
+//              "MN-major") and B as one box (K contiguous, "K-major"), 128B swizzle
+//              (32-byte-atom flavour for the tf32 A operand),
+//              into a ring of kStages shared-memory stages guarded by mbarriers;
+//   warp 1     MMA issuer: tcgen05.mma 128 x 256 x (32 bytes of K) from shared-memory
+//              descriptors into one of two 256-column TMEM accumulators;
+//              tcgen05.commit frees the stage / publishes the accumulator;
+//   warps 2-5  epilogue: tcgen05.ld the finished accumulator (lane = row m) and
+//              store C with coalesced 128-byte rows while the MMA warp already
+//              works on the next tile in the other accumulator.
+// Out-of-range parts of edge tiles are zero-filled by TMA and masked on store.
+#include "ctx.h"
+#include "ptx.cuh"
+
+using namespace ctb;
+using namespace ctb_internal;
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 256;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kAccCols = kTileN;  // f32 accumulator columns per tile
+constexpr uint32_t kTmemCols = 512;
+
+template <typename T>
+struct Cfg {
+  static constexpr int ES = sizeof(T);
+  static constexpr int BK = 128 / ES;          // K elements per stage = one 128-byte swizzle span
+  static constexpr int UK = 32 / ES;           // K per MMA instruction
+  static constexpr int CHUNK_M = 128 / ES;     // M elements per A box (128 bytes)
+  static constexpr int A_BOXES = kTileM / CHUNK_M;
+  static constexpr int A_BOX_BYTES = BK * 128;  // BK rows of 128 bytes
+  static constexpr int A_BYTES = A_BOXES * A_BOX_BYTES;
+  static constexpr int B_BYTES = kTileN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr uint32_t FMT = sizeof(T) == 4 ? FMT_TF32 : FMT_F16;
+  // An MN-major tf32 operand must use the 128-byte swizzle with 32-byte atoms
+  // (4 K-rows per swizzle period); 16-bit types use the ordinary 128-byte swizzle.
+  static constexpr uint32_t A_LAYOUT = sizeof(T) == 4 ? SDESC_SW128_ATOM32 : SDESC_SW128;
+  static constexpr uint32_t A_SBO = sizeof(T) == 4 ? 512 : 1024;
+};
+
+struct Params {
+  int M, N, K, batch;
+  long long ldc, strideC;
+  int tiles_m, tiles_n, num_tiles;
+};
+
+__device__ __forceinline__ void tile_coords(const Params& p, int t, int& b, int& tm, int& tn) {
+  const int per_batch = p.tiles_m * p.tiles_n;
+  b = t / per_batch;
+  const int r = t - b * per_batch;
+  // grouped order of examples/matmul.jl:13-24 (GROUP_SIZE_M = 8) for L2 reuse
+  const int in_group = 8 * p.tiles_n;
+  const int first = (r / in_group) * 8;
+  const int gsz = min(p.tiles_m - first, 8);
+  tm = first + (r % in_group) % gsz;
+  tn = (r % in_group) / gsz;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                T* __restrict__ C, const Params p, int* status) {
+  using G = Cfg<T>;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmapA);
+    tma_prefetch_desc(&tmapB);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* abort = &abort_s;
+  const int nk = (p.K + G::BK - 1) / G::BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+        int b, tm, tn;
+        tile_coords(p, t, b, tm, tn);
+        for (int kb = 0; kb < nk; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) goto done;
+          unsigned char* sa = smem + (size_t)stage * G::STAGE_BYTES;
+          mbar_expect_tx(&full[stage], G::STAGE_BYTES);
+#pragma unroll
+          for (int j = 0; j < G::A_BOXES; ++j)
+            tma_load_3d(sa + j * G::A_BOX_BYTES, &tmapA, tm * kTileM + j * G::CHUNK_M, kb * G::BK, b, &full[stage]);
+          tma_load_3d(sa + G::A_BYTES, &tmapB, kb * G::BK, tn * kTileN, b, &full[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(G::FMT, kTileM, kTileN, /*A MN-major*/ 1, /*B K-major*/ 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) goto done;
+        tc_fence_after();
+        const uint32_t d = tmem_base + acc * kAccCols;
+        for (int kb = 0; kb < nk; ++kb) {
+          if (!mbar_wait(&full[stage], phase, status, DEV_TIMEOUT_TMA, abort)) goto done;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * G::STAGE_BYTES);
+          const uint32_t sb = sa + G::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < G::BK / G::UK; ++k) {
+            const uint64_t ad = make_sdesc(sa + k * G::UK * 128, G::A_BOX_BYTES, G::A_SBO, G::A_LAYOUT);
+            const uint64_t bd = make_sdesc_sw128(sb + k * 32, 0, 1024);
+            if constexpr (sizeof(T) == 4)
+              mma_tf32_ss(d, ad, bd, idesc, (kb | k) != 0);
+            else
+              mma_f16_ss(d, ad, bd, idesc, (kb | k) != 0);
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        tc_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    const int sub = warp & 3;  // TMEM lanes [32*sub, 32*sub+32) belong to this warp
+    int it = 0;
+    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      int b, tm, tn;
+      tile_coords(p, t, b, tm, tn);
+      bool ok = mbar_wait(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int m = tm * kTileM + sub * 32 + lane;
+      T* crow = C + (long long)b * p.strideC + m;
+      const uint32_t taddr = tmem_base + acc * kAccCols + ((uint32_t)(sub * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kTileN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tc_wait_ld();
+        const int n0 = tn * kTileN + c * 32;
+        if (m < p.M) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (n0 + j < p.N) {
+              if constexpr (sizeof(T) == 4)
+                crow[(long long)(n0 + j) * p.ldc] = __uint_as_float(r[j]);
+              else
+                crow[(long long)(n0 + j) * p.ldc] = __float2half_rn(__uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <typename T>
+int launch(ctb_ctx* ctx, cudaStream_t st, const T* A, const T* B, T* C, int M, int N, int K, int batch, long long lda,
+           long long ldb, long long ldc, long long sA, long long sB, long long sC) {
+  using G = Cfg<T>;
+  const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap ta, tb;
+  {
+    // A memory: [batch][K][M], M contiguous
+    uint64_t dims[3] = {(uint64_t)M, (uint64_t)K, (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)lda * G::ES, (uint64_t)(batch > 1 ? sA : lda * (long long)K) * G::ES};
+    uint32_t box[3] = {(uint32_t)G::CHUNK_M, (uint32_t)G::BK, 1};
+    int r = make_tmap(&ta, dt, 3, A, dims, str, box,
+                      sizeof(T) == 4 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r) return r;
+  }
+  {
+    // B memory: [batch][N][K], K contiguous
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)ldb * G::ES, (uint64_t)(batch > 1 ? sB : ldb * (long long)N) * G::ES};
+    uint32_t box[3] = {(uint32_t)G::BK, (uint32_t)kTileN, 1};
+    int r = make_tmap(&tb, dt, 3, B, dims, str, box);
+    if (r) return r;
+  }
+  Params p;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.ldc = ldc; p.strideC = sC;
+  p.tiles_m = (M + kTileM - 1) / kTileM;
+  p.tiles_n = (N + kTileN - 1) / kTileN;
+  const long long nt = (long long)p.tiles_m * p.tiles_n * batch;
+  if (nt > INT32_MAX) return fail(CTB_UNSUPPORTED, "ctb_gemm: too many tiles");
+  p.num_tiles = (int)nt;
+  const size_t smem = (size_t)kStages * G::STAGE_BYTES + 1024;
+  auto k = gemm_kernel<T>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return cuda_fail(e, "ctb_gemm: shared memory opt-in");
+  const int grid = (int)std::min<long long>(nt, ctx->sm_count);
+  k<<<grid, kThreads, smem, st>>>(ta, tb, C, p, ctx->dev_status);
+  CTB_CHECK_LAUNCH("ctb_gemm launch");
+  return CTB_OK;
+}
+
+int gemm_common(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                int64_t batch, int64_t lda, int64_t ldb, int64_t ldc, int64_t sA, int64_t sB, int64_t sC, int dtype,
+                int tm, int tn, int tk, const char* who) {
+  CTB_CHECK_CTX(ctx);
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || batch > 65535)
+    return fail(CTB_BAD_ARG, "%s: bad shape M=%lld N=%lld K=%lld batch=%lld", who, (long long)M, (long long)N,
+                (long long)K, (long long)batch);
+  if (lda < M || ldb < K || ldc < M) return fail(CTB_BAD_ARG, "%s: leading dimension too small", who);
+  if (!is_pow2(tm) || !is_pow2(tn) || !is_pow2(tk))
+    return fail(CTB_UNSUPPORTED_TILE, "%s: tile sizes must be powers of two (got %d,%d,%d)", who, tm, tn, tk);
+  if (dtype != CTB_F32 && dtype != CTB_F16) return fail(CTB_BAD_ARG, "%s: dtype must be CTB_F32 or CTB_F16", who);
+  CTB_CHECK_DEV(A); CTB_CHECK_DEV(B); CTB_CHECK_DEV(C);
+  const int es = dtype == CTB_F32 ? 4 : 2;
+  if ((lda * es) % 16 || (ldb * es) % 16 || (sA * es) % 16 || (sB * es) % 16 || (uintptr_t)A % 16 || (uintptr_t)B % 16)
+    return fail(CTB_BAD_ALIGN, "%s: A and B need 16-byte aligned bases, leading dimensions and batch strides (TMA)", who);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CTB_F32)
+    return launch<float>(ctx, st, (const float*)A, (const float*)B, (float*)C, (int)M, (int)N, (int)K, (int)batch, lda,
+                         ldb, ldc, sA, sB, sC);
+  return launch<__half>(ctx, st, (const __half*)A, (const __half*)B, (__half*)C, (int)M, (int)N, (int)K, (int)batch,
+                        lda, ldb, ldc, sA, sB, sC);
+}
+
+}  // namespace
+
+extern "C" {
+
+int ctb_gemm(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+             int64_t lda, int64_t ldb, int64_t ldc, int dtype, int tm, int tn, int tk) {
+  return gemm_common(ctx, stream, A, B, C, M, N, K, 1, lda, ldb, ldc, 0, 0, 0, dtype, tm, tn, tk, "ctb_gemm");
+}
+
+int ctb_gemm_batched(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, int64_t M, int64_t N,
+                     int64_t K, int64_t batch, int64_t lda, int64_t ldb, int64_t ldc, int64_t strideA,
+                     int64_t strideB, int64_t strideC, int dtype, int tm, int tn, int tk) {
+  if (batch > 1 && (strideA < lda * K || strideB < ldb * N || strideC < ldc * N))
+    return fail(CTB_BAD_ARG, "ctb_gemm_batched: batch strides overlap");
+  return gemm_common(ctx, stream, A, B, C, M, N, K, batch, lda, ldb, ldc, strideA, strideB, strideC, dtype, tm, tn, tk,
+                     "ctb_gemm_batched");
+}
+
+}  // extern "C"

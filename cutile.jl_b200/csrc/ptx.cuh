@@ -1,7 +1,7 @@
 // Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk[.tensor]),
 // tcgen05 (MMA, commit, TMEM alloc/ld/st) and a few math/convert helpers.
-// Every wait is bounded: a spin that runs out records a code in the context's
-// device status word and returns false so the kernel can drain and exit.
+// Every wait is bounded in time: a wait that runs out records a code in the
+// context's device status word and returns false so the kernel can drain and exit.
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -18,7 +18,6 @@ enum DevStatus : int {
   DEV_BAD_INDEX = 4,      // an index read from memory was out of range
 };
 
-constexpr uint32_t kSpinLimit = 1u << 24;  // try_wait calls (each blocks up to the HW time slice)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -55,12 +54,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  On expiry records `code` in *status and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait in these kernels
+
+// Bounded wait.  Gives up after kWaitLimitNs, or as soon as *abort (a flag in
+// shared memory that every role of the CTA polls) is set; on expiry records
+// `code` in *status, sets *abort and returns false.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          volatile int* abort = nullptr) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-  if (status) atomicMax(status, code);
-  return false;
+    if ((i & 63u) == 0) {
+      if (abort && *abort) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        if (status) atomicMax(status, code);
+        if (abort) *abort = 1;
+        return false;
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------- TMA
@@ -168,13 +186,20 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_fmt, uint32_t m, u
   return (1u << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) |
          ((m >> 4) << 24);
 }
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
-// lbo/sbo in bytes.  K-major: sbo = stride between 8-row groups, lbo unused.
+// Shared-memory matrix descriptor (descriptor version 1), lbo/sbo in bytes.
+// layout: 2 = 128-byte swizzle with 16-byte atoms (TMA SWIZZLE_128B);
+//         1 = 128-byte swizzle with 32-byte atoms (TMA SWIZZLE_128B_ATOM_32B), the
+//             only swizzled layout the tensor core accepts for an MN-major tf32 operand.
+// K-major: sbo = stride between 8-row groups, lbo unused.
 // MN-major: lbo = stride between 128-byte chunks along M/N, sbo = stride between
-// groups of 8 K-rows.
-__device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+// groups of 8 K-rows (4 K-rows for layout 1).
+enum : uint32_t { SDESC_SW128 = 2, SDESC_SW128_ATOM32 = 1 };
+__device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
   return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) |
-         ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+         ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
+}
+__device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  return make_sdesc(smem_addr, lbo, sbo, SDESC_SW128);
 }
 
 // TMEM -> registers, 32 lanes x 32 bit, 32 consecutive columns (thread = lane).

@@ -46,6 +46,9 @@ SIGNATURES = {
     "ctb_layernorm_bwd_dx_partial_dwdb": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64,
                                           _i, _i],
     "ctb_layernorm_bwd_dwdb": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i],
+    "ctb_gemm": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i],
+    "ctb_gemm_batched": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i,
+                         _i],
 }
 _RESTYPES = {"ctb_destroy": None, "ctb_last_error": C.c_char_p, "ctb_status_string": C.c_char_p}
 

@@ -94,6 +94,21 @@ int ctb_layernorm_bwd_dx_partial_dwdb(ctb_ctx* ctx, void* stream, float* DX, con
 int ctb_layernorm_bwd_dwdb(ctb_ctx* ctx, void* stream, const float* DW, const float* DB, float* FINAL_DW,
                            float* FINAL_DB, int64_t N, int group_size_m, int tile_m, int tile_n);
 
+/* ---- GEMM ---------------------------------------------------------------- */
+/* matmul_kernel(A, B, C, tm, tn, tk)                 examples/matmul.jl:28-60
+ * C(M,N) = A(M,K) * B(K,N), column-major with leading dimensions lda/ldb/ldc.
+ * dtype CTB_F32: TF32 tensor-core operands (low 13 mantissa bits ignored), f32
+ * accumulate, f32 result.  dtype CTB_F16: f16 operands, f32 accumulate, f16 result.
+ * A and B need 16-byte aligned bases and leading dimensions (TMA). */
+int ctb_gemm(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+             int64_t lda, int64_t ldb, int64_t ldc, int dtype, int tm, int tn, int tk);
+/* batch_matmul_kernel(A, B, C, tm, tn, tk)           examples/batchmatmul.jl:15-56
+ * A(M,K,batch), B(K,N,batch), C(M,N,batch), batch last; stride* = elements
+ * between consecutive batches. */
+int ctb_gemm_batched(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, int64_t M, int64_t N,
+                     int64_t K, int64_t batch, int64_t lda, int64_t ldb, int64_t ldc, int64_t strideA,
+                     int64_t strideB, int64_t strideC, int dtype, int tm, int tn, int tk);
+
 #ifdef __cplusplus
 }
 #endif
