@@ -49,6 +49,8 @@ SIGNATURES = {
     "ctb_gemm": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i],
     "ctb_gemm_batched": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i,
                          _i],
+    "ctb_fmha_fwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f, C.c_int32, _i, _i, _i, _i,
+                     _i],
 }
 _RESTYPES = {"ctb_destroy": None, "ctb_last_error": C.c_char_p, "ctb_status_string": C.c_char_p}
 

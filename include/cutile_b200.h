@@ -109,6 +109,19 @@ int ctb_gemm_batched(ctb_ctx* ctx, void* stream, const void* A, const void* B, v
                      int64_t K, int64_t batch, int64_t lda, int64_t ldb, int64_t ldc, int64_t strideA,
                      int64_t strideB, int64_t strideC, int dtype, int tm, int tn, int tk);
 
+/* ---- Flash attention forward ------------------------------------------------ */
+/* fmha_kernel(Q, K, V, Out, qk_scale, input_pos, TILE_D, H, TILE_M, TILE_N,
+ *             QUERY_GROUP_SIZE, CAUSAL, EVEN_K)      examples/fmha.jl:20-139
+ * as launched by cutile_fmha(Q, K, V; ...)           examples/fmha.jl:146-168
+ * Q, Out (D, seq_q, heads, batch); K, V (D, seq_kv, kv_heads, batch), dense,
+ * f16.  heads = kv_heads * query_group_size.  Query i sits at position
+ * i + input_pos for the causal rule.  EVEN_K is derived from seq_kv here.
+ * Implemented: dtype CTB_F16, d_k = d_v = 64. */
+int ctb_fmha_fwd(ctb_ctx* ctx, void* stream, const void* Q, const void* K, const void* V, void* Out, int64_t d_k,
+                 int64_t d_v, int64_t seq_q, int64_t seq_kv, int64_t heads, int64_t kv_heads, int64_t batch,
+                 float qk_scale, int32_t input_pos, int tile_m, int tile_n, int query_group_size, int causal,
+                 int dtype);
+
 #ifdef __cplusplus
 }
 #endif
