@@ -1,0 +1,647 @@
+// Mixture-of-experts FFN for sm_100a (counterparts of examples/moe.jl):
+//   moe_router_kernel   logits = X^T * W_r in f32 (fixed ascending-k order so a
+//                       CPU float32 loop reproduces it bit for bit), top-k by
+//                       value with ties to the smallest index, softmax-renormalised
+//                       gates stored as f16.  (The reference example draws its ids
+//                       at random, examples/moe.jl:323-332; the router belongs to
+//                       the benchmark configuration.)
+//   moe_align_kernel    device version of moe_align_tile_size (:142-183): stable
+//                       sort of the flat slot ids by expert, each expert padded to
+//                       a multiple of tile_m with the sentinel total+1.
+//   moe_gemm_kernel     fused_moe_kernel (:45-105): per (slot block, 128 weight
+//                       rows) acc(N,M) += W_e(N,K) * A(K,M); weights stream by TMA,
+//                       token rows are gathered by slot id into 128B-swizzled
+//                       shared memory, tcgen05.mma accumulates in TMEM.  The
+//                       instruction's N extent is the block's valid slot count
+//                       rounded up to 16, so sparsely filled blocks (16 of 128
+//                       slots at top-2 over 32 experts) cost little tensor time.
+//                       Epilogues: plain f16 scatter with optional routing weight
+//                       (the reference kernel), SwiGLU over a gate/up row pair
+//                       (fuses silu_and_mul_kernel, :110-128), or weighted f32.
+//   moe_combine_kernel  sum over the top-k slots of a token (:256).
+// At 256 tokens the FFN is bound by streaming 403 MB of expert weights from HBM.
+#include <math.h>
+
+#include "ctx.h"
+#include "ptx.cuh"
+
+using namespace ctb;
+using namespace ctb_internal;
+
+namespace {
+
+// ------------------------------------------------------------------ router
+constexpr int kRouterWarps = 4;
+constexpr int kMaxEPL = 8;  // experts per lane -> E <= 256
+
+__global__ void __launch_bounds__(kRouterWarps * 32)
+    moe_router_kernel(const __half* __restrict__ X, const __half* __restrict__ Wr, int* __restrict__ ids,
+                      __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouterWarps + warp;
+  if (t >= T) return;
+  const __half* x = X + (long long)t * H;
+  float acc[kMaxEPL];
+#pragma unroll
+  for (int i = 0; i < kMaxEPL; ++i) acc[i] = 0.f;
+  const int epl = (E + 31) / 32;
+  for (int k0 = 0; k0 < H; k0 += 8) {  // H % 8 == 0
+    const uint4 xv = *reinterpret_cast<const uint4*>(x + k0);
+    const __half* xh = reinterpret_cast<const __half*>(&xv);
+#pragma unroll
+    for (int i = 0; i < kMaxEPL; ++i) {
+      const int e = lane + 32 * i;
+      if (i < epl && e < E) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(Wr + (long long)e * H + k0);
+        const __half* wh = reinterpret_cast<const __half*>(&wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i] = fmaf(__half2float(xh[j]), __half2float(wh[j]), acc[i]);  // ascending k
+      }
+    }
+  }
+  if (logits_out) {
+#pragma unroll
+    for (int i = 0; i < kMaxEPL; ++i)
+      if (i < epl && lane + 32 * i < E) logits_out[(long long)t * E + lane + 32 * i] = acc[i];
+  }
+  float sel[8];
+  int seli[8];
+  for (int s = 0; s < topk; ++s) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kMaxEPL; ++i) {
+      const int e = lane + 32 * i;
+      if (i < epl && e < E && (acc[i] > bv || (acc[i] == bv && e < bi))) {
+        bv = acc[i];
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    sel[s] = bv;
+    seli[s] = bi;
+#pragma unroll
+    for (int i = 0; i < kMaxEPL; ++i)
+      if (lane + 32 * i == bi) acc[i] = -INFINITY;
+  }
+  if (lane == 0) {
+    float sum = 0.f, ex[8];
+    for (int s = 0; s < topk; ++s) {
+      ex[s] = expf(sel[s] - sel[0]);
+      sum += ex[s];
+    }
+    for (int s = 0; s < topk; ++s) {
+      ids[(long long)s * T + t] = seli[s] + 1;
+      gates[(long long)s * T + t] = __float2half_rn(ex[s] / sum);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ align
+constexpr int kAlignThreads = 1024;
+constexpr int kAlignWarps = kAlignThreads / 32;
+constexpr int kMaxExperts = 256;
+
+template <typename IdT>
+__global__ void __launch_bounds__(kAlignThreads)
+    moe_align_kernel(const IdT* __restrict__ topk_ids, int T, int topk, int E, int tile_m,
+                     int* __restrict__ sorted_token_ids, int* __restrict__ sorted_expert_ids,
+                     int* __restrict__ num_blocks, int capacity_blocks, int* status) {
+  extern __shared__ int sm[];
+  int* wcount = sm;                       // [kAlignWarps][E]: per-warp counts, then running offsets
+  int* estart = sm + kAlignWarps * E;     // [E]: first padded position of expert e
+  int* etotal = estart + E;               // [E]
+  __shared__ int bad;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int total = T * topk;
+  const int seg = ((total + kAlignWarps - 1) / kAlignWarps + 31) & ~31;  // ids per warp, multiple of 32
+  const int lo = warp * seg, hi = min(total, lo + seg);
+  if (tid == 0) bad = 0;
+  for (int i = tid; i < kAlignWarps * E; i += kAlignThreads) wcount[i] = 0;
+  for (int i = tid; i < capacity_blocks * tile_m; i += kAlignThreads) sorted_token_ids[i] = total + 1;
+  for (int i = tid; i < capacity_blocks; i += kAlignThreads) sorted_expert_ids[i] = 0;
+  __syncthreads();
+  // flat id i (0-based) = token*topk + slot; topk_ids is (T, topk) column-major
+  auto expert_of = [&](int i) -> int {
+    const int tok = i / topk, slot = i - tok * topk;
+    return (int)topk_ids[(long long)slot * T + tok] - 1;
+  };
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    int e = i < hi ? expert_of(i) : -1;
+    if (i < hi && (e < 0 || e >= E)) {
+      bad = 1;
+      e = -1;
+    }
+    const unsigned grp = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && (grp & ((1u << lane) - 1)) == 0) wcount[warp * E + e] += __popc(grp);
+    __syncwarp();  // the next iteration's group leader may be another lane
+  }
+  __syncthreads();
+  if (tid < E) {
+    int run = 0;
+    for (int w = 0; w < kAlignWarps; ++w) {
+      const int c = wcount[w * E + tid];
+      wcount[w * E + tid] = run;
+      run += c;
+    }
+    etotal[tid] = run;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int blk = 0;
+    for (int e = 0; e < E; ++e) {
+      estart[e] = blk * tile_m;
+      const int nb = (etotal[e] + tile_m - 1) / tile_m;
+      for (int b = 0; b < nb && blk + b < capacity_blocks; ++b) sorted_expert_ids[blk + b] = e + 1;
+      blk += nb;
+    }
+    if (blk > capacity_blocks) bad = 1;
+    *num_blocks = min(blk, capacity_blocks);
+  }
+  __syncthreads();
+  if (bad) {
+    if (tid == 0) {
+      atomicMax(status, DEV_BAD_INDEX);
+      *num_blocks = 0;
+    }
+    return;
+  }
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const int e = i < hi ? expert_of(i) : -1;
+    const unsigned grp = __match_any_sync(0xffffffffu, e);
+    if (e >= 0) {
+      const int rank = __popc(grp & ((1u << lane) - 1));
+      const int pos = estart[e] + wcount[warp * E + e] + rank;
+      sorted_token_ids[pos] = i + 1;
+    }
+    __syncwarp();
+    if (e >= 0 && (grp & ((1u << lane) - 1)) == 0) wcount[warp * E + e] += __popc(grp);
+    __syncwarp();
+  }
+}
+
+// ------------------------------------------------------------------ grouped GEMM
+constexpr int kRows = 128;  // weight rows per tile = MMA M
+constexpr int kBK = 64;     // K elements per stage (128 bytes of f16)
+constexpr int kGemmThreads = 320;
+constexpr int kWTile = kRows * kBK * 2;  // 16 KiB
+
+enum Epilogue : int { EPI_F16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
+
+struct GemmParams {
+  const __half* A;        // token rows, K contiguous
+  long long lda;
+  int a_rows;             // rows of A
+  const int* sorted_ids;  // 1-based flat slot ids, padded with total+1
+  const int* expert_ids;  // 1-based expert per block (0 = unused block)
+  const int* num_blocks_dev;
+  int num_blocks_host;    // >= 0: use this instead of *num_blocks_dev
+  const __half* topk_w;   // routing weights, may be null
+  int w_tokens, w_topk;   // w_tokens == 0: topk_w is flat, indexed by id-1; else (T, topk) column-major
+  int replicas, mul_weight;
+  int K, N;               // N = output rows per expert (SwiGLU: the weight tensor holds 2N rows)
+  int E, tile_m, total;
+  void* C;                // f16 or f32, element (n, id-1) at C[(id-1)*ldc + n]
+  long long ldc;
+  int n_tiles, stages, stage_bytes;
+};
+
+// number of leading slots of the block that have to take part (last valid + 1)
+__device__ __forceinline__ int block_extent(const int* ids, int tile_m, int total, int lane) {
+  int last = 0;
+  for (int r = lane; r < tile_m; r += 32)
+    if (ids[r] >= 1 && ids[r] <= total) last = r + 1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
+  return last;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GemmParams p, int* status) {
+  constexpr int NW = EPI == EPI_SWIGLU ? 2 : 1;  // weight tiles per stage
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kMaxStages = 8;
+  __shared__ __align__(8) uint64_t w_full[kMaxStages], b_full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&w_full[s], 1);
+      mbar_init(&b_full[s], 4);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_s, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_base_s;
+  volatile int* abort = &abort_s;
+  const int nblocks = p.num_blocks_host >= 0 ? p.num_blocks_host : *p.num_blocks_dev;
+  const int items = nblocks * p.n_tiles;
+  const int nk = (p.K + kBK - 1) / kBK;
+  const int wbytes = NW * kWTile;
+
+  if (warp == 0) {
+    // ---- weight producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int it = blockIdx.x; it < items; it += gridDim.x) {
+        const int bm = it / p.n_tiles, nt = it - bm * p.n_tiles;
+        const int e = p.expert_ids[bm] - 1;
+        if (e < 0 || e >= p.E) continue;
+        for (int kb = 0; kb < nk; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) goto done;
+          unsigned char* dst = smem + (size_t)stage * p.stage_bytes;
+          mbar_expect_tx(&w_full[stage], wbytes);
+          tma_load_3d(dst, &tmW, kb * kBK, nt * kRows, e, &w_full[stage]);
+          if (NW == 2) tma_load_3d(dst + kWTile, &tmW, kb * kBK, p.N + nt * kRows, e, &w_full[stage]);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    int stage = 0, n = 0;
+    uint32_t phase = 0;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+      const int bm = it / p.n_tiles;
+      const int e = p.expert_ids[bm] - 1;
+      if (e < 0 || e >= p.E) continue;
+      const int ext = block_extent(p.sorted_ids + (long long)bm * p.tile_m, p.tile_m, p.total, lane);
+      const int nmma = max(16, (ext + 15) & ~15);
+      const int acc = n & 1;
+      const uint32_t acc_phase = (n >> 1) & 1;
+      ++n;
+      int failed = 0;
+      if (lane == 0) {
+        const uint32_t idesc = make_idesc(FMT_F16, kRows, (uint32_t)nmma, 0, 0);
+        failed = !mbar_wait(&acc_empty[acc], acc_phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+        tc_fence_after();
+        const uint32_t d = tmem + acc * 256;
+        for (int kb = 0; kb < nk && !failed; ++kb) {
+          if (!mbar_wait(&w_full[stage], phase, status, DEV_TIMEOUT_TMA, abort) ||
+              !mbar_wait(&b_full[stage], phase, status, DEV_TIMEOUT_SLOT, abort)) {
+            failed = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sw = smem_u32(smem + (size_t)stage * p.stage_bytes);
+          const uint32_t sb = sw + wbytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t bd = make_sdesc_sw128(sb + k * 32, 0, 1024);
+            mma_f16_ss(d, make_sdesc_sw128(sw + k * 32, 0, 1024), bd, idesc, (kb | k) != 0);
+            if (NW == 2) mma_f16_ss(d + 128, make_sdesc_sw128(sw + kWTile + k * 32, 0, 1024), bd, idesc, (kb | k) != 0);
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!failed) tc_commit(&acc_full[acc]);
+      }
+      failed = __shfl_sync(0xffffffffu, failed, 0);
+      if (failed) break;
+    }
+  } else if (warp < 6) {
+    // ---- token-row gather into the swizzled B operand
+    const int g = threadIdx.x - 64;  // 0..127
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+      const int bm = it / p.n_tiles;
+      const int e = p.expert_ids[bm] - 1;
+      if (e < 0 || e >= p.E) continue;
+      const int* ids = p.sorted_ids + (long long)bm * p.tile_m;
+      const int ext = block_extent(ids, p.tile_m, p.total, lane);
+      const int nmma = max(16, (ext + 15) & ~15);
+      const __half* src = nullptr;
+      if (g < p.tile_m) {
+        const int id = ids[g];
+        if (id >= 1 && id <= p.total) {
+          const int tok = (id - 1) / p.replicas;  // cld(id, replicas) - 1
+          if (tok < p.a_rows) src = p.A + (long long)tok * p.lda;
+        }
+      }
+      const uint32_t roff = (uint32_t)(g >> 3) * 1024 + (uint32_t)(g & 7) * 128;
+      for (int kb = 0; kb < nk; ++kb) {
+        bool ok = mbar_wait(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) goto done;
+        if (g < nmma) {
+          unsigned char* dst = smem + (size_t)stage * p.stage_bytes + wbytes + roff;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int k = kb * kBK + c * 8;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (src && k < p.K) v = *reinterpret_cast<const uint4*>(src + k);
+            *reinterpret_cast<uint4*>(dst + ((c ^ (g & 7)) << 4)) = v;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&b_full[stage]);
+        if (++stage == p.stages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // ---- epilogue
+    const int sub = warp & 3;
+    const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
+    int n = 0;
+    for (int it = blockIdx.x; it < items; it += gridDim.x) {
+      const int bm = it / p.n_tiles, nt = it - bm * p.n_tiles;
+      const int e = p.expert_ids[bm] - 1;
+      if (e < 0 || e >= p.E) continue;
+      const int* ids = p.sorted_ids + (long long)bm * p.tile_m;
+      const int ext = block_extent(ids, p.tile_m, p.total, lane);
+      const int acc = n & 1;
+      const uint32_t acc_phase = (n >> 1) & 1;
+      ++n;
+      bool ok = mbar_wait(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) goto done;
+      tc_fence_after();
+      const int row = nt * kRows + sub * 32 + lane;
+      const uint32_t taddr = tmem + lane_addr + acc * 256;
+      for (int c0 = 0; c0 < ext; c0 += 16) {
+        uint32_t ga[16], up[16];
+        tmem_ld16(taddr + c0, ga);
+        if (EPI == EPI_SWIGLU) tmem_ld16(taddr + 128 + c0, up);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int slot = c0 + j;
+          if (slot >= ext) break;
+          const int id = ids[slot];  // uniform across the warp
+          if (id < 1 || id > p.total || row >= p.N) continue;
+          float v = __uint_as_float(ga[j]);
+          if (EPI == EPI_SWIGLU) {
+            // silu(g) * u with flush-to-zero and an approximate reciprocal (examples/moe.jl:117-124)
+            const float sig = rcp_approx_ftz(1.0f + __expf(-v));
+            v = v * sig * __uint_as_float(up[j]);
+          }
+          if (p.mul_weight) {
+            const int f = id - 1;
+            v *= __half2float(p.topk_w[p.w_tokens ? (long long)(f % p.w_topk) * p.w_tokens + f / p.w_topk : f]);
+          }
+          if (EPI == EPI_F32)
+            reinterpret_cast<float*>(p.C)[(long long)(id - 1) * p.ldc + row] = v;
+          else
+            reinterpret_cast<__half*>(p.C)[(long long)(id - 1) * p.ldc + row] = __float2half_rn(v);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+done:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------ small kernels
+__global__ void moe_combine_kernel(const float* __restrict__ slots, __half* __restrict__ out, int T, int H, int topk) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over T*H/2
+  const int h2 = H / 2;
+  if (i >= (long long)T * h2) return;
+  const int t = (int)(i / h2), h = (int)(i - (long long)t * h2) * 2;
+  float a = 0.f, b = 0.f;
+  for (int s = 0; s < topk; ++s) {  // ascending slot: fixed order
+    const float2 v = *reinterpret_cast<const float2*>(slots + ((long long)t * topk + s) * H + h);
+    a += v.x;
+    b += v.y;
+  }
+  *reinterpret_cast<__half2*>(out + (long long)t * H + h) = __floats2half2_rn(a, b);
+}
+
+__global__ void moe_silu_and_mul_kernel(const __half* __restrict__ A, const __half* __restrict__ B,
+                                        __half* __restrict__ C, int n, long long cols, long long lda, long long ldb,
+                                        long long ldc) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= cols * n) return;
+  const long long col = i / n;
+  const int r = (int)(i - col * n);
+  const float a = __half2float(A[col * lda + r]), b = __half2float(B[col * ldb + r]);
+  const float sig = rcp_approx_ftz(1.0f + __expf(-a));
+  C[col * ldc + r] = __float2half_rn(a * sig * b);
+}
+
+// ------------------------------------------------------------------ host side
+int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long long lda, int a_rows, const __half* W,
+                int K, int wrows, int N, int E, const __half* topk_w, const int* sorted_ids, const int* expert_ids,
+                const int* nblocks_dev, int nblocks_host, int max_blocks, int replicas, int mul_weight, int tile_m,
+                int total, void* C, long long ldc, int w_tokens = 0, int w_topk = 1) {
+  CUtensorMap tw;
+  uint64_t dims[3] = {(uint64_t)K, (uint64_t)wrows, (uint64_t)E};
+  uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)K * wrows * 2};
+  uint32_t box[3] = {kBK, kRows, 1};
+  int r = make_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, W, dims, str, box);
+  if (r) return r;
+  GemmParams p;
+  p.A = A; p.lda = lda; p.a_rows = a_rows;
+  p.sorted_ids = sorted_ids; p.expert_ids = expert_ids;
+  p.num_blocks_dev = nblocks_dev; p.num_blocks_host = nblocks_host;
+  p.topk_w = topk_w; p.replicas = replicas; p.mul_weight = mul_weight;
+  p.w_tokens = w_tokens; p.w_topk = w_topk;
+  p.K = K; p.N = N; p.E = E; p.tile_m = tile_m; p.total = total;
+  p.C = C; p.ldc = ldc;
+  p.n_tiles = (N + kRows - 1) / kRows;
+  const int nw = epi == EPI_SWIGLU ? 2 : 1;
+  p.stage_bytes = nw * kWTile + tile_m * 128;
+  p.stages = std::min(8, (int)((220 * 1024) / p.stage_bytes));
+  const size_t smem = (size_t)p.stages * p.stage_bytes + 1024;
+  const long long items = (long long)max_blocks * p.n_tiles;
+  const int grid = (int)std::max<long long>(1, std::min<long long>(items, ctx->sm_count));
+  cudaError_t e;
+#define CTB_LAUNCH_MOE(EPI)                                                                              \
+  e = cudaFuncSetAttribute(moe_gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+  if (e != cudaSuccess) return cuda_fail(e, "moe gemm: shared memory opt-in");                           \
+  moe_gemm_kernel<EPI><<<grid, kGemmThreads, smem, st>>>(tw, p, ctx->dev_status);
+  if (epi == EPI_SWIGLU) { CTB_LAUNCH_MOE(EPI_SWIGLU) }
+  else if (epi == EPI_F32) { CTB_LAUNCH_MOE(EPI_F32) }
+  else { CTB_LAUNCH_MOE(EPI_F16) }
+#undef CTB_LAUNCH_MOE
+  CTB_CHECK_LAUNCH("moe gemm launch");
+  return CTB_OK;
+}
+
+int launch_align(ctb_ctx* ctx, cudaStream_t st, const void* topk_ids, int ids_bits, int T, int topk, int E, int tile_m,
+                 int* sorted_token_ids, int* sorted_expert_ids, int* num_blocks, int capacity) {
+  const size_t smem = (size_t)(kAlignWarps * E + 2 * E) * sizeof(int);
+  if (ids_bits == 32)
+    moe_align_kernel<int><<<1, kAlignThreads, smem, st>>>((const int*)topk_ids, T, topk, E, tile_m, sorted_token_ids,
+                                                          sorted_expert_ids, num_blocks, capacity, ctx->dev_status);
+  else
+    moe_align_kernel<long long><<<1, kAlignThreads, smem, st>>>((const long long*)topk_ids, T, topk, E, tile_m,
+                                                                sorted_token_ids, sorted_expert_ids, num_blocks,
+                                                                capacity, ctx->dev_status);
+  CTB_CHECK_LAUNCH("moe align launch");
+  return CTB_OK;
+}
+
+int check_tile(const char* who, int tile_m, int tile_n, int tile_k) {
+  if (!is_pow2(tile_m) || !is_pow2(tile_n) || !is_pow2(tile_k))
+    return fail(CTB_UNSUPPORTED_TILE, "%s: tile sizes must be powers of two (got %d,%d,%d)", who, tile_m, tile_n, tile_k);
+  if (tile_m < 16 || tile_m > 128)
+    return fail(CTB_UNSUPPORTED_TILE, "%s: tile_m must be between 16 and 128 (got %d)", who, tile_m);
+  return CTB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t ctb_moe_max_blocks(int64_t T, int64_t topk, int64_t E, int tile_m) {
+  if (T < 0 || topk <= 0 || E <= 0 || tile_m <= 0) return 0;
+  return (T * topk + tile_m - 1) / tile_m + E;  // sum_e ceil(c_e / tile_m) <= total/tile_m + E
+}
+
+int ctb_moe_router(ctb_ctx* ctx, void* stream, const void* hidden, const void* W_r, int32_t* topk_ids,
+                   void* topk_weights, float* logits, int64_t T, int64_t H, int64_t E, int topk) {
+  CTB_CHECK_CTX(ctx);
+  if (T < 0 || H <= 0 || E <= 0 || topk <= 0) return fail(CTB_BAD_ARG, "ctb_moe_router: non-positive dimension");
+  if (E > 32 * kMaxEPL) return fail(CTB_UNSUPPORTED, "ctb_moe_router: at most %d experts", 32 * kMaxEPL);
+  if (topk > 8 || topk > E) return fail(CTB_UNSUPPORTED, "ctb_moe_router: topk must be <= min(8, E)");
+  if (H % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_router: hidden size must be a multiple of 8");
+  if (T == 0) return CTB_OK;
+  CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(W_r); CTB_CHECK_DEV(topk_ids); CTB_CHECK_DEV(topk_weights);
+  if ((uintptr_t)hidden % 16 || (uintptr_t)W_r % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_router: 16-byte alignment");
+  moe_router_kernel<<<(int)((T + kRouterWarps - 1) / kRouterWarps), kRouterWarps * 32, 0,
+                      static_cast<cudaStream_t>(stream)>>>((const __half*)hidden, (const __half*)W_r, topk_ids,
+                                                           (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk);
+  CTB_CHECK_LAUNCH("ctb_moe_router launch");
+  return CTB_OK;
+}
+
+int ctb_moe_align(ctb_ctx* ctx, void* stream, const void* topk_ids, int ids_bits, int64_t T, int64_t topk, int64_t E,
+                  int tile_m, int32_t* sorted_token_ids, int32_t* sorted_expert_ids, int32_t* num_blocks,
+                  int64_t capacity_blocks) {
+  CTB_CHECK_CTX(ctx);
+  if (T <= 0 || topk <= 0 || E <= 0 || T * topk > (1 << 24)) return fail(CTB_BAD_ARG, "ctb_moe_align: bad shape");
+  if (E > kMaxExperts) return fail(CTB_UNSUPPORTED, "ctb_moe_align: at most %d experts", kMaxExperts);
+  if (ids_bits != 32 && ids_bits != 64) return fail(CTB_BAD_ARG, "ctb_moe_align: ids_bits must be 32 or 64");
+  if (!is_pow2(tile_m)) return fail(CTB_UNSUPPORTED_TILE, "ctb_moe_align: tile_m %d is not a power of two", tile_m);
+  if (capacity_blocks < ctb_moe_max_blocks(T, topk, E, tile_m))
+    return fail(CTB_BAD_ARG, "ctb_moe_align: capacity_blocks %lld < ctb_moe_max_blocks = %lld", (long long)capacity_blocks,
+                (long long)ctb_moe_max_blocks(T, topk, E, tile_m));
+  CTB_CHECK_DEV(topk_ids); CTB_CHECK_DEV(sorted_token_ids); CTB_CHECK_DEV(sorted_expert_ids); CTB_CHECK_DEV(num_blocks);
+  return launch_align(ctx, static_cast<cudaStream_t>(stream), topk_ids, ids_bits, (int)T, (int)topk, (int)E, tile_m,
+                      sorted_token_ids, sorted_expert_ids, num_blocks, (int)capacity_blocks);
+}
+
+int ctb_moe_fused_gemm(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, const void* topk_weights,
+                       const int32_t* sorted_token_ids, const int32_t* sorted_expert_ids, int64_t num_slots_padded,
+                       int64_t K, int64_t N, int64_t E, int64_t a_cols, int64_t c_cols, int num_token_replicas,
+                       int mul_routed_weight, int tile_m, int tile_n, int tile_k) {
+  CTB_CHECK_CTX(ctx);
+  int r = check_tile("ctb_moe_fused_gemm", tile_m, tile_n, tile_k);
+  if (r) return r;
+  if (K <= 0 || N <= 0 || E <= 0 || a_cols <= 0 || c_cols <= 0 || num_token_replicas <= 0 || num_slots_padded < 0 ||
+      num_slots_padded % tile_m)
+    return fail(CTB_BAD_ARG, "ctb_moe_fused_gemm: bad shape");
+  if (K % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_fused_gemm: K must be a multiple of 8");
+  if (num_slots_padded == 0) return CTB_OK;
+  CTB_CHECK_DEV(A); CTB_CHECK_DEV(B); CTB_CHECK_DEV(C); CTB_CHECK_DEV(sorted_token_ids); CTB_CHECK_DEV(sorted_expert_ids);
+  if (mul_routed_weight) CTB_CHECK_DEV(topk_weights);
+  if ((uintptr_t)A % 16 || (uintptr_t)B % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_fused_gemm: 16-byte alignment");
+  const int nb = (int)(num_slots_padded / tile_m);
+  return launch_gemm(ctx, static_cast<cudaStream_t>(stream), EPI_F16, (const __half*)A, K, (int)a_cols,
+                     (const __half*)B, (int)K, (int)N, (int)N, (int)E, (const __half*)topk_weights, sorted_token_ids,
+                     sorted_expert_ids, nullptr, nb, nb, num_token_replicas, mul_routed_weight, tile_m, (int)c_cols, C,
+                     N);
+}
+
+int ctb_moe_silu_and_mul(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, int64_t n, int64_t cols,
+                         int64_t lda, int64_t ldb, int64_t ldc, int tile_n) {
+  CTB_CHECK_CTX(ctx);
+  if (n <= 0 || cols < 0 || lda < n || ldb < n || ldc < n) return fail(CTB_BAD_ARG, "ctb_moe_silu_and_mul: bad shape");
+  if (!is_pow2(tile_n) || tile_n < n)
+    return fail(CTB_UNSUPPORTED_TILE, "ctb_moe_silu_and_mul: TILE_N must be a power of two >= the row count");
+  if (cols == 0) return CTB_OK;
+  CTB_CHECK_DEV(A); CTB_CHECK_DEV(B); CTB_CHECK_DEV(C);
+  const long long tot = n * cols;
+  moe_silu_and_mul_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const __half*)A, (const __half*)B, (__half*)C, (int)n, cols, lda, ldb, ldc);
+  CTB_CHECK_LAUNCH("ctb_moe_silu_and_mul launch");
+  return CTB_OK;
+}
+
+int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, const void* w2,
+                const void* topk_weights, const void* topk_ids, int ids_bits, void* out, int64_t T, int64_t H,
+                int64_t I, int64_t E, int64_t topk, int tile_m, int tile_n, int tile_k) {
+  CTB_CHECK_CTX(ctx);
+  int r = check_tile("ctb_moe_ffn", tile_m, tile_n, tile_k);
+  if (r) return r;
+  if (T <= 0 || H <= 0 || I <= 0 || E <= 0 || topk <= 0 || T * topk > (1 << 24))
+    return fail(CTB_BAD_ARG, "ctb_moe_ffn: bad shape");
+  if (E > kMaxExperts) return fail(CTB_UNSUPPORTED, "ctb_moe_ffn: at most %d experts", kMaxExperts);
+  if (H % 8 || I % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_ffn: hidden and intermediate sizes must be multiples of 8");
+  if (ids_bits != 32 && ids_bits != 64) return fail(CTB_BAD_ARG, "ctb_moe_ffn: ids_bits must be 32 or 64");
+  CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(w1); CTB_CHECK_DEV(w2); CTB_CHECK_DEV(topk_weights); CTB_CHECK_DEV(topk_ids);
+  CTB_CHECK_DEV(out);
+  if ((uintptr_t)hidden % 16 || (uintptr_t)w1 % 16 || (uintptr_t)w2 % 16 || (uintptr_t)out % 4)
+    return fail(CTB_BAD_ALIGN, "ctb_moe_ffn: 16-byte alignment of hidden, w1, w2");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int total = (int)(T * topk);
+  const int cap = (int)ctb_moe_max_blocks(T, topk, E, tile_m);
+  // scratch: sorted ids | expert ids | block count | activations (I, total) f16 | per-slot outputs (H, total) f32
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  const size_t o_tok = 0, o_exp = up((size_t)cap * tile_m * 4), o_nb = o_exp + up((size_t)cap * 4), o_act = o_nb + 256,
+               o_slots = o_act + up((size_t)total * I * 2), bytes = o_slots + up((size_t)total * H * 4);
+  void* ws;
+  r = workspace(ctx, bytes, &ws);
+  if (r) return r;
+  unsigned char* w = (unsigned char*)ws;
+  int* s_tok = (int*)(w + o_tok);
+  int* s_exp = (int*)(w + o_exp);
+  int* s_nb = (int*)(w + o_nb);
+  __half* act = (__half*)(w + o_act);
+  float* slots = (float*)(w + o_slots);
+  r = launch_align(ctx, st, topk_ids, ids_bits, (int)T, (int)topk, (int)E, tile_m, s_tok, s_exp, s_nb, cap);
+  if (r) return r;
+  // gate/up projection with the SwiGLU epilogue: act(:, id) = silu(Wg x) * (Wu x)
+  r = launch_gemm(ctx, st, EPI_SWIGLU, (const __half*)hidden, H, (int)T, (const __half*)w1, (int)H, (int)(2 * I),
+                  (int)I, (int)E, nullptr, s_tok, s_exp, s_nb, -1, cap, (int)topk, 0, tile_m, total, act, I);
+  if (r) return r;
+  // down projection scaled by the routing weight, one f32 column per slot
+  r = launch_gemm(ctx, st, EPI_F32, act, I, total, (const __half*)w2, (int)I, (int)H, (int)H, (int)E,
+                  (const __half*)topk_weights, s_tok, s_exp, s_nb, -1, cap, 1, 1, tile_m, total, slots, H, (int)T,
+                  (int)topk);
+  if (r) return r;
+  if (H % 2) return fail(CTB_BAD_ALIGN, "ctb_moe_ffn: H must be even");
+  const long long n2 = T * (H / 2);
+  moe_combine_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(slots, (__half*)out, (int)T, (int)H, (int)topk);
+  CTB_CHECK_LAUNCH("ctb_moe_ffn combine launch");
+  return CTB_OK;
+}
+
+}  // extern "C"

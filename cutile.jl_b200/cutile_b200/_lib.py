@@ -51,8 +51,15 @@ SIGNATURES = {
                          _i],
     "ctb_fmha_fwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f, C.c_int32, _i, _i, _i, _i,
                      _i],
+    "ctb_moe_max_blocks": [_i64, _i64, _i64, _i],
+    "ctb_moe_router": [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i],
+    "ctb_moe_align": [_p, _p, _p, _i, _i64, _i64, _i64, _i, _p, _p, _p, _i64],
+    "ctb_moe_fused_gemm": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i],
+    "ctb_moe_silu_and_mul": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i],
+    "ctb_moe_ffn": [_p, _p, _p, _p, _p, _p, _p, _i, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i],
 }
-_RESTYPES = {"ctb_destroy": None, "ctb_last_error": C.c_char_p, "ctb_status_string": C.c_char_p}
+_RESTYPES = {"ctb_destroy": None, "ctb_last_error": C.c_char_p, "ctb_status_string": C.c_char_p,
+             "ctb_moe_max_blocks": _i64}
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)  # AttributeError here = header and library disagree

@@ -122,6 +122,59 @@ int ctb_fmha_fwd(ctb_ctx* ctx, void* stream, const void* Q, const void* K, const
                  float qk_scale, int32_t input_pos, int tile_m, int tile_n, int query_group_size, int causal,
                  int dtype);
 
+/* ---- Mixture of experts -------------------------------------------------------- */
+/* Upper bound on the number of tile_m-slot blocks moe_align can emit:
+ * ceil(T*topk / tile_m) + E.  Size sorted_token_ids / sorted_expert_ids with it. */
+int64_t ctb_moe_max_blocks(int64_t T, int64_t topk, int64_t E, int tile_m);
+
+/* Router of the benchmark configuration (no counterpart kernel in the reference,
+ * which draws ids with randperm, examples/moe.jl:323-332).  hidden (H, T) f16,
+ * W_r (H, E) f16.  logits accumulate in f32 in ascending k; top-k by value, ties
+ * to the smallest index (the reference's arg-reduction rule,
+ * src/language/operations.jl:1675-1677); gates = softmax over the chosen logits.
+ * Outputs: topk_ids (T, topk) int32, 1-based; topk_weights (T, topk) f16;
+ * logits (E, T) f32 or NULL. */
+int ctb_moe_router(ctb_ctx* ctx, void* stream, const void* hidden, const void* W_r, int32_t* topk_ids,
+                   void* topk_weights, float* logits, int64_t T, int64_t H, int64_t E, int topk);
+
+/* moe_align_tile_size(topk_ids, tile_m, num_experts)      examples/moe.jl:142-183
+ * Runs on the device (the reference copies the ids to the host and sorts there).
+ * topk_ids (T, topk), 1-based, 32- or 64-bit integers (ids_bits).  Outputs, sized
+ * for capacity_blocks >= ctb_moe_max_blocks(...): sorted_token_ids
+ * [capacity_blocks*tile_m] (flat slot ids, sentinel T*topk+1), sorted_expert_ids
+ * [capacity_blocks] (0 marks unused blocks), num_blocks[1] (device). */
+int ctb_moe_align(ctb_ctx* ctx, void* stream, const void* topk_ids, int ids_bits, int64_t T, int64_t topk, int64_t E,
+                  int tile_m, int32_t* sorted_token_ids, int32_t* sorted_expert_ids, int32_t* num_blocks,
+                  int64_t capacity_blocks);
+
+/* fused_moe_kernel(A, B, C, topk_weights, sorted_token_ids, sorted_expert_ids,
+ *                  num_token_replicas, mul_routed_weight, TILE_M, TILE_N, TILE_K)
+ *                                                          examples/moe.jl:45-105
+ * A (K, a_cols) f16; B (K, N, E) f16; C (N, c_cols) f16; topk_weights flat
+ * [c_cols] f16 (used when mul_routed_weight); sorted_token_ids [num_slots_padded],
+ * sorted_expert_ids [num_slots_padded / tile_m].  Column id of C receives
+ * B_e * A[:, cld(id, num_token_replicas)]; ids > c_cols are padding. */
+int ctb_moe_fused_gemm(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, const void* topk_weights,
+                       const int32_t* sorted_token_ids, const int32_t* sorted_expert_ids, int64_t num_slots_padded,
+                       int64_t K, int64_t N, int64_t E, int64_t a_cols, int64_t c_cols, int num_token_replicas,
+                       int mul_routed_weight, int tile_m, int tile_n, int tile_k);
+
+/* silu_and_mul_kernel(A, B, C, TILE_N)                     examples/moe.jl:110-128
+ * C(:, j) = silu(A(:, j)) * B(:, j) for n rows and `cols` columns (views with
+ * leading dimensions lda/ldb/ldc), f16 in and out, f32 arithmetic. */
+int ctb_moe_silu_and_mul(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, int64_t n, int64_t cols,
+                         int64_t lda, int64_t ldb, int64_t ldc, int tile_n);
+
+/* cutile_moe(hidden_states, w1, w2, topk_weights, topk_ids, tile_m, tile_n, tile_k)
+ *                                                          examples/moe.jl:218-257
+ * hidden (H, T); w1 (H, 2I, E) with gate rows then up rows; w2 (I, H, E);
+ * topk_weights (T, topk) f16; topk_ids (T, topk) 1-based (ids_bits 32 or 64);
+ * out (H, T) f16.  Device-side align, gate/up GEMM with fused SwiGLU, down GEMM
+ * scaled by the routing weight, top-k sum; scratch comes from the context. */
+int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, const void* w2,
+                const void* topk_weights, const void* topk_ids, int ids_bits, void* out, int64_t T, int64_t H,
+                int64_t I, int64_t E, int64_t topk, int tile_m, int tile_n, int tile_k);
+
 #ifdef __cplusplus
 }
 #endif
