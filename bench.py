@@ -92,6 +92,7 @@ class Workload:
     dtype = "f32"
     launches_per_step = 1
     kernel = ""          # name of the dominant kernel
+    uses_blas = False    # the CPU baseline's contractions run on all host cores through OpenBLAS
 
     def work(self):      # algorithmic bytes (hbm) or flops (tensor) per step
         raise NotImplementedError
@@ -236,13 +237,179 @@ class LayerNormBwd(LayerNormFwd):
                    ref.max_abs_over_max(st["FDB"].cpu().numpy(), db))
 
 
+class Gemm(Workload):
+    name = "gemm_tf32"
+    metric = "gemm_tf32_tflops"
+    unit = "TFLOP/s"
+    bound = "tensor"
+    peak_scale = 0.5  # TF32 MMAs run at half the bf16 rate the measured peak was taken at
+    dtype = "tf32"
+    kernel = "gemm_kernel<float>"
+    uses_blas = True
+    M = N = K = 4096
+
+    def describe(self):
+        return "C=A*B f32 (TF32 operands, f32 accumulate) 4096x4096x4096, U(-1,1) seed 2"
+
+    def work(self):
+        return 2 * self.M * self.N * self.K
+
+    def host_inputs(self):
+        from oracle import inputs
+        return inputs.gemm(self.M, self.N, self.K, seed=2)
+
+    def to_device(self, host, torch):
+        A, B = torch.from_numpy(host["A"]).cuda(), torch.from_numpy(host["B"]).cuda()
+        return dict(A=A, B=B, C=torch.empty(self.N, self.M, device="cuda"))
+
+    def step(self, ctb, st):
+        ctb.matmul.matmul_kernel(st["A"], st["B"], st["C"], 64, 64, 64)
+
+    def e2e_io(self, st):
+        return [("A",), ("B",)], [("C",)]
+
+    def cpu_step(self, host, ref, np):
+        A, B = host["A"], host["B"]
+        return (lambda: ref.gemm(A, B, dtype=np.float32)), 1.0, "full 4096^3, numpy float32 matmul (OpenBLAS)"
+
+    def check(self, host, st, ref, np):
+        rows = slice(0, 64)  # 64 columns of C (rows of the memory-order array)
+        return ref.rel_fro(st["C"][rows].cpu().numpy(), ref.gemm(host["A"], host["B"][rows]))
+
+
+class BatchedGemm(Gemm):
+    name = "bgemm_tf32"
+    metric = "batched_gemm_tf32_tflops"
+    M, K, N, batch = 1024, 2048, 512, 8
+
+    def describe(self):
+        return "batched C=A*B f32/TF32, batch 8 of A[1024x2048]*B[2048x512], U(-1,1) seed 2"
+
+    def work(self):
+        return 2 * self.M * self.N * self.K * self.batch
+
+    def host_inputs(self):
+        from oracle import inputs
+        return inputs.batched_gemm(self.M, self.K, self.N, self.batch, seed=2)
+
+    def to_device(self, host, torch):
+        A, B = torch.from_numpy(host["A"]).cuda(), torch.from_numpy(host["B"]).cuda()
+        return dict(A=A, B=B, C=torch.empty(self.batch, self.N, self.M, device="cuda"))
+
+    def step(self, ctb, st):
+        ctb.batchmatmul.batch_matmul_kernel(st["A"], st["B"], st["C"], 128, 128, 64)
+
+    def cpu_step(self, host, ref, np):
+        A, B = host["A"], host["B"]
+        return (lambda: ref.batched_gemm(A, B, dtype=np.float32)), 1.0, "full batch 8, numpy float32 matmul (OpenBLAS)"
+
+    def check(self, host, st, ref, np):
+        return ref.rel_fro(st["C"][3].cpu().numpy(), ref.gemm(host["A"][3], host["B"][3]))
+
+
+class Fmha(Workload):
+    name = "fmha_causal"
+    metric = "fmha_causal_tflops"
+    unit = "TFLOP/s"
+    bound = "tensor"
+    dtype = "f16"
+    kernel = "fmha_kernel"
+    uses_blas = True
+    B, H, S, D = 8, 16, 1024, 64
+
+    def describe(self):
+        return ("causal FMHA f16 batch 8 x heads 16 x seq 1024 x dim 64, N(0,1) seed 3, scale 1/8; flops = useful "
+                "causal work 4*B*H*D*S*(S+1)/2 (the reference's un-halved count 4*B*H*S*S*D is 2.0x this)")
+
+    def work(self):
+        return 4 * self.B * self.H * self.D * self.S * (self.S + 1) // 2
+
+    def host_inputs(self):
+        from oracle import inputs
+        return inputs.fmha(self.B, self.H, self.S, self.S, self.D, seed=3)
+
+    def to_device(self, host, torch):
+        st = {k: torch.from_numpy(host[k]).cuda() for k in ("Q", "K", "V")}
+        st["Out"] = torch.empty_like(st["Q"])
+        return st
+
+    def step(self, ctb, st):
+        # the launch inside cutile_fmha; the output buffer is preallocated for the device-resident timing
+        ctb.fmha.fmha_kernel(st["Q"], st["K"], st["V"], st["Out"], 0.125, 0, self.D, self.H, 128, 128, 1, True, True)
+
+    def e2e_io(self, st):
+        return [("Q",), ("K",), ("V",)], [("Out",)]
+
+    def cpu_step(self, host, ref, np):
+        Q, K, V = host["Q"], host["K"], host["V"]
+        return (lambda: ref.fmha(Q, K, V, causal=True, dtype=np.float32)), 1.0, \
+            "full batch 8 x 16 heads, numpy float32 (OpenBLAS matmuls)"
+
+    def check(self, host, st, ref, np):
+        sl = (slice(7, 8), slice(14, 16))
+        want = ref.fmha(host["Q"][sl], host["K"][sl], host["V"][sl], causal=True)
+        return ref.rel_fro(st["Out"][sl].cpu().numpy(), want)
+
+
+class Moe(Workload):
+    name = "moe_256"
+    metric = "moe_ffn_tflops"
+    unit = "TFLOP/s"
+    bound = "hbm"
+    dtype = "f16"
+    kernel = "moe_gemm_kernel"
+    uses_blas = True
+    launches_per_step = 5  # router, align, gate/up GEMM (+SwiGLU), down GEMM, top-k combine
+    T, Hd, E, I, topk = 256, 1024, 32, 2048, 2
+
+    def describe(self):
+        return (f"MoE FFN f16 {self.T} tokens x hidden 1024, 32 experts, top-2, SwiGLU inter 2048, seed 4; step = "
+                "router + align + gate/up GEMM + down GEMM + combine; flops = 2*T*topk*H*I*3")
+
+    def work(self):
+        return 2 * self.T * self.topk * self.Hd * self.I * 3
+
+    def roof_work(self):  # HBM: the expert weights have to stream once
+        return self.E * (self.Hd * 2 * self.I + self.I * self.Hd) * 2
+
+    def host_inputs(self):
+        from oracle import inputs
+        return inputs.moe(self.T, self.Hd, self.E, self.I, self.topk, seed=4)
+
+    def to_device(self, host, torch):
+        return {k: torch.from_numpy(host[k]).cuda() for k in ("X", "Wr", "w1", "w2")}
+
+    def step(self, ctb, st):
+        w, ids = ctb.moe.moe_router(st["X"], st["Wr"], self.topk)
+        st["out"] = ctb.moe.cutile_moe(st["X"], st["w1"], st["w2"], w, ids, 128, 128, 64)
+
+    def e2e_io(self, st):
+        return [("X",)], [("out",)]  # the expert weights are model state and stay resident
+
+    def cpu_step(self, host, ref, np):
+        def f():
+            ids, gates, _ = ref.moe_router(host["X"], host["Wr"], self.topk)
+            return ref.moe_ffn(host["X"], host["w1"], host["w2"], gates, ids, dtype=np.float32)
+        return f, 1.0, f"full {self.T} tokens, numpy float32 (OpenBLAS matmuls per expert)"
+
+    def check(self, host, st, ref, np):
+        ids, gates, _ = ref.moe_router(host["X"], host["Wr"], self.topk)
+        sample = np.arange(0, self.T, max(1, self.T // 64))
+        want = ref.moe_ffn(host["X"][sample], host["w1"], host["w2"], gates[:, sample], ids[:, sample])
+        return ref.rel_fro(st["out"].cpu().numpy()[sample], want)
+
+
+class Moe4096(Moe):
+    name = "moe_4096"
+    bound = "tensor"
+    T = 4096
+
+    def roof_work(self):
+        return self.work()
+
+
 def registry():
-    w = [Softmax(0), Softmax(1), LayerNormFwd(), LayerNormBwd()]
-    try:
-        import bench_dense  # tensor-core workloads live beside this file once built
-        w = bench_dense.workloads(Workload) + w
-    except ImportError:
-        pass
+    w = [Fmha(), Moe(), Moe4096(), Gemm(), BatchedGemm(), LayerNormFwd(), LayerNormBwd(), Softmax(0), Softmax(1)]
     return {x.name: x for x in w}
 
 
@@ -292,6 +459,7 @@ def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu
     res["parity_err"] = w.check(host, sets[(warmup + steps - 1) % nsets], ref, np)
     if do_e2e:
         ins, outs = w.e2e_io(base)
+        w.step(ctb, base)  # outputs that the step itself allocates exist from here on
         pin_in = {k[0]: torch.from_numpy(host[k[0]] if k[0] in host else base[k[0]].cpu().numpy()).pin_memory() for k in ins}
         pin_out = {k[0]: torch.empty(base[k[0]].shape, dtype=base[k[0]].dtype).pin_memory() for k in outs}
 
@@ -322,7 +490,8 @@ def cpu_time(w, host, repeats=3):
         fn()
         best = min(best, time.perf_counter() - t)
     scale = 1e9 if w.unit == "GB/s" else 1e12
-    threads = int(os.environ.get("OPENBLAS_NUM_THREADS", os.cpu_count() or 1)) if w.bound == "tensor" else 1
+    # numpy's element-wise code is single-threaded; only the OpenBLAS matmuls use every core
+    threads = int(os.environ.get("OPENBLAS_NUM_THREADS", os.cpu_count() or 1)) if w.uses_blas else 1
     return dict(value=w.work() * frac / best / scale, unit=w.unit, cores=threads, kind="port",
                 sample=sample + f"; best of {repeats}; {best * 1e3:.1f} ms", host_cpus=os.cpu_count())
 
@@ -387,8 +556,9 @@ def main():
     sampler.stop()
 
     def roof(r, w):
-        peak = pk["hbm"] if w.bound == "hbm" else pk["tensor"]
-        ach = r["work_per_step"] / (r["ms_per_step"] * 1e-3) / (1e9 if w.bound == "hbm" else 1e12)
+        peak = pk["hbm"] if w.bound == "hbm" else pk["tensor"] * getattr(w, "peak_scale", 1.0)
+        rw = w.roof_work() if hasattr(w, "roof_work") else r["work_per_step"]
+        ach = rw / (r["ms_per_step"] * 1e-3) / (1e9 if w.bound == "hbm" else 1e12)
         return dict(bound=w.bound, achieved=ach, peak=peak, unit="GB/s" if w.bound == "hbm" else "TFLOP/s",
                     frac=ach / peak, traffic=getattr(w, "ncu_traffic", None), kernel=w.kernel,
                     peak_source=pk["source"])
