@@ -499,8 +499,8 @@ def cpu_time(w, host, repeats=3):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline", default=None)
     ap.add_argument("--only", default=None, help="comma-separated workload names (default: all at N=1)")
@@ -548,7 +548,7 @@ def main():
     if world == 1:
         names = [n for n in reg if n != headline]
         if a.only is not None:
-            names = [n for n in a.only.split(",") if n and n != headline]
+            names = [n for n in a.only.split(",") if n in reg and n != headline]  # "--only none": headline alone
         for n in names:
             r = run_workload(reg[n], torch, ctb, None, a.steps, a.warmup, rank, 1, True, not a.no_cpu)
             r["clocks"] = sampler.summary(r["t0"], r["t1"])
