@@ -414,19 +414,37 @@ def registry():
 
 
 # --------------------------------------------------------------------------- timing
-def device_time(torch, dist, fn_steps, steps, warmup):
-    """warmup untimed steps, then `steps` steps between two events; max over ranks."""
+def device_time(torch, dist, fn_steps, steps, warmup, graph=True):
+    """`warmup` untimed steps, then exactly `steps` steps between two CUDA events on the launching stream; max over
+    ranks.  With graph=True the `steps` launches are captured once into a CUDA graph and the timed region replays
+    it, so the figure is device time and not the host's Python launch rate (the reference's protocol brackets single
+    launches with events for the same reason, examples/benchmarks.jl:104,159-171)."""
     for i in range(warmup):
         fn_steps(i)
     torch.cuda.synchronize()
+    g = None
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for i in range(steps):
+                    fn_steps(warmup + i)
+        torch.cuda.current_stream().wait_stream(side)
+        g.replay()  # one untimed replay: the graph is uploaded before the timed region
+        torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.time()
     e0.record()
-    for i in range(steps):
-        fn_steps(warmup + i)
+    if g is not None:
+        g.replay()
+    else:
+        for i in range(steps):
+            fn_steps(warmup + i)
     e1.record()
     torch.cuda.synchronize()
     t1 = time.time()
@@ -455,7 +473,8 @@ def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu
     value = w.work() * world / (per * 1e-3) / scale
     res = dict(name=w.name, metric=w.metric, unit=w.unit, value=value, ms_per_step=per, work_per_step=w.work(),
                workload=w.describe(), l2="rotating %d input/output sets (%.0f MB total, L2 is 126 MB)" %
-               (nsets, nsets * nbytes / 1e6), t0=t0, t1=t1, launches=w.launches_per_step * steps)
+               (nsets, nsets * nbytes / 1e6), t0=t0, t1=t1, launches=w.launches_per_step * steps,
+               timing="K steps captured in one CUDA graph, replayed between two events")
     res["parity_err"] = w.check(host, sets[(warmup + steps - 1) % nsets], ref, np)
     if do_e2e:
         ins, outs = w.e2e_io(base)
@@ -469,7 +488,7 @@ def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu
             w.step(ctb, base)
             for k, h in pin_out.items():
                 h.copy_(base[k], non_blocking=True)
-        ems, _, _ = device_time(torch, dist, e2e_step, max(3, steps // 4), 3)
+        ems, _, _ = device_time(torch, dist, e2e_step, max(3, steps // 4), 3, graph=False)
         eper = ems / max(3, steps // 4)
         res["e2e"] = dict(value=w.work() * world / (eper * 1e-3) / scale, unit=w.unit, ms_per_step=eper,
                           h2d_bytes_per_step=sum(h.numel() * h.element_size() for h in pin_in.values()),
@@ -567,7 +586,8 @@ def main():
         line = dict(metric=hw.metric, value=head["value"], unit=hw.unit, n_gpus=world, steps=a.steps, warmup=a.warmup,
                     ms_per_step=head["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None,
                     dtype=hw.dtype, data="synthetic",
-                    config={"workload": hw.describe(), "l2": head["l2"], "per_gpu": "same workload on every rank"},
+                    config={"workload": hw.describe(), "l2": head["l2"], "per_gpu": "same workload on every rank",
+                            "timing": head["timing"]},
                     clocks=clocks, e2e=head.get("e2e"), gpu_launches=head["launches"], roofline=roof(head, hw),
                     cpu_baseline=head.get("cpu_baseline"), parity_err=head["parity_err"])
         if others:

@@ -14,8 +14,11 @@
 //             PV = P*V (128x64x16, P read from TMEM columns 128..191 as the A
 //             operand, V MN-major in shared memory, result in columns 192..255);
 //   warps 2-5 softmax: thread = query row (TMEM lane).  Row max, exp2, row sum,
-//             P written back to TMEM as packed f16; O is kept in registers and
-//             updated as O = O*alpha + PV after each tile.
+//             P written back to TMEM as packed f16.  O accumulates in TMEM across
+//             tiles; it is rescaled (read, multiplied, written back) only when a
+//             row's maximum has grown by more than 2^8 since the exponent
+//             reference was last moved, which is exact (P and the row sum use the
+//             same reference) and happens at most a few times per row.
 // Like the reference (:69-76) the loop stops at the last tile that a causal
 // query tile can see, and only tiles from `mask_start` on pay for masking.
 // Heavier (later) query tiles are scheduled first.
@@ -140,7 +143,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         const uint32_t aV = smem_u32(sV + vs * kTileBytes);
 #pragma unroll
         for (int k = 0; k < kTN / 16; ++k)
-          mma_f16_ts(tmem + kColO, tmem + kColP + k * 8, make_sdesc_sw128(aV + k * 2048, 0, 1024), idesc_pv, k != 0);
+          mma_f16_ts(tmem + kColO, tmem + kColP + k * 8, make_sdesc_sw128(aV + k * 2048, 0, 1024), idesc_pv, (j | k) != 0);
         tc_commit(&v_empty[vs]);
         tc_commit(&o_full);
         if (j + 1 < Tc) ok = issue_qk(j + 1);
@@ -150,11 +153,10 @@ __global__ void __launch_bounds__(kThreads, 2)
     const int sub = warp & 3;
     const int row = sub * 32 + lane;          // query row inside the tile = TMEM lane
     const int qpos = q0 + row + p.input_pos;  // position used by the causal rule
-    const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
-    float m = -INFINITY, l = 0.f;
-    float o[kD];
-#pragma unroll
-    for (int i = 0; i < kD; ++i) o[i] = 0.f;
+    const uint32_t trow = tmem + ((uint32_t)(sub * 32) << 16);
+    const int vis_last = p.causal ? min(qpos, p.seq_kv - 1) : p.seq_kv - 1;  // last visible key of this row
+    float m_ref = -INFINITY;  // exponent reference (scaled, log2 domain)
+    float l = 0.f;            // row sum relative to m_ref
     bool ok = true;
     for (int j = 0; j < Tc; ++j) {
       ok = mbar_wait(&s_full, j & 1, status, DEV_TIMEOUT_MMA, abort);
@@ -162,85 +164,134 @@ __global__ void __launch_bounds__(kThreads, 2)
       if (!ok) break;
       tc_fence_after();
       const bool masked = j >= mask_start;
-      const int key0 = j * kTN;
-      // pass 1: row maximum of the raw scores
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kTN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_addr + kColS + c * 32, r);
-        tc_wait_ld();
+      const int lim = vis_last - j * kTN;  // column i of this tile is visible iff i <= lim
+      uint32_t ra[32], rb[32];
+      // ---- pass 1: row maximum of the raw scores (loads run one chunk ahead)
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      auto max_chunk = [&](const uint32_t (&r)[32], int c) {
         if (masked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c * 32 + i;
-            const bool vis = key < p.seq_kv && (!p.causal || key <= qpos);
-            mx = fmaxf(mx, vis ? __uint_as_float(r[i]) : -INFINITY);
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, c * 32 + i + 0 <= lim ? __uint_as_float(r[i + 0]) : -INFINITY);
+            mx1 = fmaxf(mx1, c * 32 + i + 1 <= lim ? __uint_as_float(r[i + 1]) : -INFINITY);
+            mx2 = fmaxf(mx2, c * 32 + i + 2 <= lim ? __uint_as_float(r[i + 2]) : -INFINITY);
+            mx3 = fmaxf(mx3, c * 32 + i + 3 <= lim ? __uint_as_float(r[i + 3]) : -INFINITY);
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; i += 4) {
+            mx0 = fmaxf(mx0, __uint_as_float(r[i + 0]));
+            mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+          }
+        }
+      };
+      tmem_ld32(trow + kColS + 0, ra);
+      tc_wait_ld();
+      tmem_ld32(trow + kColS + 32, rb);
+      max_chunk(ra, 0);
+      tc_wait_ld();
+      tmem_ld32(trow + kColS + 64, ra);
+      max_chunk(rb, 1);
+      tc_wait_ld();
+      tmem_ld32(trow + kColS + 96, rb);
+      max_chunk(ra, 2);
+      tc_wait_ld();
+      tmem_ld32(trow + kColS + 0, ra);  // first chunk of pass 2, in flight while the maximum is finished
+      max_chunk(rb, 3);
+      const float m_true = fmaxf(m_ref, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
+      // ---- move the exponent reference (and rescale O, l) only when the maximum grew by more than 2^8
+      const bool grow = m_true - m_ref > 8.0f || m_ref == -INFINITY;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = m_true == -INFINITY ? 0.f : m_true;  // fully masked so far: keep everything zero
+        const float alpha = ex2_approx_ftz(m_ref - m_new);       // 0 on the first tile
+        l *= alpha;
+        m_ref = m_new;
+        if (j > 0) {  // O holds the sum of the previous tiles; PV(j-1) must have landed
+          ok = mbar_wait(&o_full, (j - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          tc_wait_ld();  // chunk 0 of pass 2 is already in ra; rb is free
+#pragma unroll
+          for (int c = 0; c < kD / 32; ++c) {
+            tmem_ld32(trow + kColO + c * 32, rb);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) rb[i] = __float_as_uint(__uint_as_float(rb[i]) * alpha);
+            tmem_st16(trow + kColO + c * 32, reinterpret_cast<const uint32_t(&)[16]>(rb[0]));
+            tmem_st16(trow + kColO + c * 32 + 16, reinterpret_cast<const uint32_t(&)[16]>(rb[16]));
+          }
         }
       }
-      float m_new = fmaxf(m, mx * p.scale_log2);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a fully masked row stays all-zero
-      const float alpha = ex2_approx_ftz(m - m_use);
-      // pass 2: p = exp2(s*scale - m), row sum, P -> TMEM as packed f16
-      float lsum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kTN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_addr + kColS + c * 32, r);
-        tc_wait_ld();
+      // ---- pass 2: p = exp2(s*scale - m_ref), row sum, P -> TMEM as packed f16
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      const float nm = -m_ref;
+      auto exp_chunk = [&](const uint32_t (&r)[32], int c) {
         uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx_ftz(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_use));
-          float p1 = ex2_approx_ftz(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_use));
+        for (int i = 0; i < 32; i += 4) {
+          float p0 = ex2_approx_ftz(fmaf(__uint_as_float(r[i + 0]), p.scale_log2, nm));
+          float p1 = ex2_approx_ftz(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, nm));
+          float p2 = ex2_approx_ftz(fmaf(__uint_as_float(r[i + 2]), p.scale_log2, nm));
+          float p3 = ex2_approx_ftz(fmaf(__uint_as_float(r[i + 3]), p.scale_log2, nm));
           if (masked) {
-            const int key = key0 + c * 32 + i;
-            if (!(key < p.seq_kv && (!p.causal || key <= qpos))) p0 = 0.f;
-            if (!(key + 1 < p.seq_kv && (!p.causal || key + 1 <= qpos))) p1 = 0.f;
+            if (c * 32 + i + 0 > lim) p0 = 0.f;
+            if (c * 32 + i + 1 > lim) p1 = 0.f;
+            if (c * 32 + i + 2 > lim) p2 = 0.f;
+            if (c * 32 + i + 3 > lim) p3 = 0.f;
           }
-          lsum += p0 + p1;
-          pk[i >> 1] = pack_f16x2(p0, p1);
+          s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+          pk[(i >> 1) + 0] = pack_f16x2(p0, p1);
+          pk[(i >> 1) + 1] = pack_f16x2(p2, p3);
         }
-        tmem_st16(tmem + lane_addr + kColP + c * 16, pk);
-      }
+        tmem_st16(trow + kColP + c * 16, pk);
+      };
+      tc_wait_ld();
+      tmem_ld32(trow + kColS + 32, rb);
+      exp_chunk(ra, 0);
+      tc_wait_ld();
+      tmem_ld32(trow + kColS + 64, ra);
+      exp_chunk(rb, 1);
+      tc_wait_ld();
+      tmem_ld32(trow + kColS + 96, rb);
+      exp_chunk(ra, 2);
+      tc_wait_ld();
+      exp_chunk(rb, 3);
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full);
-      l = l * alpha + lsum;
-      m = m_new;
-#pragma unroll
-      for (int i = 0; i < kD; ++i) o[i] *= alpha;
-      ok = mbar_wait(&o_full, j & 1, status, DEV_TIMEOUT_MMA, abort);
+      l += (s0 + s1) + (s2 + s3);
+    }
+    if (ok) {
+      ok = mbar_wait(&o_full, (Tc - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+    }
+    if (ok) {
       tc_fence_after();
+      const float inv = rcp_approx_ftz(l);
+      const bool store = q0 + row < p.seq_q;
+      uint4* dst = reinterpret_cast<uint4*>(Out + ((long long)bh * p.seq_q + q0 + row) * kD);
 #pragma unroll
       for (int c = 0; c < kD / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tmem + lane_addr + kColO + c * 32, r);
+        tmem_ld32(trow + kColO + c * 32, r);
         tc_wait_ld();
+        if (store) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack_f16x2(__uint_as_float(r[i * 8 + 0]) * inv, __uint_as_float(r[i * 8 + 1]) * inv);
+            v.y = pack_f16x2(__uint_as_float(r[i * 8 + 2]) * inv, __uint_as_float(r[i * 8 + 3]) * inv);
+            v.z = pack_f16x2(__uint_as_float(r[i * 8 + 4]) * inv, __uint_as_float(r[i * 8 + 5]) * inv);
+            v.w = pack_f16x2(__uint_as_float(r[i * 8 + 6]) * inv, __uint_as_float(r[i * 8 + 7]) * inv);
+            dst[c * 4 + i] = v;
+          }
+        }
       }
       tc_fence_before();
-    }
-    if (ok && q0 + row < p.seq_q) {
-      const float inv = rcp_approx_ftz(l);
-      uint4* dst = reinterpret_cast<uint4*>(Out + ((long long)bh * p.seq_q + q0 + row) * kD);
-#pragma unroll
-      for (int i = 0; i < kD / 8; ++i) {
-        uint4 v;
-        v.x = pack_f16x2(o[i * 8 + 0] * inv, o[i * 8 + 1] * inv);
-        v.y = pack_f16x2(o[i * 8 + 2] * inv, o[i * 8 + 3] * inv);
-        v.z = pack_f16x2(o[i * 8 + 4] * inv, o[i * 8 + 5] * inv);
-        v.w = pack_f16x2(o[i * 8 + 6] * inv, o[i * 8 + 7] * inv);
-        dst[i] = v;
-      }
     }
   }
   tc_fence_before();

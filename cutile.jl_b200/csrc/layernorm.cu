@@ -365,17 +365,40 @@ __global__ void __launch_bounds__(kBwdThreads)
   }
 }
 
-__global__ void ln_bwd_reduce_kernel(const float* __restrict__ DW, const float* __restrict__ DB,
-                                     float* __restrict__ FDW, float* __restrict__ FDB, int N, int G) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= N) return;
+// Column sums of the (N, G) partials.  Block = 32 columns x 8 group slices; each
+// slice adds its groups in ascending order, then the 8 slice sums are added in
+// ascending slice order: a fixed summation tree, so the result is deterministic.
+constexpr int kRedCols = 32, kRedSlices = 8;
+__global__ void __launch_bounds__(kRedCols * kRedSlices)
+    ln_bwd_reduce_kernel(const float* __restrict__ DW, const float* __restrict__ DB, float* __restrict__ FDW,
+                         float* __restrict__ FDB, int N, int G) {
+  __shared__ float sw[kRedSlices][kRedCols], sb[kRedSlices][kRedCols];
+  const int cx = threadIdx.x & (kRedCols - 1), sl = threadIdx.x / kRedCols;
+  const int c = blockIdx.x * kRedCols + cx;
+  const int per = (G + kRedSlices - 1) / kRedSlices;
   float a = 0.f, b = 0.f;
-  for (int g = 0; g < G; ++g) {  // ascending group: fixed summation order
-    a += DW[(long long)g * N + c];
-    b += DB[(long long)g * N + c];
+  if (c < N) {
+    const int g1 = min(G, (sl + 1) * per);
+#pragma unroll 4
+    for (int g = sl * per; g < g1; ++g) {
+      a += DW[(long long)g * N + c];
+      b += DB[(long long)g * N + c];
+    }
   }
-  FDW[c] = a;
-  FDB[c] = b;
+  sw[sl][cx] = a;
+  sb[sl][cx] = b;
+  __syncthreads();
+  if (sl == 0 && c < N) {
+    a = 0.f;
+    b = 0.f;
+#pragma unroll
+    for (int k = 0; k < kRedSlices; ++k) {
+      a += sw[k][cx];
+      b += sb[k][cx];
+    }
+    FDW[c] = a;
+    FDB[c] = b;
+  }
 }
 
 template <int NV>
@@ -490,9 +513,8 @@ int ctb_layernorm_bwd_dwdb(ctb_ctx* ctx, void* stream, const float* DW, const fl
   if (!is_pow2(tile_m) || !is_pow2(tile_n))
     return fail(CTB_UNSUPPORTED_TILE, "ctb_layernorm_bwd_dwdb: TILE_M/TILE_N must be powers of two");
   CTB_CHECK_DEV(DW); CTB_CHECK_DEV(DB); CTB_CHECK_DEV(FINAL_DW); CTB_CHECK_DEV(FINAL_DB);
-  const int threads = 128;
-  ln_bwd_reduce_kernel<<<(int)((N + threads - 1) / threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      DW, DB, FINAL_DW, FINAL_DB, (int)N, group_size_m);
+  ln_bwd_reduce_kernel<<<(int)((N + kRedCols - 1) / kRedCols), kRedCols * kRedSlices, 0,
+                         static_cast<cudaStream_t>(stream)>>>(DW, DB, FINAL_DW, FINAL_DB, (int)N, group_size_m);
   CTB_CHECK_LAUNCH("ctb_layernorm_bwd_dwdb launch");
   return CTB_OK;
 }

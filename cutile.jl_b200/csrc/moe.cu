@@ -10,8 +10,9 @@
 //                       a multiple of tile_m with the sentinel total+1.
 //   moe_gemm_kernel     fused_moe_kernel (:45-105): per (slot block, 128 weight
 //                       rows) acc(N,M) += W_e(N,K) * A(K,M); weights stream by TMA,
-//                       token rows are gathered by slot id into 128B-swizzled
-//                       shared memory, tcgen05.mma accumulates in TMEM.  The
+//                       token rows are gathered by slot id with cp.async into
+//                       128B-swizzled shared memory (completion arrives on the
+//                       stage's mbarrier), tcgen05.mma accumulates in TMEM.  The
 //                       instruction's N extent is the block's valid slot count
 //                       rounded up to 16, so sparsely filled blocks (16 of 128
 //                       slots at top-2 over 32 experts) cost little tensor time.
@@ -31,34 +32,77 @@ using namespace ctb_internal;
 namespace {
 
 // ------------------------------------------------------------------ router
+// One warp per token, lane = expert (experts lane, lane+32, ...).  W_r is staged
+// chunk by chunk into shared memory (rows padded by 16 bytes so that the 32
+// lanes read 32 different rows without bank conflicts); the next chunk is
+// fetched into registers while the current one is consumed.
 constexpr int kRouterWarps = 4;
+constexpr int kRouterThreads = kRouterWarps * 32;
 constexpr int kMaxEPL = 8;  // experts per lane -> E <= 256
 
-__global__ void __launch_bounds__(kRouterWarps * 32)
+template <int KC>  // K elements per staged chunk
+__global__ void __launch_bounds__(kRouterThreads)
     moe_router_kernel(const __half* __restrict__ X, const __half* __restrict__ Wr, int* __restrict__ ids,
                       __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouterWarps + warp;
-  if (t >= T) return;
+  extern __shared__ __align__(16) unsigned char rsm[];
+  constexpr int ROWB = KC * 2 + 16;  // bytes per staged expert row
+  constexpr int VPR = KC / 8;        // 16-byte vectors per row
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t = min(blockIdx.x * kRouterWarps + warp, T - 1);  // surplus warps redo the last token, write nothing
+  const bool live = blockIdx.x * kRouterWarps + warp < T;
   const __half* x = X + (long long)t * H;
+  const int epl = (E + 31) / 32;
+  const int nvec = E * VPR;
+  constexpr int kMaxPre = (256 * (128 / 8)) / kRouterThreads / 2;  // vectors a thread may have to prefetch (<= 16)
+  uint4 pre[kMaxPre];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < kMaxPre; ++i) {
+      const int idx = tid + i * kRouterThreads;
+      if (idx < nvec) {
+        const int e = idx / VPR, v = idx - e * VPR;
+        pre[i] = (k0 + v * 8 < H) ? *reinterpret_cast<const uint4*>(Wr + (long long)e * H + k0 + v * 8)
+                                  : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int i = 0; i < kMaxPre; ++i) {
+      const int idx = tid + i * kRouterThreads;
+      if (idx < nvec) {
+        const int e = idx / VPR, v = idx - e * VPR;
+        *reinterpret_cast<uint4*>(rsm + e * ROWB + v * 16) = pre[i];
+      }
+    }
+  };
   float acc[kMaxEPL];
 #pragma unroll
   for (int i = 0; i < kMaxEPL; ++i) acc[i] = 0.f;
-  const int epl = (E + 31) / 32;
-  for (int k0 = 0; k0 < H; k0 += 8) {  // H % 8 == 0
-    const uint4 xv = *reinterpret_cast<const uint4*>(x + k0);
-    const __half* xh = reinterpret_cast<const __half*>(&xv);
+  fetch(0);
+  for (int k0 = 0; k0 < H; k0 += KC) {
+    __syncthreads();  // everyone is done with the previous chunk
+    stash();
+    __syncthreads();
+    if (k0 + KC < H) fetch(k0 + KC);
+    const int klim = min(KC, H - k0);
+#pragma unroll 4
+    for (int kk = 0; kk < klim; kk += 8) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(x + k0 + kk);
+      const __half* xh = reinterpret_cast<const __half*>(&xv);
 #pragma unroll
-    for (int i = 0; i < kMaxEPL; ++i) {
-      const int e = lane + 32 * i;
-      if (i < epl && e < E) {
-        const uint4 wv = *reinterpret_cast<const uint4*>(Wr + (long long)e * H + k0);
-        const __half* wh = reinterpret_cast<const __half*>(&wv);
+      for (int i = 0; i < kMaxEPL; ++i) {
+        const int e = lane + 32 * i;
+        if (i < epl && e < E) {
+          const uint4 wv = *reinterpret_cast<const uint4*>(rsm + e * ROWB + kk * 2);
+          const __half* wh = reinterpret_cast<const __half*>(&wv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i] = fmaf(__half2float(xh[j]), __half2float(wh[j]), acc[i]);  // ascending k
+          for (int j = 0; j < 8; ++j) acc[i] = fmaf(__half2float(xh[j]), __half2float(wh[j]), acc[i]);  // ascending k
+        }
       }
     }
   }
+  if (!live) return;
   if (logits_out) {
 #pragma unroll
     for (int i = 0; i < kMaxEPL; ++i)
@@ -241,7 +285,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     abort_s = 0;
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&w_full[s], 1);
-      mbar_init(&b_full[s], 4);
+      mbar_init(&b_full[s], 128);  // one arrival per gather thread, triggered by its cp.async completion
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -309,6 +353,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             failed = 1;
             break;
           }
+          fence_proxy_async_smem();  // the gathered rows were written through the generic proxy
           tc_fence_after();
           const uint32_t sw = smem_u32(smem + (size_t)stage * p.stage_bytes);
           const uint32_t sb = sw + wbytes;
@@ -356,14 +401,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             const int k = kb * kBK + c * 8;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (src && k < p.K) v = *reinterpret_cast<const uint4*>(src + k);
-            *reinterpret_cast<uint4*>(dst + ((c ^ (g & 7)) << 4)) = v;
+            const bool valid = src && k < p.K;
+            cp_async16(dst + ((c ^ (g & 7)) << 4), valid ? (const void*)(src + k) : (const void*)p.A, valid ? 16u : 0u);
           }
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&b_full[stage]);
+        cp_async_arrive_noinc(&b_full[stage]);  // fires when this thread's copies have landed
         if (++stage == p.stages) { stage = 0; phase ^= 1; }
       }
     }
@@ -535,9 +577,14 @@ int ctb_moe_router(ctb_ctx* ctx, void* stream, const void* hidden, const void* W
   if (T == 0) return CTB_OK;
   CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(W_r); CTB_CHECK_DEV(topk_ids); CTB_CHECK_DEV(topk_weights);
   if ((uintptr_t)hidden % 16 || (uintptr_t)W_r % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_router: 16-byte alignment");
-  moe_router_kernel<<<(int)((T + kRouterWarps - 1) / kRouterWarps), kRouterWarps * 32, 0,
-                      static_cast<cudaStream_t>(stream)>>>((const __half*)hidden, (const __half*)W_r, topk_ids,
-                                                           (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk);
+  const int grid = (int)((T + kRouterWarps - 1) / kRouterWarps);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (E <= 128)  // 128 K-elements per staged chunk: at most 128 * 272 B of shared memory
+    moe_router_kernel<128><<<grid, kRouterThreads, (size_t)E * (128 * 2 + 16), st>>>(
+        (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk);
+  else
+    moe_router_kernel<64><<<grid, kRouterThreads, (size_t)E * (64 * 2 + 16), st>>>(
+        (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk);
   CTB_CHECK_LAUNCH("ctb_moe_router launch");
   return CTB_OK;
 }

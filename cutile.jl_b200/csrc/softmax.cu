@@ -10,8 +10,11 @@
 //   one pass of 128-bit loads keeps a running (max, sum) per thread; the row
 //   is kept in registers when it fits (one HBM read), else re-read once.
 //
-// Both compute in f32 with exp() and an exact divide, like the reference
-// (examples/softmax.jl:32-35,92).  HBM-bound: 2*M*N*sizeof(T) bytes per call.
+// Both compute in f32 (examples/softmax.jl:32-35,92).  exp(x - max) is evaluated
+// as ex2.approx((x - max)*log2(e)) (relative error about 2^-22 plus the rounding
+// of the product) and the division as a multiplication by the exactly
+// rounded reciprocal of the row sum, so that the kernel stays HBM-bound
+// (2*M*N*sizeof(T) bytes per call) instead of instruction-bound.
 #include <float.h>
 
 #include "ctx.h"
@@ -21,6 +24,11 @@ using namespace ctb;
 using namespace ctb_internal;
 
 namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+// exp(x - m).  The subtraction comes first so that x == m gives exactly 1 and huge
+// magnitudes cannot turn the rounding error of m*log2(e) into a wrong exponent.
+__device__ __forceinline__ float exp_sub(float x, float m) { return ex2_approx_ftz((x - m) * kLog2e); }
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
@@ -126,24 +134,24 @@ __global__ void __launch_bounds__(kThreads) softmax_staged_kernel(T* __restrict_
       }
     }
     mx = block_max(mx, red);
-    float sum = 0.f;
+    float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
       if (tid + v * kThreads < npack) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          x[v][k] = expf(x[v][k] - mx);
-          sum += x[v][k];
+          x[v][k] = exp_sub(x[v][k], mx);
+          s4[k] += x[v][k];
         }
       }
     }
-    sum = block_sum(sum, red);
+    const float inv = 1.0f / block_sum((s4[0] + s4[1]) + (s4[2] + s4[3]), red);
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
       const int p = tid + v * kThreads;
       if (p < npack) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) x[v][k] = x[v][k] / sum;
+        for (int k = 0; k < 4; ++k) x[v][k] *= inv;
         buf[p] = Pack<T>::pack(x[v]);
       }
     }
@@ -198,11 +206,11 @@ __global__ void __launch_bounds__(kThreads) softmax_online_kernel(T* __restrict_
 #pragma unroll
       for (int k = 1; k < VEC; ++k) cm = fmaxf(cm, f[k]);
       if (cm > m) {
-        l *= expf(m - cm);
+        l *= exp_sub(m, cm);
         m = cm;
       }
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) l += expf(f[k] - m);
+      for (int k = 0; k < VEC; ++k) l += exp_sub(f[k], m);
     };
 
 #pragma unroll
@@ -213,12 +221,12 @@ __global__ void __launch_bounds__(kThreads) softmax_online_kernel(T* __restrict_
       if (load(i, f)) update(f);
     }
     const float mg = block_max(m, red);
-    const float lg = block_sum(l * expf(m - mg), red);  // threads with no data: l = 0
+    const float inv = 1.0f / block_sum(l * exp_sub(m, mg), red);  // threads with no data: l = 0
 
     auto store = [&](int i, float* f) {
       const int p = tid + i * kThreads;
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) f[k] = expf(f[k] - mg) / lg;
+      for (int k = 0; k < VEC; ++k) f[k] = exp_sub(f[k], mg) * inv;
       if constexpr (VEC == 4) {
         reinterpret_cast<typename Pack<T>::type*>(dst)[p] = Pack<T>::pack(f);
       } else {
