@@ -101,53 +101,66 @@ __global__ void __launch_bounds__(kThreads, 2)
   volatile int* abort = &abort_s;
 
   if (warp == 0) {
-    if (lane == 0) {
+    // ---- TMA producer (whole warp in lock step, one elected lane issues)
+    if (elect_one()) {
       mbar_expect_tx(&q_full, kTileBytes);
       tma_load_3d(sQ, &tmQ, 0, q0, bh, &q_full);
-      const int kvz = b * p.kv_heads + kvh;
-      for (int j = 0; j < Tc; ++j) {
-        const int ks = j % kKStages, vs = j % kVStages;
-        if (!mbar_wait(&k_empty[ks], ((j / kKStages) & 1) ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+    }
+    __syncwarp();
+    const int kvz = b * p.kv_heads + kvh;
+    for (int j = 0; j < Tc; ++j) {
+      const int ks = j % kKStages, vs = j % kVStages;
+      if (!CTB_WARP_WAIT(&k_empty[ks], ((j / kKStages) & 1) ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+      if (elect_one()) {
         mbar_expect_tx(&k_full[ks], kTileBytes);
         tma_load_3d(sK + ks * kTileBytes, &tmK, 0, j * kTN, kvz, &k_full[ks]);
-        if (!mbar_wait(&v_empty[vs], ((j / kVStages) & 1) ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+      }
+      __syncwarp();
+      if (!CTB_WARP_WAIT(&v_empty[vs], ((j / kVStages) & 1) ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+      if (elect_one()) {
         mbar_expect_tx(&v_full[vs], kTileBytes);
         tma_load_3d(sV + vs * kTileBytes, &tmV, 0, j * kTN, kvz, &v_full[vs]);
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc(FMT_F16, kTM, kTN, 0, 0);
-      constexpr uint32_t idesc_pv = make_idesc(FMT_F16, kTM, kD, 0, /*V is MN-major*/ 1);
-      const uint32_t aQ = smem_u32(sQ);
-      auto issue_qk = [&](int j) -> bool {
-        const int ks = j % kKStages;
-        if (!mbar_wait(&k_full[ks], (j / kKStages) & 1, status, DEV_TIMEOUT_TMA, abort)) return false;
-        tc_fence_after();
-        const uint32_t aK = smem_u32(sK + ks * kTileBytes);
+    // ---- MMA issuer (whole warp in lock step, one elected lane issues)
+    constexpr uint32_t idesc_qk = make_idesc(FMT_F16, kTM, kTN, 0, 0);
+    constexpr uint32_t idesc_pv = make_idesc(FMT_F16, kTM, kD, 0, /*V is MN-major*/ 1);
+    const uint32_t aQ = smem_u32(sQ);
+    auto issue_qk = [&](int j) -> bool {
+      const int ks = j % kKStages;
+      if (!CTB_WARP_WAIT(&k_full[ks], (j / kKStages) & 1, status, DEV_TIMEOUT_TMA, abort)) return false;
+      tc_fence_after();
+      const uint32_t aK = smem_u32(sK + ks * kTileBytes);
+      if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k)
           mma_f16_ss(tmem + kColS, make_sdesc_sw128(aQ + k * 32, 0, 1024), make_sdesc_sw128(aK + k * 32, 0, 1024),
                      idesc_qk, k != 0);
         tc_commit(&k_empty[ks]);
         tc_commit(&s_full);
-        return true;
-      };
-      bool ok = mbar_wait(&q_full, 0, status, DEV_TIMEOUT_TMA, abort);
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; ok && j < Tc; ++j) {
-        const int vs = j % kVStages;
-        if (!mbar_wait(&p_full, j & 1, status, DEV_TIMEOUT_SLOT, abort)) break;
-        if (!mbar_wait(&v_full[vs], (j / kVStages) & 1, status, DEV_TIMEOUT_TMA, abort)) break;
-        tc_fence_after();
-        const uint32_t aV = smem_u32(sV + vs * kTileBytes);
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = CTB_WARP_WAIT(&q_full, 0, status, DEV_TIMEOUT_TMA, abort);
+    if (ok) ok = issue_qk(0);
+    for (int j = 0; ok && j < Tc; ++j) {
+      const int vs = j % kVStages;
+      if (!CTB_WARP_WAIT(&p_full, j & 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+      if (!CTB_WARP_WAIT(&v_full[vs], (j / kVStages) & 1, status, DEV_TIMEOUT_TMA, abort)) break;
+      tc_fence_after();
+      const uint32_t aV = smem_u32(sV + vs * kTileBytes);
+      if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < kTN / 16; ++k)
           mma_f16_ts(tmem + kColO, tmem + kColP + k * 8, make_sdesc_sw128(aV + k * 2048, 0, 1024), idesc_pv, (j | k) != 0);
         tc_commit(&v_empty[vs]);
         tc_commit(&o_full);
-        if (j + 1 < Tc) ok = issue_qk(j + 1);
       }
+      __syncwarp();
+      if (j + 1 < Tc) ok = issue_qk(j + 1);
     }
   } else {
     const int sub = warp & 3;

@@ -109,44 +109,52 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int nk = (p.K + G::BK - 1) / G::BK;
 
   if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
-        int b, tm, tn;
-        tile_coords(p, t, b, tm, tn);
-        for (int kb = 0; kb < nk; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) goto done;
-          unsigned char* sa = smem + (size_t)stage * G::STAGE_BYTES;
+    // ---- TMA producer: the whole warp walks the loop, one elected lane issues
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+      int b, tm, tn;
+      tile_coords(p, t, b, tm, tn);
+      bool ok = true;
+      for (int kb = 0; kb < nk; ++kb) {
+        ok = CTB_WARP_WAIT(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+        if (!ok) break;
+        unsigned char* sa = smem + (size_t)stage * G::STAGE_BYTES;
+        if (elect_one()) {
           mbar_expect_tx(&full[stage], G::STAGE_BYTES);
 #pragma unroll
           for (int j = 0; j < G::A_BOXES; ++j)
             tma_load_3d(sa + j * G::A_BOX_BYTES, &tmapA, tm * kTileM + j * G::CHUNK_M, kb * G::BK, b, &full[stage]);
           tma_load_3d(sa + G::A_BYTES, &tmapB, kb * G::BK, tn * kTileN, b, &full[stage]);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1;
-          }
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
         }
       }
+      if (!ok) break;
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(G::FMT, kTileM, kTileN, /*A MN-major*/ 1, /*B K-major*/ 0);
-      int stage = 0;
-      uint32_t phase = 0;
-      int it = 0;
-      for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++it) {
-        const int acc = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) goto done;
+    // ---- MMA issuer: the whole warp walks the loop, one elected lane issues
+    constexpr uint32_t idesc = make_idesc(G::FMT, kTileM, kTileN, /*A MN-major*/ 1, /*B K-major*/ 0);
+    int stage = 0;
+    uint32_t phase = 0;
+    int it = 0;
+    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!CTB_WARP_WAIT(&acc_empty[acc], acc_phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+      tc_fence_after();
+      const uint32_t d = tmem_base + acc * kAccCols;
+      bool ok = true;
+      for (int kb = 0; kb < nk; ++kb) {
+        ok = CTB_WARP_WAIT(&full[stage], phase, status, DEV_TIMEOUT_TMA, abort);
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t d = tmem_base + acc * kAccCols;
-        for (int kb = 0; kb < nk; ++kb) {
-          if (!mbar_wait(&full[stage], phase, status, DEV_TIMEOUT_TMA, abort)) goto done;
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + (size_t)stage * G::STAGE_BYTES);
-          const uint32_t sb = sa + G::A_BYTES;
+        const uint32_t sa = smem_u32(smem + (size_t)stage * G::STAGE_BYTES);
+        const uint32_t sb = sa + G::A_BYTES;
+        if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < G::BK / G::UK; ++k) {
             const uint64_t ad = make_sdesc(sa + k * G::UK * 128, G::A_BOX_BYTES, G::A_SBO, G::A_LAYOUT);
@@ -157,13 +165,16 @@ __global__ void __launch_bounds__(kThreads, 1)
               mma_f16_ss(d, ad, bd, idesc, (kb | k) != 0);
           }
           tc_commit(&empty[stage]);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1;
-          }
         }
-        tc_commit(&acc_full[acc]);
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
       }
+      if (!ok) break;
+      if (elect_one()) tc_commit(&acc_full[acc]);
+      __syncwarp();
     }
   } else {
     const int sub = warp & 3;  // TMEM lanes [32*sub, 32*sub+32) belong to this warp
@@ -203,7 +214,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
     }
   }
-done:
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {

@@ -32,91 +32,89 @@ using namespace ctb_internal;
 namespace {
 
 // ------------------------------------------------------------------ router
-// One warp per token, lane = expert (experts lane, lane+32, ...).  W_r is staged
-// chunk by chunk into shared memory (rows padded by 16 bytes so that the 32
-// lanes read 32 different rows without bank conflicts); the next chunk is
-// fetched into registers while the current one is consumed.
-constexpr int kRouterWarps = 4;
+// One warp per token, lane = expert (experts lane, lane+32, ...).  The token rows
+// and W_r are staged in shared memory as f32 (all of W_r at once when it fits,
+// else in K-chunks of KC); expert rows are padded by 16 bytes so that the 32
+// lanes read 32 different rows without bank conflicts.  Each (token, expert)
+// logit is one chain of fused multiply-adds in ascending k, which is what makes
+// the result reproducible bit for bit.
+constexpr int kRouterWarps = 8;
 constexpr int kRouterThreads = kRouterWarps * 32;
 constexpr int kMaxEPL = 8;  // experts per lane -> E <= 256
 
-template <int KC>  // K elements per staged chunk
+__device__ __forceinline__ float4 cvt4(uint2 u) {
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <int EPL>
 __global__ void __launch_bounds__(kRouterThreads)
     moe_router_kernel(const __half* __restrict__ X, const __half* __restrict__ Wr, int* __restrict__ ids,
-                      __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk) {
-  extern __shared__ __align__(16) unsigned char rsm[];
-  constexpr int ROWB = KC * 2 + 16;  // bytes per staged expert row
-  constexpr int VPR = KC / 8;        // 16-byte vectors per row
+                      __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk,
+                      int KC) {
+  extern __shared__ __align__(16) float rsm[];
+  const int ROW = KC + 4;                            // floats per staged expert row
+  float* sw = rsm;                                   // [E][ROW]
+  float* sx = rsm + (size_t)E * ROW;                 // [kRouterWarps][H]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int t = min(blockIdx.x * kRouterWarps + warp, T - 1);  // surplus warps redo the last token, write nothing
-  const bool live = blockIdx.x * kRouterWarps + warp < T;
-  const __half* x = X + (long long)t * H;
-  const int epl = (E + 31) / 32;
-  const int nvec = E * VPR;
-  constexpr int kMaxPre = (256 * (128 / 8)) / kRouterThreads / 2;  // vectors a thread may have to prefetch (<= 16)
-  uint4 pre[kMaxPre];
-  auto fetch = [&](int k0) {
+  const int t = min((int)blockIdx.x * kRouterWarps + warp, T - 1);  // surplus warps redo the last token, write nothing
+  const bool live = (int)blockIdx.x * kRouterWarps + warp < T;
+  {  // this warp's token row -> f32 in shared memory (H % 8 == 0)
+    const uint2* x = reinterpret_cast<const uint2*>(X + (long long)t * H);
+    float4* dst = reinterpret_cast<float4*>(sx + (size_t)warp * H);
+    for (int i = lane; i < H / 4; i += 32) dst[i] = cvt4(x[i]);
+  }
+  const int vpr = KC / 4;  // 4-element groups per staged row
+  const int ngrp = E * vpr;
+  float acc[EPL];
 #pragma unroll
-    for (int i = 0; i < kMaxPre; ++i) {
-      const int idx = tid + i * kRouterThreads;
-      if (idx < nvec) {
-        const int e = idx / VPR, v = idx - e * VPR;
-        pre[i] = (k0 + v * 8 < H) ? *reinterpret_cast<const uint4*>(Wr + (long long)e * H + k0 + v * 8)
-                                  : make_uint4(0, 0, 0, 0);
-      }
-    }
-  };
-  auto stash = [&]() {
-#pragma unroll
-    for (int i = 0; i < kMaxPre; ++i) {
-      const int idx = tid + i * kRouterThreads;
-      if (idx < nvec) {
-        const int e = idx / VPR, v = idx - e * VPR;
-        *reinterpret_cast<uint4*>(rsm + e * ROWB + v * 16) = pre[i];
-      }
-    }
-  };
-  float acc[kMaxEPL];
-#pragma unroll
-  for (int i = 0; i < kMaxEPL; ++i) acc[i] = 0.f;
-  fetch(0);
+  for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
   for (int k0 = 0; k0 < H; k0 += KC) {
     __syncthreads();  // everyone is done with the previous chunk
-    stash();
+#pragma unroll 8
+    for (int idx = tid; idx < ngrp; idx += kRouterThreads) {  // independent loads: their latencies overlap
+      const int e = idx / vpr, v = idx - e * vpr;
+      const int k = k0 + v * 4;
+      float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < H) w = cvt4(*reinterpret_cast<const uint2*>(Wr + (long long)e * H + k));
+      *reinterpret_cast<float4*>(sw + e * ROW + v * 4) = w;
+    }
     __syncthreads();
-    if (k0 + KC < H) fetch(k0 + KC);
     const int klim = min(KC, H - k0);
+    const float* xr = sx + (size_t)warp * H + k0;
 #pragma unroll 4
-    for (int kk = 0; kk < klim; kk += 8) {
-      const uint4 xv = *reinterpret_cast<const uint4*>(x + k0 + kk);
-      const __half* xh = reinterpret_cast<const __half*>(&xv);
+    for (int kk = 0; kk < klim; kk += 4) {
+      const float4 xv = *reinterpret_cast<const float4*>(xr + kk);
 #pragma unroll
-      for (int i = 0; i < kMaxEPL; ++i) {
-        const int e = lane + 32 * i;
-        if (i < epl && e < E) {
-          const uint4 wv = *reinterpret_cast<const uint4*>(rsm + e * ROWB + kk * 2);
-          const __half* wh = reinterpret_cast<const __half*>(&wv);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[i] = fmaf(__half2float(xh[j]), __half2float(wh[j]), acc[i]);  // ascending k
-        }
+      for (int i = 0; i < EPL; ++i) {
+        const int e = min(lane + 32 * i, E - 1);  // lanes past E recompute the last expert and are ignored below
+        const float4 wv = *reinterpret_cast<const float4*>(sw + e * ROW + kk);
+        acc[i] = fmaf(xv.x, wv.x, acc[i]);  // ascending k
+        acc[i] = fmaf(xv.y, wv.y, acc[i]);
+        acc[i] = fmaf(xv.z, wv.z, acc[i]);
+        acc[i] = fmaf(xv.w, wv.w, acc[i]);
       }
     }
   }
   if (!live) return;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i)
+    if (lane + 32 * i >= E) acc[i] = -INFINITY;
   if (logits_out) {
 #pragma unroll
-    for (int i = 0; i < kMaxEPL; ++i)
-      if (i < epl && lane + 32 * i < E) logits_out[(long long)t * E + lane + 32 * i] = acc[i];
+    for (int i = 0; i < EPL; ++i)
+      if (lane + 32 * i < E) logits_out[(long long)t * E + lane + 32 * i] = acc[i];
   }
-  float sel[8];
-  int seli[8];
+  float mysel = 0.f, top = 0.f, sum = 0.f;  // lane s keeps the s-th selected logit
+  int myid = 0;
   for (int s = 0; s < topk; ++s) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < kMaxEPL; ++i) {
+    for (int i = 0; i < EPL; ++i) {
       const int e = lane + 32 * i;
-      if (i < epl && e < E && (acc[i] > bv || (acc[i] == bv && e < bi))) {
+      if (e < E && (acc[i] > bv || (acc[i] == bv && e < bi))) {
         bv = acc[i];
         bi = e;
       }
@@ -130,22 +128,20 @@ __global__ void __launch_bounds__(kRouterThreads)
         bi = oi;
       }
     }
-    sel[s] = bv;
-    seli[s] = bi;
+    if (s == 0) top = bv;
+    const float ex = expf(bv - top);
+    sum += ex;
+    if (lane == s) {
+      mysel = ex;
+      myid = bi;
+    }
 #pragma unroll
-    for (int i = 0; i < kMaxEPL; ++i)
+    for (int i = 0; i < EPL; ++i)
       if (lane + 32 * i == bi) acc[i] = -INFINITY;
   }
-  if (lane == 0) {
-    float sum = 0.f, ex[8];
-    for (int s = 0; s < topk; ++s) {
-      ex[s] = expf(sel[s] - sel[0]);
-      sum += ex[s];
-    }
-    for (int s = 0; s < topk; ++s) {
-      ids[(long long)s * T + t] = seli[s] + 1;
-      gates[(long long)s * T + t] = __float2half_rn(ex[s] / sum);
-    }
+  if (lane < topk) {
+    ids[(long long)lane * T + t] = myid + 1;
+    gates[(long long)lane * T + t] = __float2half_rn(mysel / sum);
   }
 }
 
@@ -153,6 +149,7 @@ __global__ void __launch_bounds__(kRouterThreads)
 constexpr int kAlignThreads = 1024;
 constexpr int kAlignWarps = kAlignThreads / 32;
 constexpr int kMaxExperts = 256;
+constexpr int kAlignRegIds = 16;  // ids a lane keeps in registers between the two passes
 
 template <typename IdT>
 __global__ void __launch_bounds__(kAlignThreads)
@@ -162,34 +159,49 @@ __global__ void __launch_bounds__(kAlignThreads)
   extern __shared__ int sm[];
   int* wcount = sm;                       // [kAlignWarps][E]: per-warp counts, then running offsets
   int* estart = sm + kAlignWarps * E;     // [E]: first padded position of expert e
-  int* etotal = estart + E;               // [E]
+  int* bstart = estart + E;               // [E+1]: first block of expert e
   __shared__ int bad;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int total = T * topk;
   const int seg = ((total + kAlignWarps - 1) / kAlignWarps + 31) & ~31;  // ids per warp, multiple of 32
   const int lo = warp * seg, hi = min(total, lo + seg);
+  const int niter = lo < hi ? (hi - lo + 31) / 32 : 0;
   if (tid == 0) bad = 0;
   for (int i = tid; i < kAlignWarps * E; i += kAlignThreads) wcount[i] = 0;
-  for (int i = tid; i < capacity_blocks * tile_m; i += kAlignThreads) sorted_token_ids[i] = total + 1;
-  for (int i = tid; i < capacity_blocks; i += kAlignThreads) sorted_expert_ids[i] = 0;
-  __syncthreads();
   // flat id i (0-based) = token*topk + slot; topk_ids is (T, topk) column-major
   auto expert_of = [&](int i) -> int {
     const int tok = i / topk, slot = i - tok * topk;
     return (int)topk_ids[(long long)slot * T + tok] - 1;
   };
-  for (int base = lo; base < hi; base += 32) {
-    const int i = base + lane;
-    int e = i < hi ? expert_of(i) : -1;
-    if (i < hi && (e < 0 || e >= E)) {
-      bad = 1;
-      e = -1;
+  int ecache[kAlignRegIds];  // this lane's experts, loaded up front so that the loads overlap
+#pragma unroll
+  for (int q = 0; q < kAlignRegIds; ++q) {
+    const int i = lo + q * 32 + lane;
+    ecache[q] = (q < niter && i < hi) ? expert_of(i) : -1;
+  }
+  for (int i = tid; i < capacity_blocks * tile_m; i += kAlignThreads) sorted_token_ids[i] = total + 1;
+  for (int i = tid; i < capacity_blocks; i += kAlignThreads) sorted_expert_ids[i] = 0;
+  __syncthreads();
+#pragma unroll 1
+  for (int q0 = 0; q0 < niter; q0 += kAlignRegIds) {
+#pragma unroll
+    for (int qq = 0; qq < kAlignRegIds; ++qq) {
+      const int q = q0 + qq;
+      if (q < niter) {
+        const int i = lo + q * 32 + lane;
+        int e = q0 == 0 ? ecache[qq] : (i < hi ? expert_of(i) : -1);
+        if (i < hi && (e < 0 || e >= E)) {
+          bad = 1;
+          e = -1;
+        }
+        const unsigned grp = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && (grp & ((1u << lane) - 1)) == 0) wcount[warp * E + e] += __popc(grp);
+        __syncwarp();  // the next iteration's group leader may be another lane
+      }
     }
-    const unsigned grp = __match_any_sync(0xffffffffu, e);
-    if (e >= 0 && (grp & ((1u << lane) - 1)) == 0) wcount[warp * E + e] += __popc(grp);
-    __syncwarp();  // the next iteration's group leader may be another lane
   }
   __syncthreads();
+  // per expert: exclusive prefix over warps; then an exclusive scan over experts of the block counts (warp 0)
   if (tid < E) {
     int run = 0;
     for (int w = 0; w < kAlignWarps; ++w) {
@@ -197,19 +209,28 @@ __global__ void __launch_bounds__(kAlignThreads)
       wcount[w * E + tid] = run;
       run += c;
     }
-    etotal[tid] = run;
+    estart[tid] = (run + tile_m - 1) / tile_m;  // blocks of this expert, replaced by the start below
   }
   __syncthreads();
-  if (tid == 0) {
-    int blk = 0;
-    for (int e = 0; e < E; ++e) {
-      estart[e] = blk * tile_m;
-      const int nb = (etotal[e] + tile_m - 1) / tile_m;
-      for (int b = 0; b < nb && blk + b < capacity_blocks; ++b) sorted_expert_ids[blk + b] = e + 1;
-      blk += nb;
+  if (warp == 0) {
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int nb = e < E ? estart[e] : 0;
+      int inc = nb;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+      }
+      if (e < E) bstart[e] = carry + inc - nb;
+      carry += __shfl_sync(0xffffffffu, inc, 31);
     }
-    if (blk > capacity_blocks) bad = 1;
-    *num_blocks = min(blk, capacity_blocks);
+    if (lane == 0) {
+      bstart[E] = carry;
+      if (carry > capacity_blocks) bad = 1;
+      *num_blocks = min(carry, capacity_blocks);
+    }
   }
   __syncthreads();
   if (bad) {
@@ -219,18 +240,34 @@ __global__ void __launch_bounds__(kAlignThreads)
     }
     return;
   }
-  for (int base = lo; base < hi; base += 32) {
-    const int i = base + lane;
-    const int e = i < hi ? expert_of(i) : -1;
-    const unsigned grp = __match_any_sync(0xffffffffu, e);
-    if (e >= 0) {
-      const int rank = __popc(grp & ((1u << lane) - 1));
-      const int pos = estart[e] + wcount[warp * E + e] + rank;
-      sorted_token_ids[pos] = i + 1;
+  if (tid < E) estart[tid] = bstart[tid] * tile_m;
+  for (int b = tid; b < bstart[E]; b += kAlignThreads) {  // expert of block b: last e with bstart[e] <= b
+    int l = 0, h = E - 1;
+    while (l < h) {
+      const int mid = (l + h + 1) >> 1;
+      if (bstart[mid] <= b) l = mid; else h = mid - 1;
     }
-    __syncwarp();
-    if (e >= 0 && (grp & ((1u << lane) - 1)) == 0) wcount[warp * E + e] += __popc(grp);
-    __syncwarp();
+    sorted_expert_ids[b] = l + 1;
+  }
+  __syncthreads();
+#pragma unroll 1
+  for (int q0 = 0; q0 < niter; q0 += kAlignRegIds) {
+#pragma unroll
+    for (int qq = 0; qq < kAlignRegIds; ++qq) {
+      const int q = q0 + qq;
+      if (q < niter) {
+        const int i = lo + q * 32 + lane;
+        const int e = q0 == 0 ? ecache[qq] : (i < hi ? expert_of(i) : -1);
+        const unsigned grp = __match_any_sync(0xffffffffu, e);
+        if (e >= 0) {
+          const int rank = __popc(grp & ((1u << lane) - 1));
+          sorted_token_ids[estart[e] + wcount[warp * E + e] + rank] = i + 1;
+        }
+        __syncwarp();
+        if (e >= 0 && (grp & ((1u << lane) - 1)) == 0) wcount[warp * E + e] += __popc(grp);
+        __syncwarp();
+      }
+    }
   }
 }
 
@@ -270,16 +307,20 @@ __device__ __forceinline__ int block_extent(const int* ids, int tile_m, int tota
   return last;
 }
 
-template <int EPI>
+constexpr int kMetaItems = 64;  // work items whose block metadata a CTA caches per round
+
+// EPI: epilogue.  NW: 128-row weight tiles per work item (2 for SwiGLU = gate tile + up tile; 2 for the plain
+// epilogues when the expert has at least 256 output rows, so that a gathered token tile is used by 256 rows).
+template <int EPI, int NW>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     moe_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const GemmParams p, int* status) {
-  constexpr int NW = EPI == EPI_SWIGLU ? 2 : 1;  // weight tiles per stage
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int kMaxStages = 8;
   __shared__ __align__(8) uint64_t w_full[kMaxStages], b_full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ int meta_e[kMetaItems], meta_ext[kMetaItems];  // expert (0-based, -1 = skip) and slot extent per item
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     abort_s = 0;
@@ -306,162 +347,214 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   volatile int* abort = &abort_s;
   const int nblocks = p.num_blocks_host >= 0 ? p.num_blocks_host : *p.num_blocks_dev;
   const int items = nblocks * p.n_tiles;
+  const int my_items = (int)blockIdx.x < items ? (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int nk = (p.K + kBK - 1) / kBK;
-  const int wbytes = NW * kWTile;
+  constexpr int wbytes = NW * kWTile;
+  constexpr int kRowsItem = NW * kRows;  // for SwiGLU: 128 gate rows + the matching 128 up rows
 
-  if (warp == 0) {
-    // ---- weight producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int it = blockIdx.x; it < items; it += gridDim.x) {
-        const int bm = it / p.n_tiles, nt = it - bm * p.n_tiles;
-        const int e = p.expert_ids[bm] - 1;
-        if (e < 0 || e >= p.E) continue;
-        for (int kb = 0; kb < nk; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) goto done;
-          unsigned char* dst = smem + (size_t)stage * p.stage_bytes;
-          mbar_expect_tx(&w_full[stage], wbytes);
-          tma_load_3d(dst, &tmW, kb * kBK, nt * kRows, e, &w_full[stage]);
-          if (NW == 2) tma_load_3d(dst + kWTile, &tmW, kb * kBK, p.N + nt * kRows, e, &w_full[stage]);
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
-        }
+  // pipeline state of each role persists across rounds
+  int stage = 0, nacc = 0;
+  uint32_t phase = 0;
+
+  for (int r0 = 0; r0 < my_items; r0 += kMetaItems) {
+    const int rn = min(kMetaItems, my_items - r0);
+    // ---- every warp: cache the metadata of this round's items (global-load latency paid once, in parallel)
+    for (int n = warp; n < rn; n += kGemmThreads / 32) {
+      const int it = blockIdx.x + (r0 + n) * gridDim.x;
+      const int bm = it / p.n_tiles;
+      int e = p.expert_ids[bm] - 1;
+      if (e < 0 || e >= p.E) e = -1;
+      const int ext = block_extent(p.sorted_ids + (long long)bm * p.tile_m, p.tile_m, p.total, lane);
+      if (lane == 0) {
+        meta_e[n] = ext > 0 ? e : -1;
+        meta_ext[n] = ext;
       }
     }
-  } else if (warp == 1) {
-    // ---- MMA issuer
-    int stage = 0, n = 0;
-    uint32_t phase = 0;
-    for (int it = blockIdx.x; it < items; it += gridDim.x) {
-      const int bm = it / p.n_tiles;
-      const int e = p.expert_ids[bm] - 1;
-      if (e < 0 || e >= p.E) continue;
-      const int ext = block_extent(p.sorted_ids + (long long)bm * p.tile_m, p.tile_m, p.total, lane);
-      const int nmma = max(16, (ext + 15) & ~15);
-      const int acc = n & 1;
-      const uint32_t acc_phase = (n >> 1) & 1;
-      ++n;
-      int failed = 0;
-      if (lane == 0) {
+    __syncthreads();
+
+    if (warp == 0) {
+      // ---- weight producer: the whole warp walks the loop, one elected lane issues
+      for (int n = 0; n < rn && !*abort; ++n) {
+        const int e = meta_e[n];
+        if (e < 0) continue;
+        const int it = blockIdx.x + (r0 + n) * gridDim.x;
+        const int nt = it % p.n_tiles;
+        bool ok = true;
+        for (int kb = 0; kb < nk; ++kb) {
+          ok = CTB_WARP_WAIT(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+          if (!ok) break;
+          unsigned char* dst = smem + (size_t)stage * p.stage_bytes;
+          if (elect_one()) {
+            mbar_expect_tx(&w_full[stage], wbytes);
+            if (EPI == EPI_SWIGLU) {
+              tma_load_3d(dst, &tmW, kb * kBK, nt * kRows, e, &w_full[stage]);
+              tma_load_3d(dst + kWTile, &tmW, kb * kBK, p.N + nt * kRows, e, &w_full[stage]);
+            } else {
+#pragma unroll
+              for (int w = 0; w < NW; ++w)
+                tma_load_3d(dst + w * kWTile, &tmW, kb * kBK, nt * kRowsItem + w * kRows, e, &w_full[stage]);
+            }
+          }
+          __syncwarp();
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+      }
+    } else if (warp == 1) {
+      // ---- MMA issuer: the whole warp walks the loop, one elected lane issues
+      for (int n = 0; n < rn && !*abort; ++n) {
+        if (meta_e[n] < 0) continue;
+        const int nmma = max(16, (meta_ext[n] + 15) & ~15);
+        const int acc = nacc & 1;
+        const uint32_t acc_phase = (nacc >> 1) & 1;
+        ++nacc;
         const uint32_t idesc = make_idesc(FMT_F16, kRows, (uint32_t)nmma, 0, 0);
-        failed = !mbar_wait(&acc_empty[acc], acc_phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+        if (!CTB_WARP_WAIT(&acc_empty[acc], acc_phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
         tc_fence_after();
         const uint32_t d = tmem + acc * 256;
-        for (int kb = 0; kb < nk && !failed; ++kb) {
-          if (!mbar_wait(&w_full[stage], phase, status, DEV_TIMEOUT_TMA, abort) ||
-              !mbar_wait(&b_full[stage], phase, status, DEV_TIMEOUT_SLOT, abort)) {
-            failed = 1;
-            break;
-          }
+        bool ok = true;
+        for (int kb = 0; kb < nk; ++kb) {
+          ok = CTB_WARP_WAIT(&w_full[stage], phase, status, DEV_TIMEOUT_TMA, abort) &&
+               CTB_WARP_WAIT(&b_full[stage], phase, status, DEV_TIMEOUT_SLOT, abort);
+          if (!ok) break;
           fence_proxy_async_smem();  // the gathered rows were written through the generic proxy
           tc_fence_after();
           const uint32_t sw = smem_u32(smem + (size_t)stage * p.stage_bytes);
           const uint32_t sb = sw + wbytes;
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            const uint64_t bd = make_sdesc_sw128(sb + k * 32, 0, 1024);
-            mma_f16_ss(d, make_sdesc_sw128(sw + k * 32, 0, 1024), bd, idesc, (kb | k) != 0);
-            if (NW == 2) mma_f16_ss(d + 128, make_sdesc_sw128(sw + kWTile + k * 32, 0, 1024), bd, idesc, (kb | k) != 0);
+            for (int k = 0; k < kBK / 16; ++k) {
+              const uint64_t bd = make_sdesc_sw128(sb + k * 32, 0, 1024);
+#pragma unroll
+              for (int w = 0; w < NW; ++w)
+                mma_f16_ss(d + w * 128, make_sdesc_sw128(sw + w * kWTile + k * 32, 0, 1024), bd, idesc, (kb | k) != 0);
+            }
+            tc_commit(&empty[stage]);
           }
-          tc_commit(&empty[stage]);
+          __syncwarp();
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
-        if (!failed) tc_commit(&acc_full[acc]);
+        if (!ok) break;
+        if (elect_one()) tc_commit(&acc_full[acc]);
+        __syncwarp();
       }
-      failed = __shfl_sync(0xffffffffu, failed, 0);
-      if (failed) break;
-    }
-  } else if (warp < 6) {
-    // ---- token-row gather into the swizzled B operand
-    const int g = threadIdx.x - 64;  // 0..127
-    int stage = 0;
-    uint32_t phase = 0;
-    for (int it = blockIdx.x; it < items; it += gridDim.x) {
-      const int bm = it / p.n_tiles;
-      const int e = p.expert_ids[bm] - 1;
-      if (e < 0 || e >= p.E) continue;
-      const int* ids = p.sorted_ids + (long long)bm * p.tile_m;
-      const int ext = block_extent(ids, p.tile_m, p.total, lane);
-      const int nmma = max(16, (ext + 15) & ~15);
-      const __half* src = nullptr;
-      if (g < p.tile_m) {
-        const int id = ids[g];
-        if (id >= 1 && id <= p.total) {
-          const int tok = (id - 1) / p.replicas;  // cld(id, replicas) - 1
-          if (tok < p.a_rows) src = p.A + (long long)tok * p.lda;
-        }
-      }
+    } else if (warp < 6) {
+      // ---- token-row gather into the swizzled B operand (cp.async, completion arrives on b_full)
+      const int g = threadIdx.x - 64;  // 0..127 = slot inside the block
       const uint32_t roff = (uint32_t)(g >> 3) * 1024 + (uint32_t)(g & 7) * 128;
-      for (int kb = 0; kb < nk; ++kb) {
-        bool ok = mbar_wait(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) goto done;
-        if (g < nmma) {
-          unsigned char* dst = smem + (size_t)stage * p.stage_bytes + wbytes + roff;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const int k = kb * kBK + c * 8;
-            const bool valid = src && k < p.K;
-            cp_async16(dst + ((c ^ (g & 7)) << 4), valid ? (const void*)(src + k) : (const void*)p.A, valid ? 16u : 0u);
+      for (int n = 0; n < rn; ++n) {
+        if (meta_e[n] < 0) continue;
+        const int nmma = max(16, (meta_ext[n] + 15) & ~15);
+        const int it = blockIdx.x + (r0 + n) * gridDim.x;
+        const int bm = it / p.n_tiles;
+        const __half* src = nullptr;
+        if (g < p.tile_m) {
+          const int id = p.sorted_ids[(long long)bm * p.tile_m + g];
+          if (id >= 1 && id <= p.total) {
+            const int tok = (id - 1) / p.replicas;  // cld(id, replicas) - 1
+            if (tok < p.a_rows) src = p.A + (long long)tok * p.lda;
           }
         }
-        cp_async_arrive_noinc(&b_full[stage]);  // fires when this thread's copies have landed
-        if (++stage == p.stages) { stage = 0; phase ^= 1; }
-      }
-    }
-  } else {
-    // ---- epilogue
-    const int sub = warp & 3;
-    const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
-    int n = 0;
-    for (int it = blockIdx.x; it < items; it += gridDim.x) {
-      const int bm = it / p.n_tiles, nt = it - bm * p.n_tiles;
-      const int e = p.expert_ids[bm] - 1;
-      if (e < 0 || e >= p.E) continue;
-      const int* ids = p.sorted_ids + (long long)bm * p.tile_m;
-      const int ext = block_extent(ids, p.tile_m, p.total, lane);
-      const int acc = n & 1;
-      const uint32_t acc_phase = (n >> 1) & 1;
-      ++n;
-      bool ok = mbar_wait(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) goto done;
-      tc_fence_after();
-      const int row = nt * kRows + sub * 32 + lane;
-      const uint32_t taddr = tmem + lane_addr + acc * 256;
-      for (int c0 = 0; c0 < ext; c0 += 16) {
-        uint32_t ga[16], up[16];
-        tmem_ld16(taddr + c0, ga);
-        if (EPI == EPI_SWIGLU) tmem_ld16(taddr + 128 + c0, up);
-        tc_wait_ld();
+        bool ok = true;
+        for (int kb = 0; kb < nk; ++kb) {
+          ok = mbar_wait(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (g < nmma) {
+            unsigned char* dst = smem + (size_t)stage * p.stage_bytes + wbytes + roff;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int slot = c0 + j;
-          if (slot >= ext) break;
-          const int id = ids[slot];  // uniform across the warp
-          if (id < 1 || id > p.total || row >= p.N) continue;
-          float v = __uint_as_float(ga[j]);
-          if (EPI == EPI_SWIGLU) {
-            // silu(g) * u with flush-to-zero and an approximate reciprocal (examples/moe.jl:117-124)
-            const float sig = rcp_approx_ftz(1.0f + __expf(-v));
-            v = v * sig * __uint_as_float(up[j]);
+            for (int c = 0; c < 8; ++c) {
+              const int k = kb * kBK + c * 8;
+              const bool valid = src && k < p.K;
+              cp_async16(dst + ((c ^ (g & 7)) << 4), valid ? (const void*)(src + k) : (const void*)p.A, valid ? 16u : 0u);
+            }
           }
-          if (p.mul_weight) {
+          cp_async_arrive_noinc(&b_full[stage]);  // fires when this thread's copies have landed
+          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+      }
+    } else {
+      // ---- epilogue
+      const int sub = warp & 3;
+      const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
+      for (int n = 0; n < rn; ++n) {
+        if (meta_e[n] < 0) continue;
+        const int ext = meta_ext[n];
+        const int it = blockIdx.x + (r0 + n) * gridDim.x;
+        const int bm = it / p.n_tiles, nt = it - bm * p.n_tiles;
+        const int acc = nacc & 1;
+        const uint32_t acc_phase = (nacc >> 1) & 1;
+        ++nacc;
+        // slot ids and routing weights of the block: lane l holds slots l, l+32, l+64, l+96 (loaded before the wait)
+        int sid[4];
+        float swt[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int slot = q * 32 + lane;
+          int id = slot < p.tile_m ? p.sorted_ids[(long long)bm * p.tile_m + slot] : 0;
+          if (id < 1 || id > p.total) id = 0;
+          sid[q] = id;
+          swt[q] = 1.f;
+          if (p.mul_weight && id) {
             const int f = id - 1;
-            v *= __half2float(p.topk_w[p.w_tokens ? (long long)(f % p.w_topk) * p.w_tokens + f / p.w_topk : f]);
+            swt[q] = __half2float(p.topk_w[p.w_tokens ? (long long)(f % p.w_topk) * p.w_tokens + f / p.w_topk : f]);
           }
-          if (EPI == EPI_F32)
-            reinterpret_cast<float*>(p.C)[(long long)(id - 1) * p.ldc + row] = v;
-          else
-            reinterpret_cast<__half*>(p.C)[(long long)(id - 1) * p.ldc + row] = __float2half_rn(v);
         }
+        bool ok = mbar_wait(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem + lane_addr + acc * 256;
+        const int row0 = (EPI == EPI_SWIGLU ? nt * kRows : nt * kRowsItem) + sub * 32 + lane;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (q * 32 < ext) {
+#pragma unroll
+            for (int hlf = 0; hlf < 2; ++hlf) {
+              const int c0 = q * 32 + hlf * 16;
+              if (c0 < ext) {
+                uint32_t ga[16], up[16];
+                tmem_ld16(taddr + c0, ga);
+                if (NW == 2) tmem_ld16(taddr + 128 + c0, up);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const int id = __shfl_sync(0xffffffffu, sid[q], hlf * 16 + j);
+                  const float wt = __shfl_sync(0xffffffffu, swt[q], hlf * 16 + j);
+                  if (id == 0) continue;
+                  float v0 = __uint_as_float(ga[j]);
+                  if (EPI == EPI_SWIGLU) {
+                    // silu(g) * u with flush-to-zero and an approximate reciprocal (examples/moe.jl:117-124)
+                    const float sig = rcp_approx_ftz(1.0f + __expf(-v0));
+                    v0 = v0 * sig * __uint_as_float(up[j]);
+                    if (row0 < p.N) reinterpret_cast<__half*>(p.C)[(long long)(id - 1) * p.ldc + row0] = __float2half_rn(v0);
+                  } else {
+#pragma unroll
+                    for (int w = 0; w < NW; ++w) {
+                      const int row = row0 + w * kRows;
+                      const float v = (w == 0 ? v0 : __uint_as_float(up[j])) * wt;
+                      if (row < p.N) {
+                        if (EPI == EPI_F32)
+                          reinterpret_cast<float*>(p.C)[(long long)(id - 1) * p.ldc + row] = v;
+                        else
+                          reinterpret_cast<__half*>(p.C)[(long long)(id - 1) * p.ldc + row] = __float2half_rn(v);
+                      }
+                    }
+                  }
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
     }
+    __syncthreads();  // the metadata cache is rewritten in the next round
+    if (*abort) break;
   }
-done:
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -516,21 +609,23 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
   p.w_tokens = w_tokens; p.w_topk = w_topk;
   p.K = K; p.N = N; p.E = E; p.tile_m = tile_m; p.total = total;
   p.C = C; p.ldc = ldc;
-  p.n_tiles = (N + kRows - 1) / kRows;
-  const int nw = epi == EPI_SWIGLU ? 2 : 1;
+  const int nw = (epi == EPI_SWIGLU || N >= 2 * kRows) ? 2 : 1;
+  p.n_tiles = epi == EPI_SWIGLU ? (N + kRows - 1) / kRows : (N + nw * kRows - 1) / (nw * kRows);
   p.stage_bytes = nw * kWTile + tile_m * 128;
   p.stages = std::min(8, (int)((220 * 1024) / p.stage_bytes));
   const size_t smem = (size_t)p.stages * p.stage_bytes + 1024;
   const long long items = (long long)max_blocks * p.n_tiles;
   const int grid = (int)std::max<long long>(1, std::min<long long>(items, ctx->sm_count));
   cudaError_t e;
-#define CTB_LAUNCH_MOE(EPI)                                                                              \
-  e = cudaFuncSetAttribute(moe_gemm_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-  if (e != cudaSuccess) return cuda_fail(e, "moe gemm: shared memory opt-in");                           \
-  moe_gemm_kernel<EPI><<<grid, kGemmThreads, smem, st>>>(tw, p, ctx->dev_status);
-  if (epi == EPI_SWIGLU) { CTB_LAUNCH_MOE(EPI_SWIGLU) }
-  else if (epi == EPI_F32) { CTB_LAUNCH_MOE(EPI_F32) }
-  else { CTB_LAUNCH_MOE(EPI_F16) }
+#define CTB_LAUNCH_MOE(EPI, NWV)                                                                              \
+  e = cudaFuncSetAttribute(moe_gemm_kernel<EPI, NWV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+  if (e != cudaSuccess) return cuda_fail(e, "moe gemm: shared memory opt-in");                                \
+  moe_gemm_kernel<EPI, NWV><<<grid, kGemmThreads, smem, st>>>(tw, p, ctx->dev_status);
+  if (epi == EPI_SWIGLU) { CTB_LAUNCH_MOE(EPI_SWIGLU, 2) }
+  else if (epi == EPI_F32 && nw == 2) { CTB_LAUNCH_MOE(EPI_F32, 2) }
+  else if (epi == EPI_F32) { CTB_LAUNCH_MOE(EPI_F32, 1) }
+  else if (nw == 2) { CTB_LAUNCH_MOE(EPI_F16, 2) }
+  else { CTB_LAUNCH_MOE(EPI_F16, 1) }
 #undef CTB_LAUNCH_MOE
   CTB_CHECK_LAUNCH("moe gemm launch");
   return CTB_OK;
@@ -538,7 +633,7 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
 
 int launch_align(ctb_ctx* ctx, cudaStream_t st, const void* topk_ids, int ids_bits, int T, int topk, int E, int tile_m,
                  int* sorted_token_ids, int* sorted_expert_ids, int* num_blocks, int capacity) {
-  const size_t smem = (size_t)(kAlignWarps * E + 2 * E) * sizeof(int);
+  const size_t smem = (size_t)(kAlignWarps * E + 2 * E + 1) * sizeof(int);
   if (ids_bits == 32)
     moe_align_kernel<int><<<1, kAlignThreads, smem, st>>>((const int*)topk_ids, T, topk, E, tile_m, sorted_token_ids,
                                                           sorted_expert_ids, num_blocks, capacity, ctx->dev_status);
@@ -572,19 +667,35 @@ int ctb_moe_router(ctb_ctx* ctx, void* stream, const void* hidden, const void* W
   CTB_CHECK_CTX(ctx);
   if (T < 0 || H <= 0 || E <= 0 || topk <= 0) return fail(CTB_BAD_ARG, "ctb_moe_router: non-positive dimension");
   if (E > 32 * kMaxEPL) return fail(CTB_UNSUPPORTED, "ctb_moe_router: at most %d experts", 32 * kMaxEPL);
-  if (topk > 8 || topk > E) return fail(CTB_UNSUPPORTED, "ctb_moe_router: topk must be <= min(8, E)");
+  if (topk > 32 || topk > E) return fail(CTB_UNSUPPORTED, "ctb_moe_router: topk must be <= min(32, E)");
   if (H % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_router: hidden size must be a multiple of 8");
   if (T == 0) return CTB_OK;
   CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(W_r); CTB_CHECK_DEV(topk_ids); CTB_CHECK_DEV(topk_weights);
   if ((uintptr_t)hidden % 16 || (uintptr_t)W_r % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_router: 16-byte alignment");
   const int grid = (int)((T + kRouterWarps - 1) / kRouterWarps);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (E <= 128)  // 128 K-elements per staged chunk: at most 128 * 272 B of shared memory
-    moe_router_kernel<128><<<grid, kRouterThreads, (size_t)E * (128 * 2 + 16), st>>>(
-        (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk);
-  else
-    moe_router_kernel<64><<<grid, kRouterThreads, (size_t)E * (64 * 2 + 16), st>>>(
-        (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk);
+  // stage as much of W_r as fits beside the token rows (K-chunk KC, a multiple of 64)
+  const size_t budget = 200 * 1024, xbytes = (size_t)kRouterWarps * H * sizeof(float);
+  if (xbytes + (size_t)E * (64 + 4) * sizeof(float) > budget)
+    return fail(CTB_UNSUPPORTED, "ctb_moe_router: hidden size %lld too large", (long long)H);
+  int KC = (int)(((budget - xbytes) / ((size_t)E * sizeof(float)) - 4) / 64 * 64);
+  KC = (int)std::min<int64_t>(KC, (H + 63) / 64 * 64);
+  const size_t smem = xbytes + (size_t)E * (KC + 4) * sizeof(float);
+  const int epl = (int)((E + 31) / 32);
+#define CTB_ROUTER(EPL)                                                                                     \
+  {                                                                                                         \
+    cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int)smem);                                                        \
+    if (e != cudaSuccess) return cuda_fail(e, "ctb_moe_router: shared memory opt-in");                      \
+    moe_router_kernel<EPL><<<grid, kRouterThreads, smem, st>>>((const __half*)hidden, (const __half*)W_r,    \
+                                                               topk_ids, (__half*)topk_weights, logits,     \
+                                                               (int)T, (int)H, (int)E, topk, KC);           \
+  }
+  if (epl <= 1) CTB_ROUTER(1)
+  else if (epl <= 2) CTB_ROUTER(2)
+  else if (epl <= 4) CTB_ROUTER(4)
+  else CTB_ROUTER(8)
+#undef CTB_ROUTER
   CTB_CHECK_LAUNCH("ctb_moe_router launch");
   return CTB_OK;
 }

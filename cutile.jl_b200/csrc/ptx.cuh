@@ -23,6 +23,19 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// True in exactly one lane of a fully converged warp.  Role loops that feed TMA and
+// tcgen05.mma are written so that the whole warp walks them in lock step and only
+// the instruction itself sits behind this predicate: descriptors, coordinates and
+// addresses are then warp-uniform values that the compiler can keep in uniform
+// registers instead of moving them over from per-thread registers before every issue.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+// mbar_wait for a whole warp: every lane polls; the result is made uniform.
+#define CTB_WARP_WAIT(...) (__all_sync(0xffffffffu, mbar_wait(__VA_ARGS__)))
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
