@@ -12,9 +12,13 @@
 //   warp 1    MMA issuer (one thread): S = Q*K^T  (tcgen05.mma 128x128x16, both
 //             operands K-major in shared memory, S in TMEM columns 0..127);
 //             PV = P*V (128x64x16, P read from TMEM columns 128..191 as the A
-//             operand, V MN-major in shared memory, result in columns 192..255);
-//   warps 2-5 softmax: thread = query row (TMEM lane).  Row max, exp2, row sum,
-//             P written back to TMEM as packed f16.  O accumulates in TMEM across
+//             operand, V MN-major in shared memory, result in columns 192..255).
+//             S(j+1) is issued as soon as the softmax warps have pulled S(j) into
+//             registers, i.e. before P(j) is complete, so the scores of the next
+//             tile are normally waiting when softmax(j) ends;
+//   warps 2-5 softmax: thread = query row (TMEM lane).  The 128 scores of the row
+//             are pulled into registers at once (which frees S), then row max,
+//             exp2, row sum, P written back to TMEM as packed f16.  O accumulates in TMEM across
 //             tiles; it is rescaled (read, multiplied, written back) only when a
 //             row's maximum has grown by more than 2^8 since the exponent
 //             reference was last moved, which is exact (P and the row sum use the
@@ -55,7 +59,7 @@ __global__ void __launch_bounds__(kThreads, 2)
   unsigned char* sK = smem + kTileBytes;
   unsigned char* sV = sK + kKStages * kTileBytes;
   __shared__ __align__(8) uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages],
-      s_full, p_full, o_full;
+      s_full, s_free, p_full, o_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
@@ -83,6 +87,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     for (int s = 0; s < kKStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     for (int s = 0; s < kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     mbar_init(&s_full, 1);
+    mbar_init(&s_free, 4);
     mbar_init(&p_full, 4);
     mbar_init(&o_full, 1);
     fence_mbar_init();
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     const uint32_t aQ = smem_u32(sQ);
     auto issue_qk = [&](int j) -> bool {
       const int ks = j % kKStages;
-      if (!CTB_WARP_WAIT(&k_full[ks], (j / kKStages) & 1, status, DEV_TIMEOUT_TMA, abort)) return false;
+      if (j == 0 && !CTB_WARP_WAIT(&k_full[ks], 0, status, DEV_TIMEOUT_TMA, abort)) return false;  // later tiles: caller waited
       tc_fence_after();
       const uint32_t aK = smem_u32(sK + ks * kTileBytes);
       if (elect_one()) {
@@ -148,8 +153,16 @@ __global__ void __launch_bounds__(kThreads, 2)
     if (ok) ok = issue_qk(0);
     for (int j = 0; ok && j < Tc; ++j) {
       const int vs = j % kVStages;
-      if (!CTB_WARP_WAIT(&p_full, j & 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+      // S(j) has been read into registers: the next scores can overwrite it while softmax(j) still runs
+      if (j + 1 < Tc) {
+        const int ks = (j + 1) % kKStages;  // the K tile landed long ago: take that wait off the critical path
+        if (!CTB_WARP_WAIT(&k_full[ks], ((j + 1) / kKStages) & 1, status, DEV_TIMEOUT_TMA, abort)) break;
+        if (!CTB_WARP_WAIT(&s_free, j & 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+        ok = issue_qk(j + 1);
+        if (!ok) break;
+      }
       if (!CTB_WARP_WAIT(&v_full[vs], (j / kVStages) & 1, status, DEV_TIMEOUT_TMA, abort)) break;
+      if (!CTB_WARP_WAIT(&p_full, j & 1, status, DEV_TIMEOUT_SLOT, abort)) break;
       tc_fence_after();
       const uint32_t aV = smem_u32(sV + vs * kTileBytes);
       if (elect_one()) {
@@ -160,7 +173,6 @@ __global__ void __launch_bounds__(kThreads, 2)
         tc_commit(&o_full);
       }
       __syncwarp();
-      if (j + 1 < Tc) ok = issue_qk(j + 1);
     }
   } else {
     const int sub = warp & 3;
@@ -178,77 +190,75 @@ __global__ void __launch_bounds__(kThreads, 2)
       tc_fence_after();
       const bool masked = j >= mask_start;
       const int lim = vis_last - j * kTN;  // column i of this tile is visible iff i <= lim
-      uint32_t ra[32], rb[32];
-      // ---- pass 1: row maximum of the raw scores (loads run one chunk ahead)
+      // ---- the whole score row goes to registers in one go; S is then free for the next tile's Q*K^T
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(trow + kColS + c * 32, sr[c]);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free);
+      // ---- row maximum of the raw scores (four independent chains)
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-      auto max_chunk = [&](const uint32_t (&r)[32], int c) {
-        if (masked) {
+      if (masked) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, c * 32 + i + 0 <= lim ? __uint_as_float(r[i + 0]) : -INFINITY);
-            mx1 = fmaxf(mx1, c * 32 + i + 1 <= lim ? __uint_as_float(r[i + 1]) : -INFINITY);
-            mx2 = fmaxf(mx2, c * 32 + i + 2 <= lim ? __uint_as_float(r[i + 2]) : -INFINITY);
-            mx3 = fmaxf(mx3, c * 32 + i + 3 <= lim ? __uint_as_float(r[i + 3]) : -INFINITY);
+            mx0 = fmaxf(mx0, c * 32 + i + 0 <= lim ? __uint_as_float(sr[c][i + 0]) : -INFINITY);
+            mx1 = fmaxf(mx1, c * 32 + i + 1 <= lim ? __uint_as_float(sr[c][i + 1]) : -INFINITY);
+            mx2 = fmaxf(mx2, c * 32 + i + 2 <= lim ? __uint_as_float(sr[c][i + 2]) : -INFINITY);
+            mx3 = fmaxf(mx3, c * 32 + i + 3 <= lim ? __uint_as_float(sr[c][i + 3]) : -INFINITY);
           }
-        } else {
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(r[i + 0]));
-            mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+            mx0 = fmaxf(mx0, __uint_as_float(sr[c][i + 0]));
+            mx1 = fmaxf(mx1, __uint_as_float(sr[c][i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(sr[c][i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(sr[c][i + 3]));
           }
-        }
-      };
-      tmem_ld32(trow + kColS + 0, ra);
-      tc_wait_ld();
-      tmem_ld32(trow + kColS + 32, rb);
-      max_chunk(ra, 0);
-      tc_wait_ld();
-      tmem_ld32(trow + kColS + 64, ra);
-      max_chunk(rb, 1);
-      tc_wait_ld();
-      tmem_ld32(trow + kColS + 96, rb);
-      max_chunk(ra, 2);
-      tc_wait_ld();
-      tmem_ld32(trow + kColS + 0, ra);  // first chunk of pass 2, in flight while the maximum is finished
-      max_chunk(rb, 3);
+      }
       const float m_true = fmaxf(m_ref, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
       // ---- move the exponent reference (and rescale O, l) only when the maximum grew by more than 2^8
       const bool grow = m_true - m_ref > 8.0f || m_ref == -INFINITY;
+      if (j > 0) {  // PV(j-1) must have consumed P(j-1) (and, for a rescale, landed in O) before P(j) is written
+        ok = mbar_wait(&o_full, (j - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = m_true == -INFINITY ? 0.f : m_true;  // fully masked so far: keep everything zero
         const float alpha = ex2_approx_ftz(m_ref - m_new);       // 0 on the first tile
         l *= alpha;
         m_ref = m_new;
-        if (j > 0) {  // O holds the sum of the previous tiles; PV(j-1) must have landed
-          ok = mbar_wait(&o_full, (j - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          tc_wait_ld();  // chunk 0 of pass 2 is already in ra; rb is free
-#pragma unroll
-          for (int c = 0; c < kD / 32; ++c) {
-            tmem_ld32(trow + kColO + c * 32, rb);
+        if (j > 0) {  // O holds the sum of the previous tiles
+#pragma unroll 1
+          for (int c = 0; c < kD / 16; ++c) {
+            uint32_t t[16];
+            tmem_ld16(trow + kColO + c * 16, t);
             tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) rb[i] = __float_as_uint(__uint_as_float(rb[i]) * alpha);
-            tmem_st16(trow + kColO + c * 32, reinterpret_cast<const uint32_t(&)[16]>(rb[0]));
-            tmem_st16(trow + kColO + c * 32 + 16, reinterpret_cast<const uint32_t(&)[16]>(rb[16]));
+            for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+            tmem_st16(trow + kColO + c * 16, t);
           }
         }
       }
-      // ---- pass 2: p = exp2(s*scale - m_ref), row sum, P -> TMEM as packed f16
+      // ---- p = exp2(s*scale - m_ref), row sum, P -> TMEM as packed f16
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       const float nm = -m_ref;
-      auto exp_chunk = [&](const uint32_t (&r)[32], int c) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          float p0 = ex2_approx_ftz(fmaf(__uint_as_float(r[i + 0]), p.scale_log2, nm));
-          float p1 = ex2_approx_ftz(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, nm));
-          float p2 = ex2_approx_ftz(fmaf(__uint_as_float(r[i + 2]), p.scale_log2, nm));
-          float p3 = ex2_approx_ftz(fmaf(__uint_as_float(r[i + 3]), p.scale_log2, nm));
+          float p0 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][i + 0]), p.scale_log2, nm));
+          float p1 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, nm));
+          float p2 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][i + 2]), p.scale_log2, nm));
+          float p3 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][i + 3]), p.scale_log2, nm));
           if (masked) {
             if (c * 32 + i + 0 > lim) p0 = 0.f;
             if (c * 32 + i + 1 > lim) p1 = 0.f;
@@ -260,18 +270,7 @@ __global__ void __launch_bounds__(kThreads, 2)
           pk[(i >> 1) + 1] = pack_f16x2(p2, p3);
         }
         tmem_st16(trow + kColP + c * 16, pk);
-      };
-      tc_wait_ld();
-      tmem_ld32(trow + kColS + 32, rb);
-      exp_chunk(ra, 0);
-      tc_wait_ld();
-      tmem_ld32(trow + kColS + 64, ra);
-      exp_chunk(rb, 1);
-      tc_wait_ld();
-      tmem_ld32(trow + kColS + 96, rb);
-      exp_chunk(ra, 2);
-      tc_wait_ld();
-      exp_chunk(rb, 3);
+      }
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
