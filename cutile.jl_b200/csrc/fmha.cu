@@ -5,8 +5,10 @@
 // (:124), approximate final divide (:132-134), causal mask with a query offset
 // `input_pos`, ragged K/V length, grouped-query heads.
 //
-// One CTA per (128-query tile, batch*head), two CTAs resident per SM so that one
-// CTA's softmax overlaps the other's tensor-core work.  6 warps:
+// Persistent CTAs, two per SM (so that one CTA's softmax overlaps the other's
+// tensor-core work), each walking a static list of (128-query tile, batch*head)
+// work items dealt heaviest first in alternating direction.  Loads of the next
+// item (a second Q buffer, the K/V rings) run under the current one.  6 warps:
 //   warp 0    TMA producer: Q once, then K and V tiles (128 keys x 64, 128-byte
 //             swizzle) through two mbarrier rings;
 //   warp 1    MMA issuer (one thread): S = Q*K^T  (tcgen05.mma 128x128x16, both
@@ -25,7 +27,6 @@
 //             same reference) and happens at most a few times per row.
 // Like the reference (:69-76) the loop stops at the last tile that a causal
 // query tile can see, and only tiles from `mask_start` on pay for masking.
-// Heavier (later) query tiles are scheduled first.
 #include <math.h>
 
 #include "ctx.h"
@@ -37,7 +38,7 @@ using namespace ctb_internal;
 namespace {
 
 constexpr int kTM = 128, kTN = 128, kD = 64;
-constexpr int kKStages = 3, kVStages = 2;
+constexpr int kQBufs = 2, kKStages = 2, kVStages = 2;
 constexpr int kThreads = 192;
 constexpr int kTileBytes = kTN * kD * 2;  // 16 KiB: one Q, K or V tile
 constexpr uint32_t kTmemCols = 256;
@@ -47,8 +48,34 @@ struct Params {
   int seq_q, seq_kv, heads, kv_heads, group, batch;
   int input_pos, causal;
   float scale_log2;  // qk_scale / ln 2
-  int q_tiles;
+  int q_tiles, bh_total, items;
 };
+
+// One work item = one (128-query tile, batch*head).  Items are numbered heaviest first (the last query tile of a
+// causal problem sees the most keys) and dealt to the persistent CTAs in rounds of alternating direction, so that
+// every CTA gets a mix of heavy and light items.
+struct Item {
+  int bh, q0, kvz, Tc, mask_start;
+};
+__device__ __forceinline__ bool get_item(const Params& p, int i, Item& it) {
+  const int G = gridDim.x, c = blockIdx.x;
+  const long long w = (long long)i * G + ((i & 1) ? G - 1 - c : c);
+  if (w >= p.items) return false;
+  const int qt = p.q_tiles - 1 - (int)(w / p.bh_total);
+  it.bh = (int)(w % p.bh_total);
+  it.q0 = qt * kTM;
+  const int b = it.bh / p.heads, h = it.bh - b * p.heads;
+  it.kvz = b * p.kv_heads + h / p.group;
+  // loop bounds, examples/fmha.jl:65-76 (0-based tile indices here)
+  if (p.causal) {
+    it.mask_start = min((p.input_pos + it.q0) / kTN, p.seq_kv / kTN);
+    it.Tc = (min(p.input_pos + it.q0 + kTM, p.seq_kv) + kTN - 1) / kTN;
+  } else {
+    it.Tc = (p.seq_kv + kTN - 1) / kTN;
+    it.mask_start = p.seq_kv / kTN;
+  }
+  return true;
+}
 
 __global__ void __launch_bounds__(kThreads, 2)
     fmha_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -56,40 +83,24 @@ __global__ void __launch_bounds__(kThreads, 2)
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = smem;
-  unsigned char* sK = smem + kTileBytes;
+  unsigned char* sK = sQ + kQBufs * kTileBytes;
   unsigned char* sV = sK + kKStages * kTileBytes;
-  __shared__ __align__(8) uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages],
-      s_full, s_free, p_full, o_full;
+  __shared__ __align__(8) uint64_t q_full[kQBufs], q_empty[kQBufs], k_full[kKStages], k_empty[kKStages],
+      v_full[kVStages], v_empty[kVStages], s_full, s_free, p_full, o_full, o_free;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh = blockIdx.x;                           // batch*heads + head
-  const int qt = p.q_tiles - 1 - (int)blockIdx.y;      // heavy tiles first
-  const int b = bh / p.heads, h = bh - b * p.heads;
-  const int kvh = h / p.group;
-  const int q0 = qt * kTM;
-
-  // loop bounds, examples/fmha.jl:65-76 (0-based tile indices here)
-  int Tc, mask_start;
-  if (p.causal) {
-    mask_start = min((p.input_pos + q0) / kTN, p.seq_kv / kTN);
-    const int m_end = p.input_pos + q0 + kTM;
-    Tc = (min(m_end, p.seq_kv) + kTN - 1) / kTN;
-  } else {
-    Tc = (p.seq_kv + kTN - 1) / kTN;
-    mask_start = p.seq_kv / kTN;
-  }
-
   if (threadIdx.x == 0) {
     abort_s = 0;
-    mbar_init(&q_full, 1);
+    for (int s = 0; s < kQBufs; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
     for (int s = 0; s < kKStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     for (int s = 0; s < kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     mbar_init(&s_full, 1);
     mbar_init(&s_free, 4);
     mbar_init(&p_full, 4);
     mbar_init(&o_full, 1);
+    mbar_init(&o_free, 4);
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -105,39 +116,49 @@ __global__ void __launch_bounds__(kThreads, 2)
   const uint32_t tmem = tmem_base_s;
   volatile int* abort = &abort_s;
 
+  // All three roles walk the same item sequence; g counts this CTA's K/V tiles across items and indexes the
+  // K/V rings and the parity of the per-tile handshakes.
   if (warp == 0) {
     // ---- TMA producer (whole warp in lock step, one elected lane issues)
-    if (elect_one()) {
-      mbar_expect_tx(&q_full, kTileBytes);
-      tma_load_3d(sQ, &tmQ, 0, q0, bh, &q_full);
-    }
-    __syncwarp();
-    const int kvz = b * p.kv_heads + kvh;
-    for (int j = 0; j < Tc; ++j) {
-      const int ks = j % kKStages, vs = j % kVStages;
-      if (!CTB_WARP_WAIT(&k_empty[ks], ((j / kKStages) & 1) ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+    int g = 0;
+    Item it;
+    for (int i = 0; get_item(p, i, it); ++i) {
+      const int qb = i % kQBufs;
+      if (!CTB_WARP_WAIT(&q_empty[qb], ((i / kQBufs) & 1) ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
       if (elect_one()) {
-        mbar_expect_tx(&k_full[ks], kTileBytes);
-        tma_load_3d(sK + ks * kTileBytes, &tmK, 0, j * kTN, kvz, &k_full[ks]);
+        mbar_expect_tx(&q_full[qb], kTileBytes);
+        tma_load_3d(sQ + qb * kTileBytes, &tmQ, 0, it.q0, it.bh, &q_full[qb]);
       }
       __syncwarp();
-      if (!CTB_WARP_WAIT(&v_empty[vs], ((j / kVStages) & 1) ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
-      if (elect_one()) {
-        mbar_expect_tx(&v_full[vs], kTileBytes);
-        tma_load_3d(sV + vs * kTileBytes, &tmV, 0, j * kTN, kvz, &v_full[vs]);
+      bool ok = true;
+      for (int j = 0; j < it.Tc; ++j, ++g) {
+        const int ks = g % kKStages, vs = g % kVStages;
+        ok = CTB_WARP_WAIT(&k_empty[ks], ((g / kKStages) & 1) ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+        if (!ok) break;
+        if (elect_one()) {
+          mbar_expect_tx(&k_full[ks], kTileBytes);
+          tma_load_3d(sK + ks * kTileBytes, &tmK, 0, j * kTN, it.kvz, &k_full[ks]);
+        }
+        __syncwarp();
+        ok = CTB_WARP_WAIT(&v_empty[vs], ((g / kVStages) & 1) ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+        if (!ok) break;
+        if (elect_one()) {
+          mbar_expect_tx(&v_full[vs], kTileBytes);
+          tma_load_3d(sV + vs * kTileBytes, &tmV, 0, j * kTN, it.kvz, &v_full[vs]);
+        }
+        __syncwarp();
       }
-      __syncwarp();
+      if (!ok) break;
     }
   } else if (warp == 1) {
     // ---- MMA issuer (whole warp in lock step, one elected lane issues)
     constexpr uint32_t idesc_qk = make_idesc(FMT_F16, kTM, kTN, 0, 0);
     constexpr uint32_t idesc_pv = make_idesc(FMT_F16, kTM, kD, 0, /*V is MN-major*/ 1);
-    const uint32_t aQ = smem_u32(sQ);
-    auto issue_qk = [&](int j) -> bool {
-      const int ks = j % kKStages;
-      if (j == 0 && !CTB_WARP_WAIT(&k_full[ks], 0, status, DEV_TIMEOUT_TMA, abort)) return false;  // later tiles: caller waited
+    // S = Q*K^T for global tile gt (its K tile has landed, S is free); `last` frees the Q buffer afterwards
+    auto issue_qk = [&](int gt, int qb, bool last) {
       tc_fence_after();
-      const uint32_t aK = smem_u32(sK + ks * kTileBytes);
+      const int ks = gt % kKStages;
+      const uint32_t aQ = smem_u32(sQ + qb * kTileBytes), aK = smem_u32(sK + ks * kTileBytes);
       if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k)
@@ -145,165 +166,188 @@ __global__ void __launch_bounds__(kThreads, 2)
                      idesc_qk, k != 0);
         tc_commit(&k_empty[ks]);
         tc_commit(&s_full);
+        if (last) tc_commit(&q_empty[qb]);
       }
       __syncwarp();
-      return true;
     };
-    bool ok = CTB_WARP_WAIT(&q_full, 0, status, DEV_TIMEOUT_TMA, abort);
-    if (ok) ok = issue_qk(0);
-    for (int j = 0; ok && j < Tc; ++j) {
-      const int vs = j % kVStages;
-      // S(j) has been read into registers: the next scores can overwrite it while softmax(j) still runs
-      if (j + 1 < Tc) {
-        const int ks = (j + 1) % kKStages;  // the K tile landed long ago: take that wait off the critical path
-        if (!CTB_WARP_WAIT(&k_full[ks], ((j + 1) / kKStages) & 1, status, DEV_TIMEOUT_TMA, abort)) break;
-        if (!CTB_WARP_WAIT(&s_free, j & 1, status, DEV_TIMEOUT_SLOT, abort)) break;
-        ok = issue_qk(j + 1);
+    int g = 0;
+    Item it;
+    bool ok = true;
+    for (int i = 0; ok && get_item(p, i, it); ++i) {
+      const int qb = i % kQBufs;
+      ok = CTB_WARP_WAIT(&q_full[qb], (i / kQBufs) & 1, status, DEV_TIMEOUT_TMA, abort) &&
+           CTB_WARP_WAIT(&k_full[g % kKStages], (g / kKStages) & 1, status, DEV_TIMEOUT_TMA, abort);
+      // the softmax warps have pulled the previous item's last scores out of S
+      if (ok && g > 0) ok = CTB_WARP_WAIT(&s_free, (g - 1) & 1, status, DEV_TIMEOUT_SLOT, abort);
+      if (!ok) break;
+      issue_qk(g, qb, it.Tc == 1);
+      for (int j = 0; j < it.Tc; ++j) {
+        const int gj = g + j, vs = gj % kVStages;
+        if (j + 1 < it.Tc) {
+          // S(j) has been read into registers: the next scores can overwrite it while softmax(j) still runs
+          ok = CTB_WARP_WAIT(&k_full[(gj + 1) % kKStages], ((gj + 1) / kKStages) & 1, status, DEV_TIMEOUT_TMA, abort) &&
+               CTB_WARP_WAIT(&s_free, gj & 1, status, DEV_TIMEOUT_SLOT, abort);
+          if (!ok) break;
+          issue_qk(gj + 1, qb, j + 2 == it.Tc);
+        }
+        ok = CTB_WARP_WAIT(&v_full[vs], (gj / kVStages) & 1, status, DEV_TIMEOUT_TMA, abort);
+        // the first P*V of an item overwrites O: the previous item's epilogue must have read it
+        if (ok && j == 0 && i > 0) ok = CTB_WARP_WAIT(&o_free, (i - 1) & 1, status, DEV_TIMEOUT_SLOT, abort);
+        if (ok) ok = CTB_WARP_WAIT(&p_full, gj & 1, status, DEV_TIMEOUT_SLOT, abort);
         if (!ok) break;
-      }
-      if (!CTB_WARP_WAIT(&v_full[vs], (j / kVStages) & 1, status, DEV_TIMEOUT_TMA, abort)) break;
-      if (!CTB_WARP_WAIT(&p_full, j & 1, status, DEV_TIMEOUT_SLOT, abort)) break;
-      tc_fence_after();
-      const uint32_t aV = smem_u32(sV + vs * kTileBytes);
-      if (elect_one()) {
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + vs * kTileBytes);
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < kTN / 16; ++k)
-          mma_f16_ts(tmem + kColO, tmem + kColP + k * 8, make_sdesc_sw128(aV + k * 2048, 0, 1024), idesc_pv, (j | k) != 0);
-        tc_commit(&v_empty[vs]);
-        tc_commit(&o_full);
+          for (int k = 0; k < kTN / 16; ++k)
+            mma_f16_ts(tmem + kColO, tmem + kColP + k * 8, make_sdesc_sw128(aV + k * 2048, 0, 1024), idesc_pv, (j | k) != 0);
+          tc_commit(&v_empty[vs]);
+          tc_commit(&o_full);
+        }
+        __syncwarp();
       }
-      __syncwarp();
+      g += it.Tc;
     }
   } else {
+    // ---- softmax + epilogue: thread = query row = TMEM lane
     const int sub = warp & 3;
-    const int row = sub * 32 + lane;          // query row inside the tile = TMEM lane
-    const int qpos = q0 + row + p.input_pos;  // position used by the causal rule
+    const int row = sub * 32 + lane;
     const uint32_t trow = tmem + ((uint32_t)(sub * 32) << 16);
-    const int vis_last = p.causal ? min(qpos, p.seq_kv - 1) : p.seq_kv - 1;  // last visible key of this row
-    float m_ref = -INFINITY;  // exponent reference (scaled, log2 domain)
-    float l = 0.f;            // row sum relative to m_ref
+    int g = 0;
+    Item it;
     bool ok = true;
-    for (int j = 0; j < Tc; ++j) {
-      ok = mbar_wait(&s_full, j & 1, status, DEV_TIMEOUT_MMA, abort);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      const bool masked = j >= mask_start;
-      const int lim = vis_last - j * kTN;  // column i of this tile is visible iff i <= lim
-      // ---- the whole score row goes to registers in one go; S is then free for the next tile's Q*K^T
-      uint32_t sr[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(trow + kColS + c * 32, sr[c]);
-      tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free);
-      // ---- row maximum of the raw scores (four independent chains)
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-      if (masked) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, c * 32 + i + 0 <= lim ? __uint_as_float(sr[c][i + 0]) : -INFINITY);
-            mx1 = fmaxf(mx1, c * 32 + i + 1 <= lim ? __uint_as_float(sr[c][i + 1]) : -INFINITY);
-            mx2 = fmaxf(mx2, c * 32 + i + 2 <= lim ? __uint_as_float(sr[c][i + 2]) : -INFINITY);
-            mx3 = fmaxf(mx3, c * 32 + i + 3 <= lim ? __uint_as_float(sr[c][i + 3]) : -INFINITY);
-          }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx0 = fmaxf(mx0, __uint_as_float(sr[c][i + 0]));
-            mx1 = fmaxf(mx1, __uint_as_float(sr[c][i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(sr[c][i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(sr[c][i + 3]));
-          }
-      }
-      const float m_true = fmaxf(m_ref, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
-      // ---- move the exponent reference (and rescale O, l) only when the maximum grew by more than 2^8
-      const bool grow = m_true - m_ref > 8.0f || m_ref == -INFINITY;
-      if (j > 0) {  // PV(j-1) must have consumed P(j-1) (and, for a rescale, landed in O) before P(j) is written
-        ok = mbar_wait(&o_full, (j - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
+    for (int i = 0; ok && get_item(p, i, it); ++i) {
+      const int qpos = it.q0 + row + p.input_pos;  // position used by the causal rule
+      const int vis_last = p.causal ? min(qpos, p.seq_kv - 1) : p.seq_kv - 1;  // last visible key of this row
+      float m_ref = -INFINITY;  // exponent reference (scaled, log2 domain)
+      float l = 0.f;            // row sum relative to m_ref
+      for (int j = 0; j < it.Tc; ++j) {
+        const int gj = g + j;
+        ok = mbar_wait(&s_full, gj & 1, status, DEV_TIMEOUT_MMA, abort);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-      }
-      if (__any_sync(0xffffffffu, grow)) {
-        const float m_new = m_true == -INFINITY ? 0.f : m_true;  // fully masked so far: keep everything zero
-        const float alpha = ex2_approx_ftz(m_ref - m_new);       // 0 on the first tile
-        l *= alpha;
-        m_ref = m_new;
-        if (j > 0) {  // O holds the sum of the previous tiles
+        const bool masked = j >= it.mask_start;
+        const int lim = vis_last - j * kTN;  // column i of this tile is visible iff i <= lim
+        // ---- the whole score row goes to registers in one go; S is then free for the next tile's Q*K^T
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(trow + kColS + c * 32, sr[c]);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free);
+        // ---- row maximum of the raw scores (four independent chains)
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        if (masked) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int k = 0; k < 32; k += 4) {
+              mx0 = fmaxf(mx0, c * 32 + k + 0 <= lim ? __uint_as_float(sr[c][k + 0]) : -INFINITY);
+              mx1 = fmaxf(mx1, c * 32 + k + 1 <= lim ? __uint_as_float(sr[c][k + 1]) : -INFINITY);
+              mx2 = fmaxf(mx2, c * 32 + k + 2 <= lim ? __uint_as_float(sr[c][k + 2]) : -INFINITY);
+              mx3 = fmaxf(mx3, c * 32 + k + 3 <= lim ? __uint_as_float(sr[c][k + 3]) : -INFINITY);
+            }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int k = 0; k < 32; k += 4) {
+              mx0 = fmaxf(mx0, __uint_as_float(sr[c][k + 0]));
+              mx1 = fmaxf(mx1, __uint_as_float(sr[c][k + 1]));
+              mx2 = fmaxf(mx2, __uint_as_float(sr[c][k + 2]));
+              mx3 = fmaxf(mx3, __uint_as_float(sr[c][k + 3]));
+            }
+        }
+        const float m_true = fmaxf(m_ref, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2);
+        // ---- move the exponent reference (and rescale O, l) only when the maximum grew by more than 2^8
+        const bool grow = m_true - m_ref > 8.0f || m_ref == -INFINITY;
+        if (j > 0) {  // PV(j-1) must have consumed P(j-1) (and, for a rescale, landed in O) before P(j) is written
+          ok = mbar_wait(&o_full, (gj - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (__any_sync(0xffffffffu, grow)) {
+          const float m_new = m_true == -INFINITY ? 0.f : m_true;  // fully masked so far: keep everything zero
+          const float alpha = ex2_approx_ftz(m_ref - m_new);       // 0 on the first tile
+          l *= alpha;
+          m_ref = m_new;
+          if (j > 0) {  // O holds the sum of the previous tiles
 #pragma unroll 1
-          for (int c = 0; c < kD / 16; ++c) {
-            uint32_t t[16];
-            tmem_ld16(trow + kColO + c * 16, t);
-            tc_wait_ld();
+            for (int c = 0; c < kD / 16; ++c) {
+              uint32_t t[16];
+              tmem_ld16(trow + kColO + c * 16, t);
+              tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
-            tmem_st16(trow + kColO + c * 16, t);
+              for (int k = 0; k < 16; ++k) t[k] = __float_as_uint(__uint_as_float(t[k]) * alpha);
+              tmem_st16(trow + kColO + c * 16, t);
+            }
           }
         }
-      }
-      // ---- p = exp2(s*scale - m_ref), row sum, P -> TMEM as packed f16
-      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-      const float nm = -m_ref;
+        // ---- p = exp2(s*scale - m_ref), row sum, P -> TMEM as packed f16
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        const float nm = -m_ref;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          float p0 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][i + 0]), p.scale_log2, nm));
-          float p1 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][i + 1]), p.scale_log2, nm));
-          float p2 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][i + 2]), p.scale_log2, nm));
-          float p3 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][i + 3]), p.scale_log2, nm));
-          if (masked) {
-            if (c * 32 + i + 0 > lim) p0 = 0.f;
-            if (c * 32 + i + 1 > lim) p1 = 0.f;
-            if (c * 32 + i + 2 > lim) p2 = 0.f;
-            if (c * 32 + i + 3 > lim) p3 = 0.f;
+          for (int k = 0; k < 32; k += 4) {
+            float p0 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][k + 0]), p.scale_log2, nm));
+            float p1 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][k + 1]), p.scale_log2, nm));
+            float p2 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][k + 2]), p.scale_log2, nm));
+            float p3 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c][k + 3]), p.scale_log2, nm));
+            if (masked) {
+              if (c * 32 + k + 0 > lim) p0 = 0.f;
+              if (c * 32 + k + 1 > lim) p1 = 0.f;
+              if (c * 32 + k + 2 > lim) p2 = 0.f;
+              if (c * 32 + k + 3 > lim) p3 = 0.f;
+            }
+            s0 += p0; s1 += p1; s2 += p2; s3 += p3;
+            pk[(k >> 1) + 0] = pack_f16x2(p0, p1);
+            pk[(k >> 1) + 1] = pack_f16x2(p2, p3);
           }
-          s0 += p0; s1 += p1; s2 += p2; s3 += p3;
-          pk[(i >> 1) + 0] = pack_f16x2(p0, p1);
-          pk[(i >> 1) + 1] = pack_f16x2(p2, p3);
+          tmem_st16(trow + kColP + c * 16, pk);
         }
-        tmem_st16(trow + kColP + c * 16, pk);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full);
+        l += (s0 + s1) + (s2 + s3);
       }
-      tc_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full);
-      l += (s0 + s1) + (s2 + s3);
-    }
-    if (ok) {
-      ok = mbar_wait(&o_full, (Tc - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
+      if (!ok) break;
+      g += it.Tc;
+      // ---- epilogue of the item: O / l -> f16 -> global, then O is free for the next item
+      ok = mbar_wait(&o_full, (g - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
       ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
+      if (!ok) break;
       tc_fence_after();
       const float inv = rcp_approx_ftz(l);
-      const bool store = q0 + row < p.seq_q;
-      uint4* dst = reinterpret_cast<uint4*>(Out + ((long long)bh * p.seq_q + q0 + row) * kD);
+      const bool store = it.q0 + row < p.seq_q;
+      uint4* dst = reinterpret_cast<uint4*>(Out + ((long long)it.bh * p.seq_q + it.q0 + row) * kD);
 #pragma unroll
       for (int c = 0; c < kD / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(trow + kColO + c * 32, r);
         tc_wait_ld();
+        if (c == kD / 32 - 1) {  // everything is in registers: the next item may overwrite O
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_free);
+        }
         if (store) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int k = 0; k < 4; ++k) {
             uint4 v;
-            v.x = pack_f16x2(__uint_as_float(r[i * 8 + 0]) * inv, __uint_as_float(r[i * 8 + 1]) * inv);
-            v.y = pack_f16x2(__uint_as_float(r[i * 8 + 2]) * inv, __uint_as_float(r[i * 8 + 3]) * inv);
-            v.z = pack_f16x2(__uint_as_float(r[i * 8 + 4]) * inv, __uint_as_float(r[i * 8 + 5]) * inv);
-            v.w = pack_f16x2(__uint_as_float(r[i * 8 + 6]) * inv, __uint_as_float(r[i * 8 + 7]) * inv);
-            dst[c * 4 + i] = v;
+            v.x = pack_f16x2(__uint_as_float(r[k * 8 + 0]) * inv, __uint_as_float(r[k * 8 + 1]) * inv);
+            v.y = pack_f16x2(__uint_as_float(r[k * 8 + 2]) * inv, __uint_as_float(r[k * 8 + 3]) * inv);
+            v.z = pack_f16x2(__uint_as_float(r[k * 8 + 4]) * inv, __uint_as_float(r[k * 8 + 5]) * inv);
+            v.w = pack_f16x2(__uint_as_float(r[k * 8 + 6]) * inv, __uint_as_float(r[k * 8 + 7]) * inv);
+            dst[c * 4 + k] = v;
           }
         }
       }
-      tc_fence_before();
     }
   }
   tc_fence_before();
@@ -358,10 +402,14 @@ extern "C" int ctb_fmha_fwd(ctb_ctx* ctx, void* stream, const void* Q, const voi
   p.group = query_group_size; p.batch = (int)batch; p.input_pos = input_pos; p.causal = causal ? 1 : 0;
   p.scale_log2 = qk_scale * 1.4426950408889634f;
   p.q_tiles = (int)((seq_q + kTM - 1) / kTM);
-  const size_t smem = (size_t)(1 + kKStages + kVStages) * kTileBytes + 1024;
+  p.bh_total = (int)(heads * batch);
+  const long long items = (long long)p.q_tiles * p.bh_total;
+  if (items > INT32_MAX) return fail(CTB_UNSUPPORTED, "ctb_fmha_fwd: too many work items");
+  p.items = (int)items;
+  const size_t smem = (size_t)(kQBufs + kKStages + kVStages) * kTileBytes + 1024;
   cudaError_t e = cudaFuncSetAttribute(fmha_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e, "ctb_fmha_fwd: shared memory opt-in");
-  dim3 grid((unsigned)(heads * batch), (unsigned)p.q_tiles);
+  const int grid = (int)std::min<long long>(items, 2LL * ctx->sm_count);  // two persistent CTAs per SM
   fmha_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, (__half*)Out, p,
                                                                          ctx->dev_status);
   CTB_CHECK_LAUNCH("ctb_fmha_fwd launch");
