@@ -16,6 +16,9 @@
 // final reduce (layer_norm_bwd_dwdb, :186-205): column sums of the partials.
 #include <cooperative_groups.h>
 
+#include <algorithm>
+#include <mutex>
+
 #include "ctx.h"
 #include "ptx.cuh"
 
@@ -520,3 +523,123 @@ int ctb_layernorm_bwd_dwdb(ctb_ctx* ctx, void* stream, const float* DW, const fl
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- allocation-free backward
+// Some hosts of this library may not allocate device memory on the path that
+// runs the backward pass: a plug-in that lives inside another runtime's memory
+// plan, a real-time loop that may not block in the driver, code that runs
+// while a stream is being captured.  For them the partial dW/dB buffers of the
+// backward pass live in a fixed array inside the library image instead of in
+// memory the caller (or the library) would have to cudaMalloc.
+namespace {
+
+constexpr int kStaticGroups = 64;     // GROUP_SIZE_M of the built-in scratch
+constexpr int kStaticMaxN = 8192;     // widest row the built-in scratch can hold
+// [0] = partial dW, [1] = partial dB, each (N, kStaticGroups) with N <= kStaticMaxN: 4 MiB per device, held
+// from the moment the library is loaded on a device until the process exits.
+static __device__ __align__(256) float g_ln_static_partials[2 * kStaticGroups * kStaticMaxN];
+static __device__ int g_ln_static_status;  // bounded-wait codes of the static entry point (see DevStatus)
+
+struct StaticDev {
+  bool ready;
+  float* partials;  // DEVICE address of g_ln_static_partials on this device
+  int* status;
+  int sm_count;
+};
+constexpr int kMaxDevices = 64;
+StaticDev g_static_dev[kMaxDevices];
+std::mutex g_static_mu;
+
+// One-time set-up per device.  In host code the name of a __device__ array is only a handle: the address a
+// kernel can use has to be asked for with cudaGetSymbolAddress while that device is current.
+int static_setup(int dev, StaticDev** out) {
+  if (dev < 0 || dev >= kMaxDevices) return fail(CTB_UNSUPPORTED, "ctb_layernorm_bwd_static: device %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  StaticDev& d = g_static_dev[dev];
+  if (!d.ready) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_ln_static_partials);
+    if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static: cudaGetSymbolAddress(partials)");
+    d.partials = static_cast<float*>(p);
+    e = cudaGetSymbolAddress(&p, g_ln_static_status);
+    if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static: cudaGetSymbolAddress(status)");
+    d.status = static_cast<int*>(p);
+    e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static: cudaDeviceGetAttribute");
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static: cudaDeviceGetAttribute");
+    if (major != 10) return fail(CTB_NO_DEVICE, "ctb_layernorm_bwd_static: device %d is not sm_100", dev);
+    d.ready = true;
+  }
+  *out = &d;
+  return CTB_OK;
+}
+
+template <int NV>
+int launch_bwd_static(const StaticDev& d, cudaStream_t st, float* DX, const float* DY, float* DW, float* DB,
+                      const float* X, const float* W, const float* Mean, const float* Rstd, int N, int M,
+                      long long ldx, long long lddy, long long lddx) {
+  const int G = kStaticGroups;
+  const int row_stride = (N * 4 + 127) & ~127;
+  const size_t smem = (size_t)kBwdStages * 2 * row_stride;
+  auto k = ln_bwd_kernel<NV>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static: shared memory opt-in");
+  int per_sm = (int)((size_t)220 * 1024 / (smem + 1024));
+  per_sm = std::max(1, std::min(per_sm, 2048 / kBwdThreads));
+  int C = 8;
+  while (C > 1 && ((long long)G * C > (long long)d.sm_count * per_sm || (long long)G * C * 2 > M)) C >>= 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(G * C);
+  cfg.blockDim = dim3(kBwdThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = C;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, k, DX, DY, DW, DB, X, W, Mean, Rstd, N, M, ldx, lddy, lddx, G, row_stride, d.status);
+  if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static launch");
+  return CTB_OK;
+}
+
+}  // namespace
+
+extern "C" int ctb_layernorm_bwd_static(void* stream, float* DX, const float* DY, const float* X, const float* W,
+                                        const float* Mean, const float* Rstd, float* FINAL_DW, float* FINAL_DB,
+                                        int64_t N, int64_t M, int64_t ldx, int64_t lddy, int64_t lddx) {
+  if (N <= 0 || M <= 0 || M > INT32_MAX)
+    return fail(CTB_BAD_ARG, "ctb_layernorm_bwd_static: bad shape N=%lld M=%lld", (long long)N, (long long)M);
+  if (N > kStaticMaxN)
+    return fail(CTB_UNSUPPORTED, "ctb_layernorm_bwd_static: N=%lld exceeds the built-in scratch (at most %d columns); "
+                "use ctb_layernorm_bwd_dx_partial_dwdb with caller-provided partial buffers", (long long)N, kStaticMaxN);
+  if (ldx < N || lddy < N || lddx < N) return fail(CTB_BAD_ARG, "ctb_layernorm_bwd_static: leading dimension smaller than N");
+  if (N % 4 || ldx % 4 || lddy % 4 || lddx % 4 || !aligned16(X) || !aligned16(DY) || !aligned16(DX) || !aligned16(W))
+    return fail(CTB_BAD_ALIGN, "ctb_layernorm_bwd_static: N and the leading dimensions must be multiples of 4 and "
+                "X, DY, DX, W 16-byte aligned");
+  CTB_CHECK_DEV(DX); CTB_CHECK_DEV(DY); CTB_CHECK_DEV(X); CTB_CHECK_DEV(W); CTB_CHECK_DEV(Mean); CTB_CHECK_DEV(Rstd);
+  CTB_CHECK_DEV(FINAL_DW); CTB_CHECK_DEV(FINAL_DB);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static: cudaGetDevice");
+  StaticDev* d = nullptr;
+  int r = static_setup(dev, &d);
+  if (r) return r;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* DW = d->partials;
+  float* DB = d->partials + (size_t)kStaticGroups * kStaticMaxN;
+  const int n = (int)N, m = (int)M;
+  const int nv = (n / 4 + kBwdThreads - 1) / kBwdThreads;
+  if (nv <= 1) r = launch_bwd_static<1>(*d, st, DX, DY, DW, DB, X, W, Mean, Rstd, n, m, ldx, lddy, lddx);
+  else if (nv <= 2) r = launch_bwd_static<2>(*d, st, DX, DY, DW, DB, X, W, Mean, Rstd, n, m, ldx, lddy, lddx);
+  else r = launch_bwd_static<4>(*d, st, DX, DY, DW, DB, X, W, Mean, Rstd, n, m, ldx, lddy, lddx);
+  if (r) return r;
+  ln_bwd_reduce_kernel<<<(n + kRedCols - 1) / kRedCols, kRedCols * kRedSlices, 0, st>>>(DW, DB, FINAL_DW, FINAL_DB, n,
+                                                                                      kStaticGroups);
+  CTB_CHECK_LAUNCH("ctb_layernorm_bwd_static reduce launch");
+  return CTB_OK;
+}

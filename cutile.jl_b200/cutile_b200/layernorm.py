@@ -42,3 +42,25 @@ def layer_norm_bwd_dwdb(DW, DB, FINAL_DW, FINAL_DB, TILE_M, TILE_N):
     G, N = DW.shape
     _lib.check(_lib.lib.ctb_layernorm_bwd_dwdb(ctx, stream, ptr(DW), ptr(DB), ptr(FINAL_DW), ptr(FINAL_DB), N, G,
                                                int(TILE_M), int(TILE_N)))
+
+
+def layer_norm_bwd_static(DX, DY, X, W, Mean, Rstd, FINAL_DW, FINAL_DB):
+    """Backward pass for callers that must not allocate device memory where it runs (inside another runtime's
+    memory plan, in a loop that may not block in the allocator, while a stream is being captured).  Same result
+    as layer_norm_bwd_dx_partial_dwdb + layer_norm_bwd_dwdb with GROUP_SIZE_M = 64, but the partial buffers
+    live in a fixed array inside the library (N <= 8192) and no context is created.  No counterpart in the
+    reference.  Calls share that array: keep them on one stream."""
+    import ctypes as C
+    import torch
+    from ._util import ptr, rows
+    if not X.is_cuda:
+        raise _lib.CtbError(_lib.BAD_ARG, "expected CUDA tensors")
+    ldx, M, N = rows(X, "X")
+    lddy, _, _ = rows(DY, "DY")
+    lddx, _, _ = rows(DX, "DX")
+    if DY.shape != X.shape or DX.shape != X.shape:
+        raise _lib.CtbError(_lib.BAD_ARG, "layer_norm_bwd_static: DX/DY must have the shape of X")
+    with torch.cuda.device(X.device):
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _lib.check(_lib.lib.ctb_layernorm_bwd_static(stream, ptr(DX), ptr(DY), ptr(X), ptr(W), ptr(Mean), ptr(Rstd),
+                                                     ptr(FINAL_DW), ptr(FINAL_DB), N, M, ldx, lddy, lddx))

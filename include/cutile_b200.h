@@ -175,6 +175,30 @@ int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, 
                 const void* topk_weights, const void* topk_ids, int ids_bits, void* out, int64_t T, int64_t H,
                 int64_t I, int64_t E, int64_t topk, int tile_m, int tile_n, int tile_k);
 
+/* ---- LayerNorm backward without any allocation --------------------------------- */
+/* No counterpart in the reference.  For callers that cannot obtain device memory
+ * at the point where the backward pass runs (a plug-in inside another runtime's
+ * memory plan, a latency-critical loop that must not block in the allocator, a
+ * section of code that is being recorded into a stream capture) this fuses
+ * layer_norm_bwd_dx_partial_dwdb and layer_norm_bwd_dwdb with GROUP_SIZE_M = 64
+ * and keeps the (N, 64) partial dW/dB buffers in a fixed 4 MiB array inside the
+ * library image, so neither the caller nor the library calls cudaMalloc/cudaFree
+ * (nor any allocating library routine) and no context object is needed.
+ *  - Limit: N <= 8192 (the size of the built-in scratch); larger N returns
+ *    CTB_UNSUPPORTED.  N and the leading dimensions must be multiples of 4 and
+ *    X, DY, DX, W 16-byte aligned (CTB_BAD_ALIGN otherwise).
+ *  - Works on the current device.  The first call on each device looks up the
+ *    device address of the built-in array; make that first call before starting
+ *    any stream capture.
+ *  - The scratch is shared by every call on the device and keeps the previous
+ *    call's contents.  Nothing in it has to start at zero (each partial column is
+ *    fully rewritten), but two calls that overlap on the GPU (different streams,
+ *    or one still running when the next starts on another stream) race on it:
+ *    keep calls on one stream or order them with events. */
+int ctb_layernorm_bwd_static(void* stream, float* DX, const float* DY, const float* X, const float* W,
+                             const float* Mean, const float* Rstd, float* FINAL_DW, float* FINAL_DB, int64_t N,
+                             int64_t M, int64_t ldx, int64_t lddy, int64_t lddx);
+
 #ifdef __cplusplus
 }
 #endif
