@@ -450,12 +450,22 @@ def device_time(torch, dist, fn_steps, steps, warmup, graph=True):
     t1 = time.time()
     if dist is not None:
         dist.barrier()
-    ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = max_over_ranks(e0.elapsed_time(e1), torch, dist, "cuda")
     return ms, t0, t1
+
+
+def max_over_ranks(ms, torch, dist, device):
+    """The job's time is the slowest rank's (every rank must hold the same figure afterwards)."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return float(ms)
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def aggregate_value(work_per_rank, world, ms_per_step, unit):
+    """Whole-job throughput: the units all ranks processed divided by the (max-over-ranks) step time."""
+    return work_per_rank * world / (ms_per_step * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
 
 
 def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu, sampler=None):
@@ -470,7 +480,7 @@ def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu
     ctb.check_device_status(torch.cuda.current_device())
     per = ms / steps
     scale = 1e9 if w.unit == "GB/s" else 1e12
-    value = w.work() * world / (per * 1e-3) / scale
+    value = aggregate_value(w.work(), world, per, w.unit)
     res = dict(name=w.name, metric=w.metric, unit=w.unit, value=value, ms_per_step=per, work_per_step=w.work(),
                workload=w.describe(), l2="rotating %d input/output sets (%.0f MB total, L2 is 126 MB)" %
                (nsets, nsets * nbytes / 1e6), t0=t0, t1=t1, launches=w.launches_per_step * steps,

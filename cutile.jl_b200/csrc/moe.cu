@@ -1,8 +1,8 @@
 // Mixture-of-experts FFN for sm_100a (counterparts of examples/moe.jl):
-//   moe_router_kernel   logits = X^T * W_r in f32 (fixed ascending-k order so a
-//                       CPU float32 loop reproduces it bit for bit), top-k by
-//                       value with ties to the smallest index, softmax-renormalised
-//                       gates stored as f16.  (The reference example draws its ids
+//   moe_router_kernel   logits = X^T * W_r in f32 in a fixed, warp-shaped summation
+//                       order that a CPU float32 loop reproduces bit for bit,
+//                       top-k by value with ties to the smallest index,
+//                       softmax-renormalised gates stored as f16.  (The reference example draws its ids
 //                       at random, examples/moe.jl:323-332; the router belongs to
 //                       the benchmark configuration.)
 //   moe_align_kernel    device version of moe_align_tile_size (:142-183): stable
@@ -32,79 +32,80 @@ using namespace ctb_internal;
 namespace {
 
 // ------------------------------------------------------------------ router
-// One warp per token, lane = expert (experts lane, lane+32, ...).  The token rows
-// and W_r are staged in shared memory as f32 (all of W_r at once when it fits,
-// else in K-chunks of KC); expert rows are padded by 16 bytes so that the 32
-// lanes read 32 different rows without bank conflicts.  Each (token, expert)
-// logit is one chain of fused multiply-adds in ascending k, which is what makes
-// the result reproducible bit for bit.
-constexpr int kRouterWarps = 8;
+// One warp per token.  The accumulation order of a logit is fixed and shaped
+// like the warp: lane l owns the hidden indices k with (k mod 256) in
+// [8l, 8l+8) and adds their products x[k]*w[e][k] in ascending k into one f32
+// partial sum (a fused multiply-add chain; every f16*f16 product is exact in
+// f32); the 32 partials are then combined by a butterfly, v += v[lane ^ o] for
+// o = 16, 8, 4, 2, 1.  The CPU oracle performs the same operations in the same
+// order, so logits and therefore top-k ids agree bit for bit.  Every load is a
+// coalesced 16-byte access; W_r (64 KB at 32 experts x 1024) stays in L1/L2.
+constexpr int kRouterWarps = 4;
 constexpr int kRouterThreads = kRouterWarps * 32;
-constexpr int kMaxEPL = 8;  // experts per lane -> E <= 256
+constexpr int kMaxRouterE = 256;
 
-__device__ __forceinline__ float4 cvt4(uint2 u) {
-  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
-  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
-  return make_float4(a.x, a.y, b.x, b.y);
+__device__ __forceinline__ void cvt8(const uint4& u, float* f) {
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __half22float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
 }
 
-template <int EPL>
 __global__ void __launch_bounds__(kRouterThreads)
     moe_router_kernel(const __half* __restrict__ X, const __half* __restrict__ Wr, int* __restrict__ ids,
-                      __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk,
-                      int KC) {
-  extern __shared__ __align__(16) float rsm[];
-  const int ROW = KC + 4;                            // floats per staged expert row
-  float* sw = rsm;                                   // [E][ROW]
-  float* sx = rsm + (size_t)E * ROW;                 // [kRouterWarps][H]
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int t = min((int)blockIdx.x * kRouterWarps + warp, T - 1);  // surplus warps redo the last token, write nothing
-  const bool live = (int)blockIdx.x * kRouterWarps + warp < T;
-  {  // this warp's token row -> f32 in shared memory (H % 8 == 0)
-    const uint2* x = reinterpret_cast<const uint2*>(X + (long long)t * H);
-    float4* dst = reinterpret_cast<float4*>(sx + (size_t)warp * H);
-    for (int i = lane; i < H / 4; i += 32) dst[i] = cvt4(x[i]);
-  }
-  const int vpr = KC / 4;  // 4-element groups per staged row
-  const int ngrp = E * vpr;
-  float acc[EPL];
+                      __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouterWarps + warp;
+  if (t >= T) return;
+  const __half* x = X + (long long)t * H;
+  const int nchunk = (H + 255) / 256;
+  constexpr int EPL = kMaxRouterE / 32;
+  float mine[EPL];  // logits of experts lane, lane+32, ...
 #pragma unroll
-  for (int i = 0; i < EPL; ++i) acc[i] = 0.f;
-  for (int k0 = 0; k0 < H; k0 += KC) {
-    __syncthreads();  // everyone is done with the previous chunk
-#pragma unroll 8
-    for (int idx = tid; idx < ngrp; idx += kRouterThreads) {  // independent loads: their latencies overlap
-      const int e = idx / vpr, v = idx - e * vpr;
-      const int k = k0 + v * 4;
-      float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (k < H) w = cvt4(*reinterpret_cast<const uint2*>(Wr + (long long)e * H + k));
-      *reinterpret_cast<float4*>(sw + e * ROW + v * 4) = w;
+  for (int i = 0; i < EPL; ++i) mine[i] = -INFINITY;
+  for (int e0 = 0; e0 < E; e0 += 32) {
+    float acc[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+    for (int c = 0; c < nchunk; ++c) {
+      const int k = c * 256 + lane * 8;
+      float xf[8];
+      if (k < H) cvt8(*reinterpret_cast<const uint4*>(x + k), xf);  // H % 8 == 0
+      else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xf[j] = 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        float wf[8];
+        if (k < H && e0 + e < E) cvt8(*reinterpret_cast<const uint4*>(Wr + (long long)(e0 + e) * H + k), wf);
+        else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) wf[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[e] = fmaf(xf[j], wf[j], acc[e]);  // ascending k inside the lane
+      }
     }
-    __syncthreads();
-    const int klim = min(KC, H - k0);
-    const float* xr = sx + (size_t)warp * H + k0;
-#pragma unroll 4
-    for (int kk = 0; kk < klim; kk += 4) {
-      const float4 xv = *reinterpret_cast<const float4*>(xr + kk);
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        const int e = min(lane + 32 * i, E - 1);  // lanes past E recompute the last expert and are ignored below
-        const float4 wv = *reinterpret_cast<const float4*>(sw + e * ROW + kk);
-        acc[i] = fmaf(xv.x, wv.x, acc[i]);  // ascending k
-        acc[i] = fmaf(xv.y, wv.y, acc[i]);
-        acc[i] = fmaf(xv.z, wv.z, acc[i]);
-        acc[i] = fmaf(xv.w, wv.w, acc[i]);
+    for (int e = 0; e < 32; ++e) {
+      float v = acc[e];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == e && e0 + e < E) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i)
+          if (i == e0 / 32) mine[i] = v;
       }
     }
   }
-  if (!live) return;
-#pragma unroll
-  for (int i = 0; i < EPL; ++i)
-    if (lane + 32 * i >= E) acc[i] = -INFINITY;
   if (logits_out) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
-      if (lane + 32 * i < E) logits_out[(long long)t * E + lane + 32 * i] = acc[i];
+      if (lane + 32 * i < E) logits_out[(long long)t * E + lane + 32 * i] = mine[i];
   }
   float mysel = 0.f, top = 0.f, sum = 0.f;  // lane s keeps the s-th selected logit
   int myid = 0;
@@ -114,8 +115,8 @@ __global__ void __launch_bounds__(kRouterThreads)
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
       const int e = lane + 32 * i;
-      if (e < E && (acc[i] > bv || (acc[i] == bv && e < bi))) {
-        bv = acc[i];
+      if (e < E && (mine[i] > bv || (mine[i] == bv && e < bi))) {
+        bv = mine[i];
         bi = e;
       }
     }
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(kRouterThreads)
     }
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
-      if (lane + 32 * i == bi) acc[i] = -INFINITY;
+      if (lane + 32 * i == bi) mine[i] = -INFINITY;
   }
   if (lane < topk) {
     ids[(long long)lane * T + t] = myid + 1;
@@ -439,20 +440,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         __syncwarp();
       }
     } else if (warp < 6) {
-      // ---- token-row gather into the swizzled B operand (cp.async, completion arrives on b_full)
-      const int g = threadIdx.x - 64;  // 0..127 = slot inside the block
-      const uint32_t roff = (uint32_t)(g >> 3) * 1024 + (uint32_t)(g & 7) * 128;
+      // ---- token-row gather into the swizzled B operand (cp.async, completion arrives on b_full).
+      // Thread t copies the 16-byte chunks t, t+128, ... of the (slots x 8 chunks) tile, so one warp
+      // instruction moves four whole 128-byte row segments (full cache lines, conflict-free stores).
+      const int g = threadIdx.x - 64;  // 0..127
+      const int cch = g & 7;           // chunk inside the 128-byte row segment (the same for every copy of the thread)
       for (int n = 0; n < rn; ++n) {
         if (meta_e[n] < 0) continue;
         const int nmma = max(16, (meta_ext[n] + 15) & ~15);
         const int it = blockIdx.x + (r0 + n) * gridDim.x;
         const int bm = it / p.n_tiles;
-        const __half* src = nullptr;
-        if (g < p.tile_m) {
-          const int id = p.sorted_ids[(long long)bm * p.tile_m + g];
-          if (id >= 1 && id <= p.total) {
-            const int tok = (id - 1) / p.replicas;  // cld(id, replicas) - 1
-            if (tok < p.a_rows) src = p.A + (long long)tok * p.lda;
+        const __half* src[8];  // row q*16 + g/8 of the block, q = 0..7
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int r = q * 16 + (g >> 3);
+          src[q] = nullptr;
+          if (r < p.tile_m && r < nmma) {
+            const int id = p.sorted_ids[(long long)bm * p.tile_m + r];
+            if (id >= 1 && id <= p.total) {
+              const int tok = (id - 1) / p.replicas;  // cld(id, replicas) - 1
+              if (tok < p.a_rows) src[q] = p.A + (long long)tok * p.lda + cch * 8;
+            }
           }
         }
         bool ok = true;
@@ -460,13 +468,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           ok = mbar_wait(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          if (g < nmma) {
-            unsigned char* dst = smem + (size_t)stage * p.stage_bytes + wbytes + roff;
+          unsigned char* base = smem + (size_t)stage * p.stage_bytes + wbytes;
+          const int k = kb * kBK + cch * 8;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const int k = kb * kBK + c * 8;
-              const bool valid = src && k < p.K;
-              cp_async16(dst + ((c ^ (g & 7)) << 4), valid ? (const void*)(src + k) : (const void*)p.A, valid ? 16u : 0u);
+          for (int q = 0; q < 8; ++q) {
+            const int r = q * 16 + (g >> 3);
+            if (r < nmma) {
+              const bool valid = src[q] != nullptr && k < p.K;
+              cp_async16(base + (r >> 3) * 1024 + (r & 7) * 128 + ((cch ^ (r & 7)) << 4),
+                         valid ? (const void*)(src[q] + kb * kBK) : (const void*)p.A, valid ? 16u : 0u);
             }
           }
           cp_async_arrive_noinc(&b_full[stage]);  // fires when this thread's copies have landed
@@ -666,36 +676,15 @@ int ctb_moe_router(ctb_ctx* ctx, void* stream, const void* hidden, const void* W
                    void* topk_weights, float* logits, int64_t T, int64_t H, int64_t E, int topk) {
   CTB_CHECK_CTX(ctx);
   if (T < 0 || H <= 0 || E <= 0 || topk <= 0) return fail(CTB_BAD_ARG, "ctb_moe_router: non-positive dimension");
-  if (E > 32 * kMaxEPL) return fail(CTB_UNSUPPORTED, "ctb_moe_router: at most %d experts", 32 * kMaxEPL);
+  if (E > kMaxRouterE) return fail(CTB_UNSUPPORTED, "ctb_moe_router: at most %d experts", kMaxRouterE);
   if (topk > 32 || topk > E) return fail(CTB_UNSUPPORTED, "ctb_moe_router: topk must be <= min(32, E)");
   if (H % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_router: hidden size must be a multiple of 8");
   if (T == 0) return CTB_OK;
   CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(W_r); CTB_CHECK_DEV(topk_ids); CTB_CHECK_DEV(topk_weights);
   if ((uintptr_t)hidden % 16 || (uintptr_t)W_r % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_router: 16-byte alignment");
   const int grid = (int)((T + kRouterWarps - 1) / kRouterWarps);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // stage as much of W_r as fits beside the token rows (K-chunk KC, a multiple of 64)
-  const size_t budget = 200 * 1024, xbytes = (size_t)kRouterWarps * H * sizeof(float);
-  if (xbytes + (size_t)E * (64 + 4) * sizeof(float) > budget)
-    return fail(CTB_UNSUPPORTED, "ctb_moe_router: hidden size %lld too large", (long long)H);
-  int KC = (int)(((budget - xbytes) / ((size_t)E * sizeof(float)) - 4) / 64 * 64);
-  KC = (int)std::min<int64_t>(KC, (H + 63) / 64 * 64);
-  const size_t smem = xbytes + (size_t)E * (KC + 4) * sizeof(float);
-  const int epl = (int)((E + 31) / 32);
-#define CTB_ROUTER(EPL)                                                                                     \
-  {                                                                                                         \
-    cudaError_t e = cudaFuncSetAttribute(moe_router_kernel<EPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                         (int)smem);                                                        \
-    if (e != cudaSuccess) return cuda_fail(e, "ctb_moe_router: shared memory opt-in");                      \
-    moe_router_kernel<EPL><<<grid, kRouterThreads, smem, st>>>((const __half*)hidden, (const __half*)W_r,    \
-                                                               topk_ids, (__half*)topk_weights, logits,     \
-                                                               (int)T, (int)H, (int)E, topk, KC);           \
-  }
-  if (epl <= 1) CTB_ROUTER(1)
-  else if (epl <= 2) CTB_ROUTER(2)
-  else if (epl <= 4) CTB_ROUTER(4)
-  else CTB_ROUTER(8)
-#undef CTB_ROUTER
+  moe_router_kernel<<<grid, kRouterThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk);
   CTB_CHECK_LAUNCH("ctb_moe_router launch");
   return CTB_OK;
 }

@@ -120,19 +120,30 @@ def fmha(Q, K, V, qk_scale=None, causal=False, input_pos=0, dtype=np.float64):
 # ---------------------------------------------------------------------------- MoE
 def moe_router(X, Wr, topk):
     """Router of the benchmark configuration (the reference draws ids with
-    ``randperm``, ``examples/moe.jl:323-332``, so this step is specified here):
-    logits[t,e] = sum_k X[t,k]*Wr[e,k] accumulated in float32 in ascending k (each
-    f16*f16 product is exact in float32, so a fused multiply-add and
-    multiply-then-add agree); top-k by value, ties to the smallest expert index
-    (the reference's arg-reduction rule, ``src/language/operations.jl:1675-1677``);
+    ``randperm``, ``examples/moe.jl:323-332``, so this step is specified here).
+    logits[t,e] = sum_k X[t,k]*Wr[e,k] in float32 in a fixed order: 32 partial
+    sums, partial l taking the k with (k mod 256) in [8l, 8l+8) in ascending k
+    (each f16*f16 product is exact in float32, so a fused multiply-add and
+    multiply-then-add agree), combined by the butterfly v += v[l ^ o] for
+    o = 16, 8, 4, 2, 1.  Top-k by value, ties to the smallest expert index (the
+    reference's arg-reduction rule, ``src/language/operations.jl:1675-1677``);
     gates = softmax over the k chosen logits in float32, stored as f16.
     X[T,H] f16, Wr[E,H] f16 -> ids[topk,T] int32 (1-based), gates[topk,T] f16,
     logits[T,E] float32."""
     T, H = X.shape
-    Xf = X.astype(np.float32); Wf = Wr.astype(np.float32)
-    acc = np.zeros((T, Wr.shape[0]), dtype=np.float32)
-    for k in range(H):
-        acc = acc + Xf[:, k:k + 1] * Wf[None, :, k]
+    E = Wr.shape[0]
+    Hp = -(-H // 256) * 256
+    Xf = np.zeros((T, Hp), np.float32); Xf[:, :H] = X.astype(np.float32)
+    Wf = np.zeros((E, Hp), np.float32); Wf[:, :H] = Wr.astype(np.float32)
+    lanes = np.arange(32)
+    part = np.zeros((T, E, 32), dtype=np.float32)
+    for c in range(Hp // 256):
+        for j in range(8):
+            k = c * 256 + lanes * 8 + j
+            part = part + Xf[:, None, k] * Wf[None, :, k]
+    for o in (16, 8, 4, 2, 1):
+        part = part + part[:, :, lanes ^ o]
+    acc = np.ascontiguousarray(part[:, :, 0])
     work = acc.copy()
     ids = np.empty((topk, T), dtype=np.int32)
     sel = np.empty((topk, T), dtype=np.float32)
