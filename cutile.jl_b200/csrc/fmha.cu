@@ -223,8 +223,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       float l = 0.f;            // row sum relative to m_ref
       for (int j = 0; j < it.Tc; ++j) {
         const int gj = g + j;
-        ok = mbar_wait(&s_full, gj & 1, status, DEV_TIMEOUT_MMA, abort);
-        ok = __all_sync(0xffffffffu, ok);
+        ok = CTB_WARP_WAIT(&s_full, gj & 1, status, DEV_TIMEOUT_MMA, abort);
         if (!ok) break;
         tc_fence_after();
         const bool masked = j >= it.mask_start;
@@ -264,8 +263,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         // ---- move the exponent reference (and rescale O, l) only when the maximum grew by more than 2^8
         const bool grow = m_true - m_ref > 8.0f || m_ref == -INFINITY;
         if (j > 0) {  // PV(j-1) must have consumed P(j-1) (and, for a rescale, landed in O) before P(j) is written
-          ok = mbar_wait(&o_full, (gj - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
-          ok = __all_sync(0xffffffffu, ok);
+          ok = CTB_WARP_WAIT(&o_full, (gj - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
           if (!ok) break;
           tc_fence_after();
         }
@@ -319,8 +317,7 @@ __global__ void __launch_bounds__(kThreads, 2)
       if (!ok) break;
       g += it.Tc;
       // ---- epilogue of the item: O / l -> f16 -> global, then O is free for the next item
-      ok = mbar_wait(&o_full, (g - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = CTB_WARP_WAIT(&o_full, (g - 1) & 1, status, DEV_TIMEOUT_MMA, abort);
       if (!ok) break;
       tc_fence_after();
       const float inv = rcp_approx_ftz(l);

@@ -184,8 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t acc_phase = (it >> 1) & 1;
       int b, tm, tn;
       tile_coords(p, t, b, tm, tn);
-      bool ok = mbar_wait(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
-      ok = __all_sync(0xffffffffu, ok);
+      bool ok = CTB_WARP_WAIT(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
       if (!ok) break;
       tc_fence_after();
       const int m = tm * kTileM + sub * 32 + lane;

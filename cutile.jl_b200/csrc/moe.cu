@@ -40,7 +40,7 @@ namespace {
 // o = 16, 8, 4, 2, 1.  The CPU oracle performs the same operations in the same
 // order, so logits and therefore top-k ids agree bit for bit.  Every load is a
 // coalesced 16-byte access; W_r (64 KB at 32 experts x 1024) stays in L1/L2.
-constexpr int kRouterWarps = 4;
+constexpr int kRouterWarps = 8;
 constexpr int kRouterThreads = kRouterWarps * 32;
 constexpr int kMaxRouterE = 256;
 
@@ -54,54 +54,78 @@ __device__ __forceinline__ void cvt8(const uint4& u, float* f) {
   }
 }
 
+// The CTA's 8 token rows and `eg` expert rows of W_r at a time (all of them when they fit) are copied to
+// shared memory with cp.async, every thread keeping many 16-byte copies in flight, so the global-memory
+// latency is paid once per staging step and the arithmetic then runs out of shared memory.
 __global__ void __launch_bounds__(kRouterThreads)
     moe_router_kernel(const __half* __restrict__ X, const __half* __restrict__ Wr, int* __restrict__ ids,
-                      __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouterWarps + warp;
-  if (t >= T) return;
-  const __half* x = X + (long long)t * H;
+                      __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk,
+                      int eg) {
+  extern __shared__ __align__(16) unsigned char rsm[];
+  __half* sx = reinterpret_cast<__half*>(rsm);                              // [kRouterWarps][H]
+  __half* sw = reinterpret_cast<__half*>(rsm) + (size_t)kRouterWarps * H;   // [eg][H]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t = min((int)blockIdx.x * kRouterWarps + warp, T - 1);  // surplus warps redo the last token, write nothing
+  const bool live = (int)blockIdx.x * kRouterWarps + warp < T;
+  const int vpr = H / 8;  // 16-byte vectors per row (H % 8 == 0)
+  for (int i = lane; i < vpr; i += 32) cp_async16(sx + (size_t)warp * H + i * 8, X + (long long)t * H + i * 8, 16);
   const int nchunk = (H + 255) / 256;
   constexpr int EPL = kMaxRouterE / 32;
   float mine[EPL];  // logits of experts lane, lane+32, ...
 #pragma unroll
   for (int i = 0; i < EPL; ++i) mine[i] = -INFINITY;
-  for (int e0 = 0; e0 < E; e0 += 32) {
-    float acc[32];
+  const __half* x = sx + (size_t)warp * H;
+#pragma unroll 1
+  for (int g0 = 0; g0 < E; g0 += eg) {
+    const int ge = min(eg, E - g0);
+    __syncthreads();  // the previous group of expert rows has been consumed
+    for (int i = tid; i < ge * vpr; i += kRouterThreads)
+      cp_async16(sw + (size_t)i * 8, Wr + (long long)g0 * H + (size_t)i * 8, 16);
+    cp_async_wait_all();
+    __syncthreads();
+    // four experts at a time in rolled loops (the body runs once per warp: keep it small for the instruction cache)
+    constexpr int EG = 4;
+#pragma unroll 1
+    for (int e0 = 0; e0 < ge; e0 += EG) {
+      float acc[EG];
 #pragma unroll
-    for (int e = 0; e < 32; ++e) acc[e] = 0.f;
-    for (int c = 0; c < nchunk; ++c) {
-      const int k = c * 256 + lane * 8;
-      float xf[8];
-      if (k < H) cvt8(*reinterpret_cast<const uint4*>(x + k), xf);  // H % 8 == 0
-      else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) xf[j] = 0.f;
-      }
-#pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        float wf[8];
-        if (k < H && e0 + e < E) cvt8(*reinterpret_cast<const uint4*>(Wr + (long long)(e0 + e) * H + k), wf);
+      for (int e = 0; e < EG; ++e) acc[e] = 0.f;
+#pragma unroll 2
+      for (int c = 0; c < nchunk; ++c) {
+        const int k = c * 256 + lane * 8;
+        float xf[8];
+        if (k < H) cvt8(*reinterpret_cast<const uint4*>(x + k), xf);
         else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) wf[j] = 0.f;
+          for (int j = 0; j < 8; ++j) xf[j] = 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[e] = fmaf(xf[j], wf[j], acc[e]);  // ascending k inside the lane
+        for (int e = 0; e < EG; ++e) {
+          float wf[8];
+          if (k < H && e0 + e < ge) cvt8(*reinterpret_cast<const uint4*>(sw + (size_t)(e0 + e) * H + k), wf);
+          else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wf[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[e] = fmaf(xf[j], wf[j], acc[e]);  // ascending k inside the lane
+        }
       }
-    }
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      float v = acc[e];
+      for (int e = 0; e < EG; ++e) {
+        float v = acc[e];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == e && e0 + e < E) {
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        const int ex = g0 + e0 + e;
+        if (e0 + e < ge && lane == (ex & 31)) {
 #pragma unroll
-        for (int i = 0; i < EPL; ++i)
-          if (i == e0 / 32) mine[i] = v;
+          for (int i = 0; i < EPL; ++i)
+            if (i == (ex >> 5)) mine[i] = v;
+        }
       }
     }
   }
+  if (!live) return;
   if (logits_out) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
@@ -465,8 +489,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
         bool ok = true;
         for (int kb = 0; kb < nk; ++kb) {
-          ok = mbar_wait(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
-          ok = __all_sync(0xffffffffu, ok);
+          ok = CTB_WARP_WAIT1(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
           if (!ok) break;
           unsigned char* base = smem + (size_t)stage * p.stage_bytes + wbytes;
           const int k = kb * kBK + cch * 8;
@@ -511,8 +534,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             swt[q] = __half2float(p.topk_w[p.w_tokens ? (long long)(f % p.w_topk) * p.w_tokens + f / p.w_topk : f]);
           }
         }
-        bool ok = mbar_wait(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
-        ok = __all_sync(0xffffffffu, ok);
+        bool ok = CTB_WARP_WAIT1(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem + lane_addr + acc * 256;
@@ -683,8 +705,16 @@ int ctb_moe_router(ctb_ctx* ctx, void* stream, const void* hidden, const void* W
   CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(W_r); CTB_CHECK_DEV(topk_ids); CTB_CHECK_DEV(topk_weights);
   if ((uintptr_t)hidden % 16 || (uintptr_t)W_r % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_router: 16-byte alignment");
   const int grid = (int)((T + kRouterWarps - 1) / kRouterWarps);
-  moe_router_kernel<<<grid, kRouterThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk);
+  // expert rows staged per step: all of W_r when it fits beside the token rows
+  const size_t budget = 200 * 1024, xbytes = (size_t)kRouterWarps * H * 2, rowbytes = (size_t)H * 2;
+  if (xbytes + 4 * rowbytes > budget) return fail(CTB_UNSUPPORTED, "ctb_moe_router: hidden size %lld too large", (long long)H);
+  const int eg = (int)std::min<size_t>((size_t)E, (budget - xbytes) / rowbytes / 4 * 4);
+  const size_t smem = xbytes + (size_t)eg * rowbytes;
+  cudaError_t ce = cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (ce != cudaSuccess) return cuda_fail(ce, "ctb_moe_router: shared memory opt-in");
+  moe_router_kernel<<<grid, kRouterThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk,
+      eg);
   CTB_CHECK_LAUNCH("ctb_moe_router launch");
   return CTB_OK;
 }

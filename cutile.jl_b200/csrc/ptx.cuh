@@ -33,8 +33,13 @@ __device__ __forceinline__ bool elect_one() {
   asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
   return pred != 0;
 }
-// mbar_wait for a whole warp: every lane polls; the result is made uniform.
+// mbar_wait for a whole (converged) warp, result made uniform.
+// CTB_WARP_WAIT: every lane polls.  Lowest wake-up latency; used by the single producer / MMA warps.
+// CTB_WARP_WAIT1: lane 0 polls, the others wait at the shuffle.  Used where several warps of a CTA wait on the
+// same barrier for long (gather and epilogue warps): 32 polling lanes per warp would crowd the shared-memory
+// pipe that the working warps need for their shuffles, loads and stores.
 #define CTB_WARP_WAIT(...) (__all_sync(0xffffffffu, mbar_wait(__VA_ARGS__)))
+#define CTB_WARP_WAIT1(...) (__shfl_sync(0xffffffffu, (threadIdx.x & 31) == 0 ? (int)mbar_wait(__VA_ARGS__) : 1, 0) != 0)
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -123,6 +128,7 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, uin
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(src_bytes)
                : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // Arrive on `bar` once all cp.async issued so far by this thread have landed
 // (counts against the barrier's initial arrival count).
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
