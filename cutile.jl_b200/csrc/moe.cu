@@ -342,7 +342,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int kMaxStages = 8;
-  __shared__ __align__(8) uint64_t w_full[kMaxStages], b_full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
+  // full[s]: one arrival with the TMA byte count from the weight producer + one arrival per gather thread
+  __shared__ __align__(8) uint64_t full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int meta_e[kMetaItems], meta_ext[kMetaItems];  // expert (0-based, -1 = skip) and slot extent per item
@@ -350,8 +351,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (threadIdx.x == 0) {
     abort_s = 0;
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&w_full[s], 1);
-      mbar_init(&b_full[s], 128);  // one arrival per gather thread, triggered by its cp.async completion
+      mbar_init(&full[s], 1 + 128);  // gather threads arrive when their cp.async copies have landed
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -410,14 +410,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (!ok) break;
           unsigned char* dst = smem + (size_t)stage * p.stage_bytes;
           if (elect_one()) {
-            mbar_expect_tx(&w_full[stage], wbytes);
+            mbar_expect_tx(&full[stage], wbytes);
             if (EPI == EPI_SWIGLU) {
-              tma_load_3d(dst, &tmW, kb * kBK, nt * kRows, e, &w_full[stage]);
-              tma_load_3d(dst + kWTile, &tmW, kb * kBK, p.N + nt * kRows, e, &w_full[stage]);
+              tma_load_3d(dst, &tmW, kb * kBK, nt * kRows, e, &full[stage]);
+              tma_load_3d(dst + kWTile, &tmW, kb * kBK, p.N + nt * kRows, e, &full[stage]);
             } else {
 #pragma unroll
               for (int w = 0; w < NW; ++w)
-                tma_load_3d(dst + w * kWTile, &tmW, kb * kBK, nt * kRowsItem + w * kRows, e, &w_full[stage]);
+                tma_load_3d(dst + w * kWTile, &tmW, kb * kBK, nt * kRowsItem + w * kRows, e, &full[stage]);
             }
           }
           __syncwarp();
@@ -439,8 +439,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const uint32_t d = tmem + acc * 256;
         bool ok = true;
         for (int kb = 0; kb < nk; ++kb) {
-          ok = CTB_WARP_WAIT(&w_full[stage], phase, status, DEV_TIMEOUT_TMA, abort) &&
-               CTB_WARP_WAIT(&b_full[stage], phase, status, DEV_TIMEOUT_SLOT, abort);
+          ok = CTB_WARP_WAIT(&full[stage], phase, status, DEV_TIMEOUT_TMA, abort);
           if (!ok) break;
           fence_proxy_async_smem();  // the gathered rows were written through the generic proxy
           tc_fence_after();
@@ -502,7 +501,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                          valid ? (const void*)(src[q] + kb * kBK) : (const void*)p.A, valid ? 16u : 0u);
             }
           }
-          cp_async_arrive_noinc(&b_full[stage]);  // fires when this thread's copies have landed
+          cp_async_arrive_noinc(&full[stage]);  // fires when this thread's copies have landed
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
@@ -550,27 +549,44 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 tmem_ld16(taddr + c0, ga);
                 if (NW == 2) tmem_ld16(taddr + 128 + c0, up);
                 tc_wait_ld();
+                // Three branch-free phases so that the 16 columns overlap: in one loop with a shuffle and an
+                // early-out per column every column waited for its own shuffle -> exp -> reciprocal chain.
+                int idv[16];
+                float wtv[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                  const int id = __shfl_sync(0xffffffffu, sid[q], hlf * 16 + j);
-                  const float wt = __shfl_sync(0xffffffffu, swt[q], hlf * 16 + j);
-                  if (id == 0) continue;
-                  float v0 = __uint_as_float(ga[j]);
+                  idv[j] = __shfl_sync(0xffffffffu, sid[q], hlf * 16 + j);
+                  wtv[j] = __shfl_sync(0xffffffffu, swt[q], hlf * 16 + j);
+                }
+                float o0[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const float v0 = __uint_as_float(ga[j]);
                   if (EPI == EPI_SWIGLU) {
                     // silu(g) * u with flush-to-zero and an approximate reciprocal (examples/moe.jl:117-124)
-                    const float sig = rcp_approx_ftz(1.0f + __expf(-v0));
-                    v0 = v0 * sig * __uint_as_float(up[j]);
-                    if (row0 < p.N) reinterpret_cast<__half*>(p.C)[(long long)(id - 1) * p.ldc + row0] = __float2half_rn(v0);
+                    o0[j] = v0 * rcp_approx_ftz(1.0f + __expf(-v0)) * __uint_as_float(up[j]);
                   } else {
+                    o0[j] = v0 * wtv[j];
+                    if (NW == 2) up[j] = __float_as_uint(__uint_as_float(up[j]) * wtv[j]);
+                  }
+                }
 #pragma unroll
-                    for (int w = 0; w < NW; ++w) {
-                      const int row = row0 + w * kRows;
-                      const float v = (w == 0 ? v0 : __uint_as_float(up[j])) * wt;
-                      if (row < p.N) {
-                        if (EPI == EPI_F32)
-                          reinterpret_cast<float*>(p.C)[(long long)(id - 1) * p.ldc + row] = v;
-                        else
-                          reinterpret_cast<__half*>(p.C)[(long long)(id - 1) * p.ldc + row] = __float2half_rn(v);
+                for (int j = 0; j < 16; ++j) {
+                  const long long col = (long long)(idv[j] - 1) * p.ldc;
+                  if (idv[j] != 0) {
+                    if (EPI == EPI_SWIGLU) {
+                      if (row0 < p.N) reinterpret_cast<__half*>(p.C)[col + row0] = __float2half_rn(o0[j]);
+                    } else {
+#pragma unroll
+                      for (int w = 0; w < NW; ++w) {
+                        const int row = row0 + w * kRows;
+                        const float v = w == 0 ? o0[j] : __uint_as_float(up[j]);
+                        if (row < p.N) {
+                          if (EPI == EPI_F32)
+                            reinterpret_cast<float*>(p.C)[col + row] = v;
+                          else
+                            reinterpret_cast<__half*>(p.C)[col + row] = __float2half_rn(v);
+                        }
                       }
                     }
                   }
