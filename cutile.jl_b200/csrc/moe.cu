@@ -40,92 +40,12 @@ namespace {
 // o = 16, 8, 4, 2, 1.  The CPU oracle performs the same operations in the same
 // order, so logits and therefore top-k ids agree bit for bit.  Every load is a
 // coalesced 16-byte access; W_r (64 KB at 32 experts x 1024) stays in L1/L2.
-constexpr int kRouterWarps = 8;
-constexpr int kRouterThreads = kRouterWarps * 32;
-constexpr int kMaxRouterE = 256;
-
-__device__ __forceinline__ void cvt8(const uint4& u, float* f) {
-  const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 v = __half22float2(h[i]);
-    f[2 * i] = v.x;
-    f[2 * i + 1] = v.y;
-  }
-}
-
-// The CTA's 8 token rows and `eg` expert rows of W_r at a time (all of them when they fit) are copied to
-// shared memory with cp.async, every thread keeping many 16-byte copies in flight, so the global-memory
-// latency is paid once per staging step and the arithmetic then runs out of shared memory.
-__global__ void __launch_bounds__(kRouterThreads)
-    moe_router_kernel(const __half* __restrict__ X, const __half* __restrict__ Wr, int* __restrict__ ids,
-                      __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk,
-                      int eg) {
-  extern __shared__ __align__(16) unsigned char rsm[];
-  __half* sx = reinterpret_cast<__half*>(rsm);                              // [kRouterWarps][H]
-  __half* sw = reinterpret_cast<__half*>(rsm) + (size_t)kRouterWarps * H;   // [eg][H]
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int t = min((int)blockIdx.x * kRouterWarps + warp, T - 1);  // surplus warps redo the last token, write nothing
-  const bool live = (int)blockIdx.x * kRouterWarps + warp < T;
-  const int vpr = H / 8;  // 16-byte vectors per row (H % 8 == 0)
-  for (int i = lane; i < vpr; i += 32) cp_async16(sx + (size_t)warp * H + i * 8, X + (long long)t * H + i * 8, 16);
-  const int nchunk = (H + 255) / 256;
-  constexpr int EPL = kMaxRouterE / 32;
-  float mine[EPL];  // logits of experts lane, lane+32, ...
-#pragma unroll
-  for (int i = 0; i < EPL; ++i) mine[i] = -INFINITY;
-  const __half* x = sx + (size_t)warp * H;
-#pragma unroll 1
-  for (int g0 = 0; g0 < E; g0 += eg) {
-    const int ge = min(eg, E - g0);
-    __syncthreads();  // the previous group of expert rows has been consumed
-    for (int i = tid; i < ge * vpr; i += kRouterThreads)
-      cp_async16(sw + (size_t)i * 8, Wr + (long long)g0 * H + (size_t)i * 8, 16);
-    cp_async_wait_all();
-    __syncthreads();
-    // four experts at a time in rolled loops (the body runs once per warp: keep it small for the instruction cache)
-    constexpr int EG = 4;
-#pragma unroll 1
-    for (int e0 = 0; e0 < ge; e0 += EG) {
-      float acc[EG];
-#pragma unroll
-      for (int e = 0; e < EG; ++e) acc[e] = 0.f;
-#pragma unroll 2
-      for (int c = 0; c < nchunk; ++c) {
-        const int k = c * 256 + lane * 8;
-        float xf[8];
-        if (k < H) cvt8(*reinterpret_cast<const uint4*>(x + k), xf);
-        else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) xf[j] = 0.f;
-        }
-#pragma unroll
-        for (int e = 0; e < EG; ++e) {
-          float wf[8];
-          if (k < H && e0 + e < ge) cvt8(*reinterpret_cast<const uint4*>(sw + (size_t)(e0 + e) * H + k), wf);
-          else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) wf[j] = 0.f;
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[e] = fmaf(xf[j], wf[j], acc[e]);  // ascending k inside the lane
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < EG; ++e) {
-        float v = acc[e];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        const int ex = g0 + e0 + e;
-        if (e0 + e < ge && lane == (ex & 31)) {
-#pragma unroll
-          for (int i = 0; i < EPL; ++i)
-            if (i == (ex >> 5)) mine[i] = v;
-        }
-      }
-    }
-  }
-  if (!live) return;
+constexpr int kRouterEPL = 256 / 32;
+// Top-k selection and gate weights of one token from its logits (lane l holds experts l, l+32, ...).
+__device__ __forceinline__ void route_one(float (&mine)[kRouterEPL], int t, int* __restrict__ ids,
+                                          __half* __restrict__ gates, float* __restrict__ logits_out, int T, int E,
+                                          int topk, int lane) {
+  constexpr int EPL = kRouterEPL;
   if (logits_out) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
@@ -170,11 +90,138 @@ __global__ void __launch_bounds__(kRouterThreads)
   }
 }
 
+constexpr int kRouterWarps = 8;
+constexpr int kRouterThreads = kRouterWarps * 32;
+constexpr int kRouterTok = 2 * kRouterWarps;  // tokens per group: each warp carries two tokens through the loop
+constexpr int kMaxRouterE = 256;
+
+__device__ __forceinline__ void cvt8(const uint4& u, float* f) {
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __half22float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+// Rows are staged in shared memory as f32, zero-padded to a multiple of 256 and permuted inside each
+// 256-element chunk so that lane l finds its elements 8l..8l+3 at float4 slot l and 8l+4..8l+7 at float4
+// slot 32+l: both 128-bit reads of a warp are then conflict-free.
+__device__ __forceinline__ void stage8(float* row, int v /*vector index = k/8*/, const float* f) {
+  float4* dst = reinterpret_cast<float4*>(row + (v >> 5) * 256) + (v & 31);
+  dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+  dst[32] = make_float4(f[4], f[5], f[6], f[7]);
+}
+
+// Persistent CTAs: `eg` expert rows of W_r (all of them when they fit) are converted to f32 in shared memory
+// once, then the CTA walks over groups of 16 tokens.  Every thread keeps several 16-byte loads in flight while
+// staging, so the global-memory latency is paid per staging step, not per multiply-add.
+__global__ void __launch_bounds__(kRouterThreads)
+    moe_router_kernel(const __half* __restrict__ X, const __half* __restrict__ Wr, int* __restrict__ ids,
+                      __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk,
+                      int eg) {
+  extern __shared__ __align__(16) float rsm[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nchunk = (H + 255) / 256, Hp = nchunk * 256;
+  float* sx = rsm;                              // [kRouterTok][Hp]
+  float* sw = rsm + (size_t)kRouterTok * Hp;    // [eg][Hp]
+  const int vpr = Hp / 8;                       // 8-element vectors per padded row
+  const int ngroups = (T + kRouterTok - 1) / kRouterTok;
+  constexpr int EPL = kMaxRouterE / 32;
+  auto stage_rows = [&](float* dst, const __half* src, int nrows, int row_limit) {
+#pragma unroll 4
+    for (int i = tid; i < nrows * vpr; i += kRouterThreads) {
+      const int r = i / vpr, v = i - r * vpr;
+      float f[8];
+      if (r < row_limit && v * 8 < H) cvt8(*reinterpret_cast<const uint4*>(src + (long long)r * H + v * 8), f);
+      else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = 0.f;
+      }
+      stage8(dst + (size_t)r * Hp, v, f);
+    }
+  };
+  const bool resident = eg >= E;  // all of W_r stays in shared memory for the CTA's lifetime
+  if (resident) stage_rows(sw, Wr, E, E);
+#pragma unroll 1
+  for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
+    const int tbase = grp * kRouterTok;
+    __syncthreads();  // the previous group's token rows have been consumed
+    stage_rows(sx, X + (long long)tbase * H, kRouterTok, T - tbase);
+    float mine[2][EPL];  // logits of experts lane, lane+32, ... for the warp's two tokens
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) mine[u][i] = -INFINITY;
+    const float4* x0 = reinterpret_cast<const float4*>(sx + (size_t)(2 * warp) * Hp) + lane;
+    const float4* x1 = reinterpret_cast<const float4*>(sx + (size_t)(2 * warp + 1) * Hp) + lane;
+#pragma unroll 1
+    for (int g0 = 0; g0 < E; g0 += eg) {
+      const int ge = min(eg, E - g0);
+      if (!resident) {
+        __syncthreads();  // the previous expert rows have been consumed
+        stage_rows(sw, Wr + (long long)g0 * H, ge, ge);
+      }
+      __syncthreads();
+      // four experts at a time in rolled loops (the body runs a few times per warp: keep it small for the
+      // instruction cache)
+      constexpr int EG = 4;
+#pragma unroll 1
+      for (int e0 = 0; e0 < ge; e0 += EG) {
+        float acc[2][EG];
+#pragma unroll
+        for (int e = 0; e < EG; ++e) acc[0][e] = acc[1][e] = 0.f;
+#pragma unroll 2
+        for (int c = 0; c < nchunk; ++c) {
+          const float4 a0 = x0[c * 64], a1 = x0[c * 64 + 32], b0 = x1[c * 64], b1 = x1[c * 64 + 32];
+#pragma unroll
+          for (int e = 0; e < EG; ++e) {
+            const float4* w = reinterpret_cast<const float4*>(sw + (size_t)min(e0 + e, ge - 1) * Hp) + lane + c * 64;
+            const float4 w0 = w[0], w1 = w[32];
+            // ascending k inside the lane
+            acc[0][e] = fmaf(a0.x, w0.x, acc[0][e]); acc[1][e] = fmaf(b0.x, w0.x, acc[1][e]);
+            acc[0][e] = fmaf(a0.y, w0.y, acc[0][e]); acc[1][e] = fmaf(b0.y, w0.y, acc[1][e]);
+            acc[0][e] = fmaf(a0.z, w0.z, acc[0][e]); acc[1][e] = fmaf(b0.z, w0.z, acc[1][e]);
+            acc[0][e] = fmaf(a0.w, w0.w, acc[0][e]); acc[1][e] = fmaf(b0.w, w0.w, acc[1][e]);
+            acc[0][e] = fmaf(a1.x, w1.x, acc[0][e]); acc[1][e] = fmaf(b1.x, w1.x, acc[1][e]);
+            acc[0][e] = fmaf(a1.y, w1.y, acc[0][e]); acc[1][e] = fmaf(b1.y, w1.y, acc[1][e]);
+            acc[0][e] = fmaf(a1.z, w1.z, acc[0][e]); acc[1][e] = fmaf(b1.z, w1.z, acc[1][e]);
+            acc[0][e] = fmaf(a1.w, w1.w, acc[0][e]); acc[1][e] = fmaf(b1.w, w1.w, acc[1][e]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+          for (int e = 0; e < EG; ++e) {
+            float v = acc[u][e];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            const int ex = g0 + e0 + e;
+            if (e0 + e < ge && lane == (ex & 31)) {
+#pragma unroll
+              for (int i = 0; i < EPL; ++i)
+                if (i == (ex >> 5)) mine[u][i] = v;
+            }
+          }
+      }
+    }
+#pragma unroll 1
+    for (int u = 0; u < 2; ++u) {
+      const int t = tbase + 2 * warp + u;
+      if (t >= T) break;
+      float lg[EPL];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) lg[i] = u == 0 ? mine[0][i] : mine[1][i];
+      route_one(lg, t, ids, gates, logits_out, T, E, topk, lane);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ align
 constexpr int kAlignThreads = 1024;
 constexpr int kAlignWarps = kAlignThreads / 32;
 constexpr int kMaxExperts = 256;
-constexpr int kAlignRegIds = 16;  // ids a lane keeps in registers between the two passes
+constexpr int kAlignRegIds = 8;   // ids a lane keeps in registers between the two passes
 
 template <typename IdT>
 __global__ void __launch_bounds__(kAlignThreads)
@@ -612,18 +659,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 }
 
 // ------------------------------------------------------------------ small kernels
-__global__ void moe_combine_kernel(const float* __restrict__ slots, __half* __restrict__ out, int T, int H, int topk) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over T*H/2
-  const int h2 = H / 2;
-  if (i >= (long long)T * h2) return;
-  const int t = (int)(i / h2), h = (int)(i - (long long)t * h2) * 2;
-  float a = 0.f, b = 0.f;
+// out(:, t) = sum over the top-k slot outputs of token t.  The slot outputs are f16 like the reference's cache3
+// (examples/moe.jl:230,256); they are added in f32 in ascending slot order and rounded once.
+__global__ void moe_combine_kernel(const __half* __restrict__ slots, __half* __restrict__ out, int T, int H, int topk) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over T*H/8
+  const int h8 = H / 8;
+  if (i >= (long long)T * h8) return;
+  const int t = (int)(i / h8), h = (int)(i - (long long)t * h8) * 8;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
   for (int s = 0; s < topk; ++s) {  // ascending slot: fixed order
-    const float2 v = *reinterpret_cast<const float2*>(slots + ((long long)t * topk + s) * H + h);
-    a += v.x;
-    b += v.y;
+    const uint4 v = *reinterpret_cast<const uint4*>(slots + ((long long)t * topk + s) * H + h);
+    const __half2* hv = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(hv[j]);
+      acc[2 * j] += f.x;
+      acc[2 * j + 1] += f.y;
+    }
   }
-  *reinterpret_cast<__half2*>(out + (long long)t * H + h) = __floats2half2_rn(a, b);
+  uint4 o;
+  o.x = pack_f16x2(acc[0], acc[1]); o.y = pack_f16x2(acc[2], acc[3]);
+  o.z = pack_f16x2(acc[4], acc[5]); o.w = pack_f16x2(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(out + (long long)t * H + h) = o;
 }
 
 __global__ void moe_silu_and_mul_kernel(const __half* __restrict__ A, const __half* __restrict__ B,
@@ -720,15 +779,16 @@ int ctb_moe_router(ctb_ctx* ctx, void* stream, const void* hidden, const void* W
   if (T == 0) return CTB_OK;
   CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(W_r); CTB_CHECK_DEV(topk_ids); CTB_CHECK_DEV(topk_weights);
   if ((uintptr_t)hidden % 16 || (uintptr_t)W_r % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_router: 16-byte alignment");
-  const int grid = (int)((T + kRouterWarps - 1) / kRouterWarps);
-  // expert rows staged per step: all of W_r when it fits beside the token rows
-  const size_t budget = 200 * 1024, xbytes = (size_t)kRouterWarps * H * 2, rowbytes = (size_t)H * 2;
+  // shared memory: 16 token rows + eg expert rows, f32, rows padded to a multiple of 256 elements
+  const int64_t Hp = (H + 255) / 256 * 256;
+  const size_t budget = 220 * 1024, rowbytes = (size_t)Hp * 4, xbytes = (size_t)kRouterTok * rowbytes;
   if (xbytes + 4 * rowbytes > budget) return fail(CTB_UNSUPPORTED, "ctb_moe_router: hidden size %lld too large", (long long)H);
   const int eg = (int)std::min<size_t>((size_t)E, (budget - xbytes) / rowbytes / 4 * 4);
   const size_t smem = xbytes + (size_t)eg * rowbytes;
   cudaError_t ce = cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (ce != cudaSuccess) return cuda_fail(ce, "ctb_moe_router: shared memory opt-in");
-  moe_router_kernel<<<grid, kRouterThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+  const int ngroups = (int)((T + kRouterTok - 1) / kRouterTok);
+  moe_router_kernel<<<std::min(ngroups, ctx->sm_count), kRouterThreads, smem, static_cast<cudaStream_t>(stream)>>>(
       (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk,
       eg);
   CTB_CHECK_LAUNCH("ctb_moe_router launch");
@@ -801,15 +861,15 @@ int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, 
   if (ids_bits != 32 && ids_bits != 64) return fail(CTB_BAD_ARG, "ctb_moe_ffn: ids_bits must be 32 or 64");
   CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(w1); CTB_CHECK_DEV(w2); CTB_CHECK_DEV(topk_weights); CTB_CHECK_DEV(topk_ids);
   CTB_CHECK_DEV(out);
-  if ((uintptr_t)hidden % 16 || (uintptr_t)w1 % 16 || (uintptr_t)w2 % 16 || (uintptr_t)out % 4)
+  if ((uintptr_t)hidden % 16 || (uintptr_t)w1 % 16 || (uintptr_t)w2 % 16 || (uintptr_t)out % 16)
     return fail(CTB_BAD_ALIGN, "ctb_moe_ffn: 16-byte alignment of hidden, w1, w2");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int total = (int)(T * topk);
   const int cap = (int)ctb_moe_max_blocks(T, topk, E, tile_m);
-  // scratch: sorted ids | expert ids | block count | activations (I, total) f16 | per-slot outputs (H, total) f32
+  // scratch: sorted ids | expert ids | block count | activations (I, total) f16 | per-slot outputs (H, total) f16
   auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
   const size_t o_tok = 0, o_exp = up((size_t)cap * tile_m * 4), o_nb = o_exp + up((size_t)cap * 4), o_act = o_nb + 256,
-               o_slots = o_act + up((size_t)total * I * 2), bytes = o_slots + up((size_t)total * H * 4);
+               o_slots = o_act + up((size_t)total * I * 2), bytes = o_slots + up((size_t)total * H * 2);
   void* ws;
   r = workspace(ctx, bytes, &ws);
   if (r) return r;
@@ -818,21 +878,20 @@ int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, 
   int* s_exp = (int*)(w + o_exp);
   int* s_nb = (int*)(w + o_nb);
   __half* act = (__half*)(w + o_act);
-  float* slots = (float*)(w + o_slots);
+  __half* slots = (__half*)(w + o_slots);
   r = launch_align(ctx, st, topk_ids, ids_bits, (int)T, (int)topk, (int)E, tile_m, s_tok, s_exp, s_nb, cap);
   if (r) return r;
   // gate/up projection with the SwiGLU epilogue: act(:, id) = silu(Wg x) * (Wu x)
   r = launch_gemm(ctx, st, EPI_SWIGLU, (const __half*)hidden, H, (int)T, (const __half*)w1, (int)H, (int)(2 * I),
                   (int)I, (int)E, nullptr, s_tok, s_exp, s_nb, -1, cap, (int)topk, 0, tile_m, total, act, I);
   if (r) return r;
-  // down projection scaled by the routing weight, one f32 column per slot
-  r = launch_gemm(ctx, st, EPI_F32, act, I, total, (const __half*)w2, (int)I, (int)H, (int)H, (int)E,
+  // down projection scaled by the routing weight, one f16 column per slot (the reference's cache3)
+  r = launch_gemm(ctx, st, EPI_F16, act, I, total, (const __half*)w2, (int)I, (int)H, (int)H, (int)E,
                   (const __half*)topk_weights, s_tok, s_exp, s_nb, -1, cap, 1, 1, tile_m, total, slots, H, (int)T,
                   (int)topk);
   if (r) return r;
-  if (H % 2) return fail(CTB_BAD_ALIGN, "ctb_moe_ffn: H must be even");
-  const long long n2 = T * (H / 2);
-  moe_combine_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(slots, (__half*)out, (int)T, (int)H, (int)topk);
+  const long long n8 = T * (H / 8);
+  moe_combine_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(slots, (__half*)out, (int)T, (int)H, (int)topk);
   CTB_CHECK_LAUNCH("ctb_moe_ffn combine launch");
   return CTB_OK;
 }
