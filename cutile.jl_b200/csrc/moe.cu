@@ -685,6 +685,29 @@ __global__ void moe_combine_kernel(const __half* __restrict__ slots, __half* __r
   *reinterpret_cast<uint4*>(out + (long long)t * H + h) = o;
 }
 
+// dst row i = src row (ids[i]-1)/replicas (zero when the id is out of range); rows of `vecs` 16-byte vectors
+__global__ void moe_gather_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                       const int* __restrict__ ids, long long n, int vecs, int replicas,
+                                       long long src_rows) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * vecs) return;
+  const long long r = i / vecs;
+  const int v = (int)(i - r * vecs);
+  const long long id = ids[r];
+  const long long sr = id >= 1 ? (id - 1) / replicas : -1;
+  dst[i] = (sr >= 0 && sr < src_rows) ? src[sr * vecs + v] : make_uint4(0, 0, 0, 0);
+}
+// dst row ids[i]-1 = src row i (ids out of range are skipped)
+__global__ void moe_scatter_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                        const int* __restrict__ ids, long long n, int vecs, long long dst_rows) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * vecs) return;
+  const long long r = i / vecs;
+  const int v = (int)(i - r * vecs);
+  const long long id = ids[r];
+  if (id >= 1 && id <= dst_rows) dst[(id - 1) * vecs + v] = src[i];
+}
+
 __global__ void moe_silu_and_mul_kernel(const __half* __restrict__ A, const __half* __restrict__ B,
                                         __half* __restrict__ C, int n, long long cols, long long lda, long long ldb,
                                         long long ldc) {
@@ -893,6 +916,53 @@ int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, 
   const long long n8 = T * (H / 8);
   moe_combine_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(slots, (__half*)out, (int)T, (int)H, (int)topk);
   CTB_CHECK_LAUNCH("ctb_moe_ffn combine launch");
+  return CTB_OK;
+}
+
+int ctb_moe_gather_rows(ctb_ctx* ctx, void* stream, void* dst, const void* src, const int32_t* ids, int64_t n_ids,
+                        int64_t row_elems, int num_token_replicas, int64_t src_rows) {
+  CTB_CHECK_CTX(ctx);
+  if (n_ids < 0 || row_elems <= 0 || num_token_replicas <= 0 || src_rows < 0)
+    return fail(CTB_BAD_ARG, "ctb_moe_gather_rows: bad shape");
+  if (row_elems % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_gather_rows: rows must be multiples of 8 f16 elements");
+  if (n_ids == 0) return CTB_OK;
+  CTB_CHECK_DEV(dst); CTB_CHECK_DEV(src); CTB_CHECK_DEV(ids);
+  if ((uintptr_t)dst % 16 || (uintptr_t)src % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_gather_rows: 16-byte alignment");
+  const int vecs = (int)(row_elems / 8);
+  const long long tot = n_ids * vecs;
+  moe_gather_rows_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (uint4*)dst, (const uint4*)src, ids, n_ids, vecs, num_token_replicas, src_rows);
+  CTB_CHECK_LAUNCH("ctb_moe_gather_rows launch");
+  return CTB_OK;
+}
+
+int ctb_moe_scatter_rows(ctb_ctx* ctx, void* stream, void* dst, const void* src, const int32_t* ids, int64_t n_ids,
+                         int64_t row_elems, int64_t dst_rows) {
+  CTB_CHECK_CTX(ctx);
+  if (n_ids < 0 || row_elems <= 0 || dst_rows < 0) return fail(CTB_BAD_ARG, "ctb_moe_scatter_rows: bad shape");
+  if (row_elems % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_scatter_rows: rows must be multiples of 8 f16 elements");
+  if (n_ids == 0) return CTB_OK;
+  CTB_CHECK_DEV(dst); CTB_CHECK_DEV(src); CTB_CHECK_DEV(ids);
+  if ((uintptr_t)dst % 16 || (uintptr_t)src % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_scatter_rows: 16-byte alignment");
+  const int vecs = (int)(row_elems / 8);
+  const long long tot = n_ids * vecs;
+  moe_scatter_rows_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (uint4*)dst, (const uint4*)src, ids, n_ids, vecs, dst_rows);
+  CTB_CHECK_LAUNCH("ctb_moe_scatter_rows launch");
+  return CTB_OK;
+}
+
+int ctb_moe_combine(ctb_ctx* ctx, void* stream, const void* slots, void* out, int64_t T, int64_t H, int64_t topk) {
+  CTB_CHECK_CTX(ctx);
+  if (T < 0 || H <= 0 || topk <= 0) return fail(CTB_BAD_ARG, "ctb_moe_combine: bad shape");
+  if (H % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_combine: H must be a multiple of 8");
+  if (T == 0) return CTB_OK;
+  CTB_CHECK_DEV(slots); CTB_CHECK_DEV(out);
+  if ((uintptr_t)slots % 16 || (uintptr_t)out % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_combine: 16-byte alignment");
+  const long long n8 = T * (H / 8);
+  moe_combine_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const __half*)slots, (__half*)out, (int)T, (int)H, (int)topk);
+  CTB_CHECK_LAUNCH("ctb_moe_combine launch");
   return CTB_OK;
 }
 

@@ -57,6 +57,9 @@ SIGNATURES = {
     "ctb_moe_align": [_p, _p, _p, _i, _i64, _i64, _i64, _i, _p, _p, _p, _i64],
     "ctb_moe_fused_gemm": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i, _i],
     "ctb_moe_silu_and_mul": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i],
+    "ctb_moe_gather_rows": [_p, _p, _p, _p, _p, _i64, _i64, _i, _i64],
+    "ctb_moe_scatter_rows": [_p, _p, _p, _p, _p, _i64, _i64, _i64],
+    "ctb_moe_combine": [_p, _p, _p, _p, _i64, _i64, _i64],
     "ctb_moe_ffn": [_p, _p, _p, _p, _p, _p, _p, _i, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i],
 }
 _RESTYPES = {"ctb_destroy": None, "ctb_last_error": C.c_char_p, "ctb_status_string": C.c_char_p,

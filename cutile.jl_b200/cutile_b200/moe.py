@@ -109,3 +109,71 @@ def cutile_moe(hidden_states, w1, w2, topk_weights, topk_ids, tile_m, tile_n, ti
                                     ptr(topk_ids), _ids_bits(topk_ids), ptr(out), T, H, I, E, topk, int(tile_m),
                                     int(tile_n), int(tile_k)))
     return out
+
+
+# --------------------------------------------------------------------------- expert parallelism
+def ep_plan(topk_ids, num_experts, world_size):
+    """Dispatch plan of one rank for expert-parallel MoE.  `topk_ids` [topk, T_local] (1-based global expert ids).
+    Experts are split in contiguous shards of num_experts/world_size per rank.  Returns
+    (order, send_counts): `order` = 1-based flat slot ids (token*topk + slot + 1) sorted by expert, stable -- the
+    order in which token rows are sent -- and `send_counts[r]` = slots that go to rank r.  Plain torch ops: runs
+    on CPU tensors as well (used by the gloo tests)."""
+    if num_experts % world_size:
+        raise _lib.CtbError(_lib.BAD_ARG, "ep_plan: the number of experts must be a multiple of the world size")
+    flat = topk_ids.t().reshape(-1).to(torch.int64)  # slot fastest, examples/moe.jl:146-148
+    order = torch.argsort(flat, stable=True)
+    dest = (flat[order] - 1) // (num_experts // world_size)
+    send_counts = torch.bincount(dest, minlength=world_size)
+    return (order + 1).to(torch.int32), send_counts
+
+
+def cutile_moe_ep(hidden_states, w1_local, w2_local, topk_weights, topk_ids, num_experts, tile_m, tile_n, tile_k,
+                  group=None):
+    """Expert-parallel cutile_moe: this rank holds T_local tokens and the expert shard
+    [rank*E/N, (rank+1)*E/N) (w1_local [E/N, 2I, H], w2_local [E/N, H, I]).  Token rows are packed in expert
+    order, exchanged with one all-to-all (NCCL), run through the local experts with the single-GPU kernels
+    (topk = 1, gate applied), sent back by the reverse all-to-all and summed over each token's slots.
+    Returns [T_local, H] f16; bit-identical to cutile_moe on the gathered problem."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    ctx, stream = handles(hidden_states)
+    T, H = hidden_states.shape
+    topk = topk_ids.shape[0]
+    El = num_experts // world
+    total = T * topk
+    order, send_counts = ep_plan(topk_ids, num_experts, world)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    counts = torch.stack([send_counts, recv_counts]).cpu()  # one small D2H: NCCL needs the split sizes on the host
+    send_l, recv_l = counts[0].tolist(), counts[1].tolist()
+    R = int(sum(recv_l))
+    dev = hidden_states.device
+    # pack: token rows, local expert ids and gates in send order
+    send_rows = torch.empty((total, H), dtype=torch.float16, device=dev)
+    _lib.check(_lib.lib.ctb_moe_gather_rows(ctx, stream, ptr(send_rows), ptr(hidden_states), ptr(order), total, H,
+                                            topk, T))
+    o64 = order.to(torch.int64) - 1
+    flat_e = topk_ids.t().reshape(-1)[o64].to(torch.int32)
+    flat_w = topk_weights.t().reshape(-1)[o64].contiguous()
+    recv_rows = torch.empty((max(R, 1), H), dtype=torch.float16, device=dev)
+    recv_e = torch.empty(max(R, 1), dtype=torch.int32, device=dev)
+    recv_w = torch.empty(max(R, 1), dtype=torch.float16, device=dev)
+    dist.all_to_all_single(recv_rows[:R], send_rows, recv_l, send_l, group=group)
+    dist.all_to_all_single(recv_e[:R], flat_e, recv_l, send_l, group=group)
+    dist.all_to_all_single(recv_w[:R], flat_w, recv_l, send_l, group=group)
+    # local experts: every received row is one token with topk = 1
+    if R > 0:
+        local_ids = (recv_e[:R] - rank * El).reshape(1, R).contiguous()
+        y = cutile_moe(recv_rows[:R], w1_local, w2_local, recv_w[:R].reshape(1, R).contiguous(), local_ids,
+                       tile_m, tile_n, tile_k)
+    else:
+        y = recv_rows[:0]
+    back = torch.empty((total, H), dtype=torch.float16, device=dev)
+    dist.all_to_all_single(back, y, send_l, recv_l, group=group)
+    # unsort into flat slot order and add each token's slots
+    slots = torch.empty((total, H), dtype=torch.float16, device=dev)
+    _lib.check(_lib.lib.ctb_moe_scatter_rows(ctx, stream, ptr(slots), ptr(back), ptr(order), total, H, total))
+    out = torch.empty((T, H), dtype=torch.float16, device=dev)
+    _lib.check(_lib.lib.ctb_moe_combine(ctx, stream, ptr(slots), ptr(out), T, H, topk))
+    return out

@@ -175,6 +175,25 @@ int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, 
                 const void* topk_weights, const void* topk_ids, int ids_bits, void* out, int64_t T, int64_t H,
                 int64_t I, int64_t E, int64_t topk, int tile_m, int tile_n, int tile_k);
 
+/* Building blocks of the expert-parallel MoE (one process per GPU; experts
+ * [r*E/N, (r+1)*E/N) live on rank r; tokens start sharded by rank).  The reference
+ * is single-GPU; the sharding comes from the benchmark configuration.  The
+ * exchange itself (all-to-all of token rows and of their outputs) is done by the
+ * host binding with NCCL.
+ * ctb_moe_gather_rows : dst(:, i) = src(:, cld(ids[i], replicas)), the gather half
+ *   of fused_moe_kernel (examples/moe.jl:62-70) as a stand-alone copy: packs the
+ *   token rows of the locally routed slots, sorted by destination expert, into the
+ *   send buffer.  Out-of-range ids give zero rows.
+ * ctb_moe_scatter_rows: dst(:, ids[i]) = src(:, i): puts the returned slot outputs
+ *   back in flat slot order (the scatter half, examples/moe.jl:99-102).
+ * ctb_moe_combine     : out(:, t) = sum over the topk slots of token t, slots
+ *   (H, topk, T) f16 (examples/moe.jl:256). */
+int ctb_moe_gather_rows(ctb_ctx* ctx, void* stream, void* dst, const void* src, const int32_t* ids, int64_t n_ids,
+                        int64_t row_elems, int num_token_replicas, int64_t src_rows);
+int ctb_moe_scatter_rows(ctb_ctx* ctx, void* stream, void* dst, const void* src, const int32_t* ids, int64_t n_ids,
+                         int64_t row_elems, int64_t dst_rows);
+int ctb_moe_combine(ctb_ctx* ctx, void* stream, const void* slots, void* out, int64_t T, int64_t H, int64_t topk);
+
 /* ---- LayerNorm backward without any allocation --------------------------------- */
 /* No counterpart in the reference.  For callers that cannot obtain device memory
  * at the point where the backward pass runs (a plug-in inside another runtime's
