@@ -597,6 +597,8 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # the version banner goes to stdout, which carries the JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     sampler = ClockSampler(local)
     sampler.start()
