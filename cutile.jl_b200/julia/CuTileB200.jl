@@ -178,4 +178,36 @@ function cutile_moe(hidden_states::CuArray{T}, w1, w2, topk_weights, topk_ids, t
     return out
 end
 
+# ---- building blocks of the expert-parallel MoE (the all-to-all itself is the host's, e.g. NCCL.jl) ----
+"dst(:, i) = src(:, cld(ids[i], num_token_replicas)); ids out of range give zero rows."
+function moe_gather_rows(dst::CuArray{Float16,2}, src::CuArray{Float16,2}, ids::CuArray{Int32,1}, num_token_replicas::Int)
+    check(ccall((:ctb_moe_gather_rows, LIB), Cint,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int64, Int64, Cint, Int64),
+        context(), stream(), dptr(dst), dptr(src), dptr(ids), length(ids), size(src, 1), num_token_replicas, size(src, 2)))
+end
+
+"dst(:, ids[i]) = src(:, i)."
+function moe_scatter_rows(dst::CuArray{Float16,2}, src::CuArray{Float16,2}, ids::CuArray{Int32,1})
+    check(ccall((:ctb_moe_scatter_rows, LIB), Cint,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int64, Int64, Int64),
+        context(), stream(), dptr(dst), dptr(src), dptr(ids), length(ids), size(src, 1), size(dst, 2)))
+end
+
+"out(:, t) = sum of the topk slot rows of token t; slots is (H, topk, T) (examples/moe.jl:256)."
+function moe_combine(slots::CuArray{Float16,3}, out::CuArray{Float16,2})
+    H, topk, T = size(slots)
+    check(ccall((:ctb_moe_combine, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int64, Int64, Int64),
+        context(), stream(), dptr(slots), dptr(out), T, H, topk))
+end
+
+# ---- LayerNorm backward with built-in scratch (no context, no partial buffers; N <= 8192) ----
+function layer_norm_bwd_static(DX, DY, X, W, Mean, Rstd, FINAL_DW, FINAL_DB)
+    N, M = size(X)
+    check(ccall((:ctb_layernorm_bwd_static, LIB), Cint,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
+         Int64, Int64, Int64, Int64, Int64),
+        stream(), dptr(DX), dptr(DY), dptr(X), dptr(W), dptr(Mean), dptr(Rstd), dptr(FINAL_DW), dptr(FINAL_DB),
+        N, M, stride(X, 2), stride(DY, 2), stride(DX, 2)))
+end
+
 end # module
