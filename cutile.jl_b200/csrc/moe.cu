@@ -346,7 +346,9 @@ __global__ void __launch_bounds__(kAlignThreads)
 // ------------------------------------------------------------------ grouped GEMM
 constexpr int kRows = 128;  // weight rows per tile = MMA M
 constexpr int kBK = 64;     // K elements per stage (128 bytes of f16)
-constexpr int kGemmThreads = 320;
+constexpr int kGatherWarps = 8;
+constexpr int kGatherThreads = kGatherWarps * 32;
+constexpr int kGemmThreads = 64 + kGatherThreads + 128;  // producer + MMA warps, gather warps, 4 epilogue warps
 constexpr int kWTile = kRows * kBK * 2;  // 16 KiB
 
 enum Epilogue : int { EPI_F16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
@@ -398,7 +400,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (threadIdx.x == 0) {
     abort_s = 0;
     for (int s = 0; s < p.stages; ++s) {
-      mbar_init(&full[s], 1 + 128);  // gather threads arrive when their cp.async copies have landed
+      mbar_init(&full[s], 1 + kGatherThreads);  // gather threads arrive when their cp.async copies have landed
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -509,27 +511,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (elect_one()) tc_commit(&acc_full[acc]);
         __syncwarp();
       }
-    } else if (warp < 6) {
-      // ---- token-row gather into the swizzled B operand (cp.async, completion arrives on b_full).
-      // Thread t copies the 16-byte chunks t, t+128, ... of the (slots x 8 chunks) tile, so one warp
-      // instruction moves four whole 128-byte row segments (full cache lines, conflict-free stores).
-      const int g = threadIdx.x - 64;  // 0..127
+    } else if (warp < 2 + kGatherWarps) {
+      // ---- token-row gather into the swizzled B operand (cp.async; the copy engine arrives on the stage's
+      // barrier when a thread's copies have landed, so no thread waits for its data).
+      // Thread g copies the 16-byte chunks g, g+256, ... of the (slots x 8 chunks) tile, so one warp instruction
+      // moves four whole 128-byte row segments (full cache lines, conflict-free stores).  The loop is the critical
+      // path of a k-block when few warps share it: everything that does not depend on the k-block (source rows,
+      // byte counts, the chunk's place inside a stage) is computed once per work item.
+      const int g = threadIdx.x - 64;  // 0..255
       const int cch = g & 7;           // chunk inside the 128-byte row segment (the same for every copy of the thread)
+      constexpr int kQ = 128 * 8 / kGatherThreads;   // copies per thread and k-block
+      constexpr int kRowStep = kGatherThreads / 8;   // block rows between two copies of a thread
+      // byte offset of the thread's first chunk inside the B part of a stage: row g/8, 128-byte swizzle
+      const uint32_t chunk_off = (uint32_t)((g >> 6) * 1024 + ((g >> 3) & 7) * 128 + ((cch ^ ((g >> 3) & 7)) << 4));
       for (int n = 0; n < rn; ++n) {
         if (meta_e[n] < 0) continue;
         const int nmma = max(16, (meta_ext[n] + 15) & ~15);
         const int it = blockIdx.x + (r0 + n) * gridDim.x;
         const int bm = it / p.n_tiles;
-        const __half* src[8];  // row q*16 + g/8 of the block, q = 0..7
+        const __half* src[kQ];  // row q*kRowStep + g/8 of the block; invalid rows read nothing (zero fill)
+        uint32_t nbytes[kQ];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const int r = q * 16 + (g >> 3);
-          src[q] = nullptr;
+        for (int q = 0; q < kQ; ++q) {
+          const int r = q * kRowStep + (g >> 3);
+          src[q] = p.A;
+          nbytes[q] = 0;
           if (r < p.tile_m && r < nmma) {
             const int id = p.sorted_ids[(long long)bm * p.tile_m + r];
             if (id >= 1 && id <= p.total) {
               const int tok = (id - 1) / p.replicas;  // cld(id, replicas) - 1
-              if (tok < p.a_rows) src[q] = p.A + (long long)tok * p.lda + cch * 8;
+              if (tok < p.a_rows) {
+                src[q] = p.A + (long long)tok * p.lda + cch * 8;
+                nbytes[q] = 16;
+              }
             }
           }
         }
@@ -537,15 +551,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int kb = 0; kb < nk; ++kb) {
           ok = CTB_WARP_WAIT1(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
           if (!ok) break;
-          unsigned char* base = smem + (size_t)stage * p.stage_bytes + wbytes;
-          const int k = kb * kBK + cch * 8;
+          const uint32_t base = smem_u32(smem + (size_t)stage * p.stage_bytes + wbytes) + chunk_off;
+          const bool in_k = kb * kBK + cch * 8 < p.K;  // K is a multiple of 8: a chunk is inside or outside as a whole
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const int r = q * 16 + (g >> 3);
-            if (r < nmma) {
-              const bool valid = src[q] != nullptr && k < p.K;
-              cp_async16(base + (r >> 3) * 1024 + (r & 7) * 128 + ((cch ^ (r & 7)) << 4),
-                         valid ? (const void*)(src[q] + kb * kBK) : (const void*)p.A, valid ? 16u : 0u);
+          for (int q = 0; q < kQ; ++q) {
+            if (q * kRowStep + (g >> 3) < nmma) {  // the same for the whole warp (nmma is a multiple of 16)
+              cp_async16_s(base + q * (kRowStep / 8) * 1024, src[q], in_k ? nbytes[q] : 0u);
+              src[q] += kBK;
             }
           }
           cp_async_arrive_noinc(&full[stage]);  // fires when this thread's copies have landed
