@@ -6,6 +6,12 @@ import json
 import os
 import sys
 
+
+def _emit(obj):
+    """One write per line: the ranks share a pipe, and print() writes text and newline separately."""
+    os.write(1, (json.dumps(obj) + "\n").encode())
+
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 for p in (ROOT, os.path.join(ROOT, "cutile.jl_b200")):
     if p not in sys.path:
@@ -48,7 +54,7 @@ def main():
         assert ((got_e >= lo) & (got_e <= hi)).all()  # only this rank's experts arrive
         allflat = ids.T.reshape(-1)
         assert got_e.numel() == int(((allflat >= lo) & (allflat <= hi)).sum())  # and all of them
-        print(json.dumps({"rank": rank, "ok": True, "received": got_e.numel()}), flush=True)
+        _emit({"rank": rank, "ok": True, "received": got_e.numel()})
     else:
         from oracle import inputs
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -63,7 +69,7 @@ def main():
         torch.cuda.synchronize()
         ctb.check_device_status(torch.cuda.current_device())
         same = bool(torch.equal(out, full[my]))
-        print(json.dumps({"rank": rank, "ok": same}), flush=True)
+        _emit({"rank": rank, "ok": same})
         assert same
     dist.destroy_process_group()
 
