@@ -92,8 +92,8 @@ __device__ __forceinline__ void route_one(float (&mine)[kRouterEPL], int t, int*
 
 constexpr int kRouterWarps = 8;
 constexpr int kRouterThreads = kRouterWarps * 32;
-constexpr int kRouterTok = 2 * kRouterWarps;  // tokens per group: each warp carries two tokens through the loop
 constexpr int kMaxRouterE = 256;
+constexpr int kRouterTE = 4;  // experts a warp carries through the hidden dimension at a time
 
 __device__ __forceinline__ void cvt8(const uint4& u, float* f) {
   const __half2* h = reinterpret_cast<const __half2*>(&u);
@@ -104,57 +104,49 @@ __device__ __forceinline__ void cvt8(const uint4& u, float* f) {
     f[2 * i + 1] = v.y;
   }
 }
-// Rows are staged in shared memory as f32, zero-padded to a multiple of 256 and permuted inside each
-// 256-element chunk so that lane l finds its elements 8l..8l+3 at float4 slot l and 8l+4..8l+7 at float4
-// slot 32+l: both 128-bit reads of a warp are then conflict-free.
-__device__ __forceinline__ void stage8(float* row, int v /*vector index = k/8*/, const float* f) {
-  float4* dst = reinterpret_cast<float4*>(row + (v >> 5) * 256) + (v & 31);
-  dst[0] = make_float4(f[0], f[1], f[2], f[3]);
-  dst[32] = make_float4(f[4], f[5], f[6], f[7]);
-}
 
-// Persistent CTAs: `eg` expert rows of W_r (all of them when they fit) are converted to f32 in shared memory
-// once, then the CTA walks over groups of 16 tokens.  Every thread keeps several 16-byte loads in flight while
-// staging, so the global-memory latency is paid per staging step, not per multiply-add.
+// A CTA works on groups of G = TT * tw tokens.  Its 8 warps form tw token-warps x ew expert-warps (tw * ew = 8):
+// a warp owns TT tokens and every ew-th block of four experts, computes those logits in the fixed order (lane l
+// = partial sum l, its 8 elements of each 256-chunk are one 16-byte shared-memory read, conflict-free without any
+// permutation) and leaves them in shared memory; after a barrier the warps take the group's tokens in turn for
+// top-k and gates.  Few tokens: small groups split over expert-warps, so that a 256-token batch still fills the
+// GPU; many tokens: TT = 4 tokens per warp, so that every weight vector read from shared memory feeds four
+// multiply-adds.  Rows are staged as f16 with cp.async (zero-filled up to a multiple of 256 elements); W_r stays
+// resident for the CTA's lifetime when it fits, else it passes through in slices of eg experts.
+template <int TT>
 __global__ void __launch_bounds__(kRouterThreads)
     moe_router_kernel(const __half* __restrict__ X, const __half* __restrict__ Wr, int* __restrict__ ids,
                       __half* __restrict__ gates, float* __restrict__ logits_out, int T, int H, int E, int topk,
-                      int eg) {
-  extern __shared__ __align__(16) float rsm[];
+                      int eg, int tw) {
+  extern __shared__ __align__(16) unsigned char rsm_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nchunk = (H + 255) / 256, Hp = nchunk * 256;
-  float* sx = rsm;                              // [kRouterTok][Hp]
-  float* sw = rsm + (size_t)kRouterTok * Hp;    // [eg][Hp]
-  const int vpr = Hp / 8;                       // 8-element vectors per padded row
-  const int ngroups = (T + kRouterTok - 1) / kRouterTok;
-  constexpr int EPL = kMaxRouterE / 32;
-  auto stage_rows = [&](float* dst, const __half* src, int nrows, int row_limit) {
-#pragma unroll 4
+  const int ew = kRouterWarps / tw, G = TT * tw;
+  __half* sx = reinterpret_cast<__half*>(rsm_raw);                     // [G][Hp]
+  __half* sw = sx + (size_t)G * Hp;                                    // [eg][Hp]
+  float* sl = reinterpret_cast<float*>(sw + (size_t)eg * Hp);          // [G][E] logits of the group
+  const int vpr = Hp / 8;                                              // 16-byte vectors per padded row
+  const int ngroups = (T + G - 1) / G;
+  constexpr int EPL = kRouterEPL;
+  auto stage_rows = [&](__half* dst, const __half* src, int nrows, int row_limit) {
     for (int i = tid; i < nrows * vpr; i += kRouterThreads) {
       const int r = i / vpr, v = i - r * vpr;
-      float f[8];
-      if (r < row_limit && v * 8 < H) cvt8(*reinterpret_cast<const uint4*>(src + (long long)r * H + v * 8), f);
-      else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = 0.f;
-      }
-      stage8(dst + (size_t)r * Hp, v, f);
+      const bool valid = r < row_limit && v * 8 < H;
+      cp_async16(dst + (size_t)r * Hp + v * 8, valid ? (const void*)(src + (long long)r * H + v * 8) : (const void*)src,
+                 valid ? 16u : 0u);
     }
   };
   const bool resident = eg >= E;  // all of W_r stays in shared memory for the CTA's lifetime
   if (resident) stage_rows(sw, Wr, E, E);
+  const int wt = warp / ew, we = warp - wt * ew;
 #pragma unroll 1
   for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
-    const int tbase = grp * kRouterTok;
-    __syncthreads();  // the previous group's token rows have been consumed
-    stage_rows(sx, X + (long long)tbase * H, kRouterTok, T - tbase);
-    float mine[2][EPL];  // logits of experts lane, lane+32, ... for the warp's two tokens
+    const int tbase = grp * G;
+    __syncthreads();  // the previous group's token rows and logits have been consumed
+    stage_rows(sx, X + (long long)tbase * H, G, T - tbase);
+    const uint4* xrow[TT];
 #pragma unroll
-    for (int u = 0; u < 2; ++u)
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) mine[u][i] = -INFINITY;
-    const float4* x0 = reinterpret_cast<const float4*>(sx + (size_t)(2 * warp) * Hp) + lane;
-    const float4* x1 = reinterpret_cast<const float4*>(sx + (size_t)(2 * warp + 1) * Hp) + lane;
+    for (int u = 0; u < TT; ++u) xrow[u] = reinterpret_cast<const uint4*>(sx + (size_t)(wt * TT + u) * Hp) + lane;
 #pragma unroll 1
     for (int g0 = 0; g0 < E; g0 += eg) {
       const int ge = min(eg, E - g0);
@@ -162,59 +154,59 @@ __global__ void __launch_bounds__(kRouterThreads)
         __syncthreads();  // the previous expert rows have been consumed
         stage_rows(sw, Wr + (long long)g0 * H, ge, ge);
       }
+      cp_async_wait_all();
       __syncthreads();
       // four experts at a time in rolled loops (the body runs a few times per warp: keep it small for the
       // instruction cache)
-      constexpr int EG = 4;
+      constexpr int TE = kRouterTE;
 #pragma unroll 1
-      for (int e0 = 0; e0 < ge; e0 += EG) {
-        float acc[2][EG];
+      for (int e0 = we * TE; e0 < ge; e0 += ew * TE) {
+        float acc[TT][TE];
 #pragma unroll
-        for (int e = 0; e < EG; ++e) acc[0][e] = acc[1][e] = 0.f;
+        for (int u = 0; u < TT; ++u)
+#pragma unroll
+          for (int e = 0; e < TE; ++e) acc[u][e] = 0.f;
+        const uint4* wrow[TE];
+#pragma unroll
+        for (int e = 0; e < TE; ++e) wrow[e] = reinterpret_cast<const uint4*>(sw + (size_t)min(e0 + e, ge - 1) * Hp) + lane;
 #pragma unroll 2
         for (int c = 0; c < nchunk; ++c) {
-          const float4 a0 = x0[c * 64], a1 = x0[c * 64 + 32], b0 = x1[c * 64], b1 = x1[c * 64 + 32];
+          float xf[TT][8];
 #pragma unroll
-          for (int e = 0; e < EG; ++e) {
-            const float4* w = reinterpret_cast<const float4*>(sw + (size_t)min(e0 + e, ge - 1) * Hp) + lane + c * 64;
-            const float4 w0 = w[0], w1 = w[32];
-            // ascending k inside the lane
-            acc[0][e] = fmaf(a0.x, w0.x, acc[0][e]); acc[1][e] = fmaf(b0.x, w0.x, acc[1][e]);
-            acc[0][e] = fmaf(a0.y, w0.y, acc[0][e]); acc[1][e] = fmaf(b0.y, w0.y, acc[1][e]);
-            acc[0][e] = fmaf(a0.z, w0.z, acc[0][e]); acc[1][e] = fmaf(b0.z, w0.z, acc[1][e]);
-            acc[0][e] = fmaf(a0.w, w0.w, acc[0][e]); acc[1][e] = fmaf(b0.w, w0.w, acc[1][e]);
-            acc[0][e] = fmaf(a1.x, w1.x, acc[0][e]); acc[1][e] = fmaf(b1.x, w1.x, acc[1][e]);
-            acc[0][e] = fmaf(a1.y, w1.y, acc[0][e]); acc[1][e] = fmaf(b1.y, w1.y, acc[1][e]);
-            acc[0][e] = fmaf(a1.z, w1.z, acc[0][e]); acc[1][e] = fmaf(b1.z, w1.z, acc[1][e]);
-            acc[0][e] = fmaf(a1.w, w1.w, acc[0][e]); acc[1][e] = fmaf(b1.w, w1.w, acc[1][e]);
+          for (int u = 0; u < TT; ++u) cvt8(xrow[u][c * 32], xf[u]);
+#pragma unroll
+          for (int e = 0; e < TE; ++e) {
+            float wf[8];
+            cvt8(wrow[e][c * 32], wf);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)  // ascending k inside the lane
+#pragma unroll
+              for (int u = 0; u < TT; ++u) acc[u][e] = fmaf(xf[u][j], wf[j], acc[u][e]);
           }
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
+        for (int u = 0; u < TT; ++u)
 #pragma unroll
-          for (int e = 0; e < EG; ++e) {
+          for (int e = 0; e < TE; ++e) {
             float v = acc[u][e];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            const int ex = g0 + e0 + e;
-            if (e0 + e < ge && lane == (ex & 31)) {
-#pragma unroll
-              for (int i = 0; i < EPL; ++i)
-                if (i == (ex >> 5)) mine[u][i] = v;
-            }
+            if (lane == 0 && e0 + e < ge) sl[(size_t)(wt * TT + u) * E + g0 + e0 + e] = v;
           }
       }
     }
+    __syncthreads();
 #pragma unroll 1
-    for (int u = 0; u < 2; ++u) {
-      const int t = tbase + 2 * warp + u;
+    for (int tl = warp; tl < G; tl += kRouterWarps) {
+      const int t = tbase + tl;
       if (t >= T) break;
       float lg[EPL];
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) lg[i] = u == 0 ? mine[0][i] : mine[1][i];
+      for (int i = 0; i < EPL; ++i) lg[i] = lane + 32 * i < E ? sl[(size_t)tl * E + lane + 32 * i] : -INFINITY;
       route_one(lg, t, ids, gates, logits_out, T, E, topk, lane);
     }
   }
+  cp_async_wait_all();  // a CTA without any group still has its copy of W_r in flight
 }
 
 // ------------------------------------------------------------------ align
@@ -346,9 +338,11 @@ __global__ void __launch_bounds__(kAlignThreads)
 // ------------------------------------------------------------------ grouped GEMM
 constexpr int kRows = 128;  // weight rows per tile = MMA M
 constexpr int kBK = 64;     // K elements per stage (128 bytes of f16)
+constexpr int kMaxTileM = 256;  // slots per block at most = largest MMA N (needs NW == 1 above 128)
 constexpr int kGatherWarps = 8;
 constexpr int kGatherThreads = kGatherWarps * 32;
-constexpr int kGemmThreads = 64 + kGatherThreads + 128;  // producer + MMA warps, gather warps, 4 epilogue warps
+constexpr int kEpiWarps = 8;  // two per TMEM lane quadrant: they take alternate 16-slot column groups
+constexpr int kGemmThreads = 64 + kGatherThreads + 32 * kEpiWarps;  // producer + MMA warps, gather warps, epilogue warps
 constexpr int kWTile = kRows * kBK * 2;  // 16 KiB
 
 enum Epilogue : int { EPI_F16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
@@ -405,7 +399,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 4);
+      mbar_init(&acc_empty[a], kEpiWarps);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmW);
@@ -520,7 +514,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // byte counts, the chunk's place inside a stage) is computed once per work item.
       const int g = threadIdx.x - 64;  // 0..255
       const int cch = g & 7;           // chunk inside the 128-byte row segment (the same for every copy of the thread)
-      constexpr int kQ = 128 * 8 / kGatherThreads;   // copies per thread and k-block
+      constexpr int kQ = kMaxTileM * 8 / kGatherThreads;   // copies per thread and k-block at most
       constexpr int kRowStep = kGatherThreads / 8;   // block rows between two copies of a thread
       // byte offset of the thread's first chunk inside the B part of a stage: row g/8, 128-byte swizzle
       const uint32_t chunk_off = (uint32_t)((g >> 6) * 1024 + ((g >> 3) & 7) * 128 + ((cch ^ ((g >> 3) & 7)) << 4));
@@ -568,6 +562,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     } else {
       // ---- epilogue
       const int sub = warp & 3;
+      const int half = (warp - (2 + kGatherWarps)) >> 2;  // which of the two 16-column groups of every 32 slots
       const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
       for (int n = 0; n < rn; ++n) {
         if (meta_e[n] < 0) continue;
@@ -577,11 +572,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const int acc = nacc & 1;
         const uint32_t acc_phase = (nacc >> 1) & 1;
         ++nacc;
-        // slot ids and routing weights of the block: lane l holds slots l, l+32, l+64, l+96 (loaded before the wait)
-        int sid[4];
-        float swt[4];
+        // slot ids and routing weights of the block: lane l holds slots l, l+32, ... (loaded before the wait)
+        constexpr int kGroups = kMaxTileM / 32;
+        int sid[kGroups];
+        float swt[kGroups];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < kGroups; ++q) {
           const int slot = q * 32 + lane;
           int id = slot < p.tile_m ? p.sorted_ids[(long long)bm * p.tile_m + slot] : 0;
           if (id < 1 || id > p.total) id = 0;
@@ -598,10 +594,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         const uint32_t taddr = tmem + lane_addr + acc * 256;
         const int row0 = (EPI == EPI_SWIGLU ? nt * kRows : nt * kRowsItem) + sub * 32 + lane;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < (NW == 2 ? 4 : kGroups); ++q) {
           if (q * 32 < ext) {
-#pragma unroll
-            for (int hlf = 0; hlf < 2; ++hlf) {
+            {
+              const int hlf = half;
               const int c0 = q * 32 + hlf * 16;
               if (c0 < ext) {
                 uint32_t ga[16], up[16];
@@ -751,7 +747,10 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
   p.w_tokens = w_tokens; p.w_topk = w_topk;
   p.K = K; p.N = N; p.E = E; p.tile_m = tile_m; p.total = total;
   p.C = C; p.ldc = ldc;
-  const int nw = (epi == EPI_SWIGLU || N >= 2 * kRows) ? 2 : 1;
+  // two 128-row weight tiles per item share one gathered token tile; above 128 slots the accumulator of one
+  // weight tile already fills a TMEM buffer (256 columns)
+  if (epi == EPI_SWIGLU && tile_m > 128) return fail(CTB_UNSUPPORTED_TILE, "moe gemm: SwiGLU epilogue needs tile_m <= 128");
+  const int nw = (epi == EPI_SWIGLU || (N >= 2 * kRows && tile_m <= 128)) ? 2 : 1;
   p.n_tiles = epi == EPI_SWIGLU ? (N + kRows - 1) / kRows : (N + nw * kRows - 1) / (nw * kRows);
   p.stage_bytes = nw * kWTile + tile_m * 128;
   p.stages = std::min(8, (int)((220 * 1024) / p.stage_bytes));
@@ -790,8 +789,8 @@ int launch_align(ctb_ctx* ctx, cudaStream_t st, const void* topk_ids, int ids_bi
 int check_tile(const char* who, int tile_m, int tile_n, int tile_k) {
   if (!is_pow2(tile_m) || !is_pow2(tile_n) || !is_pow2(tile_k))
     return fail(CTB_UNSUPPORTED_TILE, "%s: tile sizes must be powers of two (got %d,%d,%d)", who, tile_m, tile_n, tile_k);
-  if (tile_m < 16 || tile_m > 128)
-    return fail(CTB_UNSUPPORTED_TILE, "%s: tile_m must be between 16 and 128 (got %d)", who, tile_m);
+  if (tile_m < 16 || tile_m > kMaxTileM)
+    return fail(CTB_UNSUPPORTED_TILE, "%s: tile_m must be between 16 and %d (got %d)", who, kMaxTileM, tile_m);
   return CTB_OK;
 }
 
@@ -814,18 +813,36 @@ int ctb_moe_router(ctb_ctx* ctx, void* stream, const void* hidden, const void* W
   if (T == 0) return CTB_OK;
   CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(W_r); CTB_CHECK_DEV(topk_ids); CTB_CHECK_DEV(topk_weights);
   if ((uintptr_t)hidden % 16 || (uintptr_t)W_r % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_router: 16-byte alignment");
-  // shared memory: 16 token rows + eg expert rows, f32, rows padded to a multiple of 256 elements
+  // Group shape: (tokens per warp, token-warps).  Cost model: rounds of groups over the SMs x tokens per group x
+  // shared-memory reads per token-expert block, (TT + 4) / TT.
+  static const int cand[5][2] = {{2, 1}, {2, 2}, {2, 4}, {2, 8}, {4, 8}};
+  int best = 0;
+  double best_cost = 1e300;
+  for (int c = 0; c < 5; ++c) {
+    const int G = cand[c][0] * cand[c][1];
+    const long long groups = (T + G - 1) / G, rounds = (groups + ctx->sm_count - 1) / ctx->sm_count;
+    const double cost = (double)rounds * G * (cand[c][0] + kRouterTE) / cand[c][0];
+    if (cost < best_cost * 0.999) { best_cost = cost; best = c; }
+  }
+  const int TT = cand[best][0], tw = cand[best][1], G = TT * tw;
+  // shared memory: G token rows + eg expert rows as f16, rows padded to a multiple of 256 elements, + G x E logits
   const int64_t Hp = (H + 255) / 256 * 256;
-  const size_t budget = 220 * 1024, rowbytes = (size_t)Hp * 4, xbytes = (size_t)kRouterTok * rowbytes;
-  if (xbytes + 4 * rowbytes > budget) return fail(CTB_UNSUPPORTED, "ctb_moe_router: hidden size %lld too large", (long long)H);
-  const int eg = (int)std::min<size_t>((size_t)E, (budget - xbytes) / rowbytes / 4 * 4);
-  const size_t smem = xbytes + (size_t)eg * rowbytes;
-  cudaError_t ce = cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (ce != cudaSuccess) return cuda_fail(ce, "ctb_moe_router: shared memory opt-in");
-  const int ngroups = (int)((T + kRouterTok - 1) / kRouterTok);
-  moe_router_kernel<<<std::min(ngroups, ctx->sm_count), kRouterThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, topk,
-      eg);
+  const size_t budget = 220 * 1024, rowbytes = (size_t)Hp * 2, fixed = (size_t)G * rowbytes + (size_t)G * E * 4;
+  if (fixed + kRouterTE * rowbytes > budget)
+    return fail(CTB_UNSUPPORTED, "ctb_moe_router: hidden size %lld too large", (long long)H);
+  const int eg = (int)std::min<size_t>((size_t)E, (budget - fixed) / rowbytes / kRouterTE * kRouterTE);
+  const size_t smem = fixed + (size_t)eg * rowbytes;
+  const int ngroups = (int)((T + G - 1) / G);
+  const int grid = std::min(ngroups, ctx->sm_count);
+  cudaError_t ce;
+#define CTB_LAUNCH_ROUTER(TTV)                                                                                  \
+  ce = cudaFuncSetAttribute(moe_router_kernel<TTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+  if (ce != cudaSuccess) return cuda_fail(ce, "ctb_moe_router: shared memory opt-in");                          \
+  moe_router_kernel<TTV><<<grid, kRouterThreads, smem, static_cast<cudaStream_t>(stream)>>>(                    \
+      (const __half*)hidden, (const __half*)W_r, topk_ids, (__half*)topk_weights, logits, (int)T, (int)H, (int)E, \
+      topk, eg, tw);
+  if (TT == 4) { CTB_LAUNCH_ROUTER(4) } else { CTB_LAUNCH_ROUTER(2) }
+#undef CTB_LAUNCH_ROUTER
   CTB_CHECK_LAUNCH("ctb_moe_router launch");
   return CTB_OK;
 }
