@@ -353,14 +353,14 @@ __global__ void __launch_bounds__(kAlignThreads)
 // ------------------------------------------------------------------ grouped GEMM
 constexpr int kRows = 128;  // weight rows per tile = MMA M
 constexpr int kBK = 64;     // K elements per stage (128 bytes of f16)
-constexpr int kMaxTileM = 256;  // slots per block at most = largest MMA N (needs NW == 1 above 128)
+constexpr int kMaxTileM = 128;  // slots per block at most = MMA M
 constexpr int kGatherWarps = 8;
 constexpr int kGatherThreads = kGatherWarps * 32;
-constexpr int kEpiWarps = 8;  // two per TMEM lane quadrant: they take alternate 16-slot column groups
+constexpr int kEpiWarps = 8;  // two per TMEM lane quadrant: each takes half of the output rows of the item
 constexpr int kGemmThreads = 64 + kGatherThreads + 32 * kEpiWarps;  // producer + MMA warps, gather warps, epilogue warps
 constexpr int kWTile = kRows * kBK * 2;  // 16 KiB
 
-enum Epilogue : int { EPI_F16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
+enum Epilogue : int { EPI_F16 = 0, EPI_SWIGLU = 1 };
 
 struct GemmParams {
   const __half* A;        // token rows, K contiguous
@@ -375,7 +375,8 @@ struct GemmParams {
   int replicas, mul_weight;
   int K, N;               // N = output rows per expert (SwiGLU: the weight tensor holds 2N rows)
   int E, tile_m, total;
-  void* C;                // f16 or f32, element (n, id-1) at C[(id-1)*ldc + n]
+  __half* C;              // element (n, id-1) at C[(id-1)*ldc + n]
+  int c_vec;              // 1: columns of C start on 16-byte boundaries (ldc % 8 == 0, aligned base)
   long long ldc;
   int n_tiles, stages, stage_bytes;
 };
@@ -484,14 +485,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!ok) break;
       }
     } else if (warp == 1) {
-      // ---- MMA issuer: the whole warp walks the loop, one elected lane issues
+      // ---- MMA issuer: the whole warp walks the loop, one elected lane issues.
+      // The gathered token tile is the A operand (M = 128 slots = TMEM lanes), the weight tile(s) the B operand
+      // (N = NW * 128 weight rows = accumulator columns): one 128 x N x 16 instruction per k-step.
+      constexpr uint32_t idesc = make_idesc(FMT_F16, kRows, (uint32_t)(NW * kRows), 0, 0);
       for (int n = 0; n < rn && !*abort; ++n) {
         if (meta_e[n] < 0) continue;
-        const int nmma = max(16, (meta_ext[n] + 15) & ~15);
         const int acc = nacc & 1;
         const uint32_t acc_phase = (nacc >> 1) & 1;
         ++nacc;
-        const uint32_t idesc = make_idesc(FMT_F16, kRows, (uint32_t)nmma, 0, 0);
         if (!CTB_WARP_WAIT(&acc_empty[acc], acc_phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
         tc_fence_after();
         const uint32_t d = tmem + acc * 256;
@@ -502,15 +504,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           fence_proxy_async_smem();  // the gathered rows were written through the generic proxy
           tc_fence_after();
           const uint32_t sw = smem_u32(smem + (size_t)stage * p.stage_bytes);
-          const uint32_t sb = sw + wbytes;
+          const uint32_t st = sw + wbytes;
           if (elect_one()) {
 #pragma unroll
-            for (int k = 0; k < kBK / 16; ++k) {
-              const uint64_t bd = make_sdesc_sw128(sb + k * 32, 0, 1024);
-#pragma unroll
-              for (int w = 0; w < NW; ++w)
-                mma_f16_ss(d + w * 128, make_sdesc_sw128(sw + w * kWTile + k * 32, 0, 1024), bd, idesc, (kb | k) != 0);
-            }
+            for (int k = 0; k < kBK / 16; ++k)
+              mma_f16_ss(d, make_sdesc_sw128(st + k * 32, 0, 1024), make_sdesc_sw128(sw + k * 32, 0, 1024), idesc,
+                         (kb | k) != 0);
             tc_commit(&empty[stage]);
           }
           __syncwarp();
@@ -535,7 +534,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const uint32_t chunk_off = (uint32_t)((g >> 6) * 1024 + ((g >> 3) & 7) * 128 + ((cch ^ ((g >> 3) & 7)) << 4));
       for (int n = 0; n < rn; ++n) {
         if (meta_e[n] < 0) continue;
-        const int nmma = max(16, (meta_ext[n] + 15) & ~15);
+        // rows up to the block's extent carry tokens; the others are not copied: whatever they hold only produces
+        // accumulator rows (TMEM lanes) that nobody reads
+        const int nrows = max(16, (meta_ext[n] + 15) & ~15);
         const int it = blockIdx.x + (r0 + n) * gridDim.x;
         const int bm = it / p.n_tiles;
         const __half* src[kQ];  // row q*kRowStep + g/8 of the block; invalid rows read nothing (zero fill)
@@ -545,7 +546,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const int r = q * kRowStep + (g >> 3);
           src[q] = p.A;
           nbytes[q] = 0;
-          if (r < p.tile_m && r < nmma) {
+          if (r < p.tile_m && r < nrows) {
             const int id = p.sorted_ids[(long long)bm * p.tile_m + r];
             if (id >= 1 && id <= p.total) {
               const int tok = (id - 1) / p.replicas;  // cld(id, replicas) - 1
@@ -564,7 +565,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const bool in_k = kb * kBK + cch * 8 < p.K;  // K is a multiple of 8: a chunk is inside or outside as a whole
 #pragma unroll
           for (int q = 0; q < kQ; ++q) {
-            if (q * kRowStep + (g >> 3) < nmma) {  // the same for the whole warp (nmma is a multiple of 16)
+            if (q * kRowStep + (g >> 3) < nrows) {  // the same for the whole warp (nrows is a multiple of 16)
               cp_async16_s(base + q * (kRowStep / 8) * 1024, src[q], in_k ? nbytes[q] : 0u);
               src[q] += kBK;
             }
@@ -575,93 +576,68 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!ok) break;
       }
     } else {
-      // ---- epilogue
+      // ---- epilogue: thread = slot (TMEM lane), accumulator columns = output rows of the item.  The two warps of
+      // a lane quadrant split the columns; a thread's outputs are contiguous in C, so they leave as 16-byte stores.
       const int sub = warp & 3;
-      const int half = (warp - (2 + kGatherWarps)) >> 2;  // which of the two 16-column groups of every 32 slots
+      const int half = (warp - (2 + kGatherWarps)) >> 2;
       const uint32_t lane_addr = (uint32_t)(sub * 32) << 16;
+      const int slot = sub * 32 + lane;
+      constexpr int kOutCols = EPI == EPI_SWIGLU ? kRows : NW * kRows;  // output rows per item
+      constexpr int kMyCols = kOutCols / 2;                            // ... of which this warp writes half
       for (int n = 0; n < rn; ++n) {
         if (meta_e[n] < 0) continue;
-        const int ext = meta_ext[n];
         const int it = blockIdx.x + (r0 + n) * gridDim.x;
         const int bm = it / p.n_tiles, nt = it - bm * p.n_tiles;
         const int acc = nacc & 1;
         const uint32_t acc_phase = (nacc >> 1) & 1;
         ++nacc;
-        // slot ids and routing weights of the block: lane l holds slots l, l+32, ... (loaded before the wait)
-        constexpr int kGroups = kMaxTileM / 32;
-        int sid[kGroups];
-        float swt[kGroups];
-#pragma unroll
-        for (int q = 0; q < kGroups; ++q) {
-          const int slot = q * 32 + lane;
-          int id = slot < p.tile_m ? p.sorted_ids[(long long)bm * p.tile_m + slot] : 0;
-          if (id < 1 || id > p.total) id = 0;
-          sid[q] = id;
-          swt[q] = 1.f;
-          if (p.mul_weight && id) {
-            const int f = id - 1;
-            swt[q] = __half2float(p.topk_w[p.w_tokens ? (long long)(f % p.w_topk) * p.w_tokens + f / p.w_topk : f]);
-          }
+        // slot id and routing weight of this thread's slot (loaded before the wait)
+        int id = slot < p.tile_m ? p.sorted_ids[(long long)bm * p.tile_m + slot] : 0;
+        if (id < 1 || id > p.total) id = 0;
+        float wt = 1.f;
+        if (p.mul_weight && id) {
+          const int f = id - 1;
+          wt = __half2float(p.topk_w[p.w_tokens ? (long long)(f % p.w_topk) * p.w_tokens + f / p.w_topk : f]);
         }
+        __half* crow = p.C + (long long)(id ? id - 1 : 0) * p.ldc;
         bool ok = CTB_WARP_WAIT1(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem + lane_addr + acc * 256;
-        const int row0 = (EPI == EPI_SWIGLU ? nt * kRows : nt * kRowsItem) + sub * 32 + lane;
+        const int n_base = nt * kOutCols + half * kMyCols;
+#pragma unroll 2
+        for (int c = 0; c < kMyCols / 16; ++c) {
+          const int col = half * kMyCols + c * 16;
+          uint32_t ga[16], up[16];
+          tmem_ld16(taddr + col, ga);
+          if (EPI == EPI_SWIGLU) tmem_ld16(taddr + kRows + col, up);
+          tc_wait_ld();
+          uint32_t pk[8];
 #pragma unroll
-        for (int q = 0; q < (NW == 2 ? 4 : kGroups); ++q) {
-          if (q * 32 < ext) {
-            {
-              const int hlf = half;
-              const int c0 = q * 32 + hlf * 16;
-              if (c0 < ext) {
-                uint32_t ga[16], up[16];
-                tmem_ld16(taddr + c0, ga);
-                if (NW == 2) tmem_ld16(taddr + 128 + c0, up);
-                tc_wait_ld();
-                // Three branch-free phases so that the 16 columns overlap: in one loop with a shuffle and an
-                // early-out per column every column waited for its own shuffle -> exp -> reciprocal chain.
-                int idv[16];
-                float wtv[16];
+          for (int j = 0; j < 16; j += 2) {
+            float o0, o1;
+            const float v0 = __uint_as_float(ga[j]), v1 = __uint_as_float(ga[j + 1]);
+            if (EPI == EPI_SWIGLU) {
+              // silu(g) * u with flush-to-zero and an approximate reciprocal (examples/moe.jl:117-124)
+              o0 = v0 * rcp_approx_ftz(1.0f + __expf(-v0)) * __uint_as_float(up[j]);
+              o1 = v1 * rcp_approx_ftz(1.0f + __expf(-v1)) * __uint_as_float(up[j + 1]);
+            } else {
+              o0 = v0 * wt;
+              o1 = v1 * wt;
+            }
+            pk[j >> 1] = pack_f16x2(o0, o1);
+          }
+          const int n0 = n_base + c * 16;
+          if (id) {
+            if (p.c_vec && n0 + 16 <= p.N) {
+              uint4* dst = reinterpret_cast<uint4*>(crow + n0);
+              dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  idv[j] = __shfl_sync(0xffffffffu, sid[q], hlf * 16 + j);
-                  wtv[j] = __shfl_sync(0xffffffffu, swt[q], hlf * 16 + j);
-                }
-                float o0[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const float v0 = __uint_as_float(ga[j]);
-                  if (EPI == EPI_SWIGLU) {
-                    // silu(g) * u with flush-to-zero and an approximate reciprocal (examples/moe.jl:117-124)
-                    o0[j] = v0 * rcp_approx_ftz(1.0f + __expf(-v0)) * __uint_as_float(up[j]);
-                  } else {
-                    o0[j] = v0 * wtv[j];
-                    if (NW == 2) up[j] = __float_as_uint(__uint_as_float(up[j]) * wtv[j]);
-                  }
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const long long col = (long long)(idv[j] - 1) * p.ldc;
-                  if (idv[j] != 0) {
-                    if (EPI == EPI_SWIGLU) {
-                      if (row0 < p.N) reinterpret_cast<__half*>(p.C)[col + row0] = __float2half_rn(o0[j]);
-                    } else {
-#pragma unroll
-                      for (int w = 0; w < NW; ++w) {
-                        const int row = row0 + w * kRows;
-                        const float v = w == 0 ? o0[j] : __uint_as_float(up[j]);
-                        if (row < p.N) {
-                          if (EPI == EPI_F32)
-                            reinterpret_cast<float*>(p.C)[col + row] = v;
-                          else
-                            reinterpret_cast<__half*>(p.C)[col + row] = __float2half_rn(v);
-                        }
-                      }
-                    }
-                  }
-                }
-              }
+              for (int j = 0; j < 16; ++j)
+                if (n0 + j < p.N)
+                  crow[n0 + j] = __ushort_as_half((unsigned short)((j & 1) ? (pk[j >> 1] >> 16) : (pk[j >> 1] & 0xffffu)));
             }
           }
         }
@@ -761,13 +737,13 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
   p.topk_w = topk_w; p.replicas = replicas; p.mul_weight = mul_weight;
   p.w_tokens = w_tokens; p.w_topk = w_topk;
   p.K = K; p.N = N; p.E = E; p.tile_m = tile_m; p.total = total;
-  p.C = C; p.ldc = ldc;
-  // two 128-row weight tiles per item share one gathered token tile; above 128 slots the accumulator of one
-  // weight tile already fills a TMEM buffer (256 columns)
-  if (epi == EPI_SWIGLU && tile_m > 128) return fail(CTB_UNSUPPORTED_TILE, "moe gemm: SwiGLU epilogue needs tile_m <= 128");
-  const int nw = (epi == EPI_SWIGLU || (N >= 2 * kRows && tile_m <= 128)) ? 2 : 1;
+  p.C = (__half*)C; p.ldc = ldc;
+  p.c_vec = (ldc % 8 == 0 && (uintptr_t)C % 16 == 0) ? 1 : 0;
+  // two 128-row weight tiles per item share one gathered token tile (MMA N = 256)
+  const int nw = (epi == EPI_SWIGLU || N >= 2 * kRows) ? 2 : 1;
   p.n_tiles = epi == EPI_SWIGLU ? (N + kRows - 1) / kRows : (N + nw * kRows - 1) / (nw * kRows);
-  p.stage_bytes = nw * kWTile + tile_m * 128;
+  // the token tile is the MMA's A operand with M = 128 rows whatever tile_m is: the instruction reads all of them
+  p.stage_bytes = nw * kWTile + kRows * 128;
   p.stages = std::min(8, (int)((220 * 1024) / p.stage_bytes));
   const size_t smem = (size_t)p.stages * p.stage_bytes + 1024;
   const long long items = (long long)max_blocks * p.n_tiles;
@@ -778,8 +754,6 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
   if (e != cudaSuccess) return cuda_fail(e, "moe gemm: shared memory opt-in");                                \
   moe_gemm_kernel<EPI, NWV><<<grid, kGemmThreads, smem, st>>>(tw, p, ctx->dev_status);
   if (epi == EPI_SWIGLU) { CTB_LAUNCH_MOE(EPI_SWIGLU, 2) }
-  else if (epi == EPI_F32 && nw == 2) { CTB_LAUNCH_MOE(EPI_F32, 2) }
-  else if (epi == EPI_F32) { CTB_LAUNCH_MOE(EPI_F32, 1) }
   else if (nw == 2) { CTB_LAUNCH_MOE(EPI_F16, 2) }
   else { CTB_LAUNCH_MOE(EPI_F16, 1) }
 #undef CTB_LAUNCH_MOE
