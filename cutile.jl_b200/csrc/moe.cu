@@ -391,6 +391,9 @@ __device__ __forceinline__ int block_extent(const int* ids, int tile_m, int tota
   return last;
 }
 
+constexpr int kPassCols = 32;                      // output columns an epilogue thread stages per bulk copy
+constexpr int kStagePitch = kPassCols * 2 + 16;    // bytes between staging rows
+constexpr int kEpiStageBytes = kEpiWarps * 32 * kStagePitch;
 constexpr int kMetaItems = 64;  // work items whose block metadata a CTA caches per round
 
 // EPI: epilogue.  NW: 128-row weight tiles per work item (2 for SwiGLU = gate tile + up tile; 2 for the plain
@@ -584,6 +587,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int slot = sub * 32 + lane;
       constexpr int kOutCols = EPI == EPI_SWIGLU ? kRows : NW * kRows;  // output rows per item
       constexpr int kMyCols = kOutCols / 2;                            // ... of which this warp writes half
+      // this thread's row of its warp's staging tile (rows 16 bytes apart from a multiple of 128: no bank conflicts)
+      unsigned char* stg = smem + (size_t)p.stages * p.stage_bytes +
+                           ((size_t)(warp - (2 + kGatherWarps)) * 32 + lane) * kStagePitch;
       for (int n = 0; n < rn; ++n) {
         if (meta_e[n] < 0) continue;
         const int it = blockIdx.x + (r0 + n) * gridDim.x;
@@ -605,41 +611,52 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         tc_fence_after();
         const uint32_t taddr = tmem + lane_addr + acc * 256;
         const int n_base = nt * kOutCols + half * kMyCols;
-#pragma unroll 2
-        for (int c = 0; c < kMyCols / 16; ++c) {
-          const int col = half * kMyCols + c * 16;
-          uint32_t ga[16], up[16];
-          tmem_ld16(taddr + col, ga);
-          if (EPI == EPI_SWIGLU) tmem_ld16(taddr + kRows + col, up);
-          tc_wait_ld();
-          uint32_t pk[8];
+        // kPassCols outputs at a time: registers -> this thread's row of the staging tile -> one bulk copy to the
+        // slot's row of C.  (Stored straight from registers, 32 lanes hit 32 different rows of C with every
+        // instruction; those scattered stores kept the load/store unit busy for about 2000 clocks per item, during
+        // which the gather's copies and the MMA warp's proxy fence queued up behind them.)
+#pragma unroll 1
+        for (int ps = 0; ps < kMyCols / kPassCols; ++ps) {
+          uint32_t pk[kPassCols / 2];
 #pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            float o0, o1;
-            const float v0 = __uint_as_float(ga[j]), v1 = __uint_as_float(ga[j + 1]);
-            if (EPI == EPI_SWIGLU) {
-              // silu(g) * u with flush-to-zero and an approximate reciprocal (examples/moe.jl:117-124)
-              o0 = v0 * rcp_approx_ftz(1.0f + __expf(-v0)) * __uint_as_float(up[j]);
-              o1 = v1 * rcp_approx_ftz(1.0f + __expf(-v1)) * __uint_as_float(up[j + 1]);
-            } else {
-              o0 = v0 * wt;
-              o1 = v1 * wt;
+          for (int c = 0; c < kPassCols / 16; ++c) {
+            const int col = half * kMyCols + ps * kPassCols + c * 16;
+            uint32_t ga[16], up[16];
+            tmem_ld16(taddr + col, ga);
+            if (EPI == EPI_SWIGLU) tmem_ld16(taddr + kRows + col, up);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              float o0, o1;
+              const float v0 = __uint_as_float(ga[j]), v1 = __uint_as_float(ga[j + 1]);
+              if (EPI == EPI_SWIGLU) {
+                // silu(g) * u with flush-to-zero and an approximate reciprocal (examples/moe.jl:117-124)
+                o0 = v0 * rcp_approx_ftz(1.0f + __expf(-v0)) * __uint_as_float(up[j]);
+                o1 = v1 * rcp_approx_ftz(1.0f + __expf(-v1)) * __uint_as_float(up[j + 1]);
+              } else {
+                o0 = v0 * wt;
+                o1 = v1 * wt;
+              }
+              pk[c * 8 + (j >> 1)] = pack_f16x2(o0, o1);
             }
-            pk[j >> 1] = pack_f16x2(o0, o1);
           }
-          const int n0 = n_base + c * 16;
+          const int n0 = n_base + ps * kPassCols;
+          bulk_wait_read<0>();  // the previous pass's copy has read this thread's staging row
           if (id) {
-            if (p.c_vec && n0 + 16 <= p.N) {
-              uint4* dst = reinterpret_cast<uint4*>(crow + n0);
-              dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-              dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            if (p.c_vec && n0 + kPassCols <= p.N) {
+              uint4* srow = reinterpret_cast<uint4*>(stg);
+#pragma unroll
+              for (int v = 0; v < kPassCols / 8; ++v) srow[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+              fence_proxy_async_smem();
+              bulk_s2g(crow + n0, stg, kPassCols * 2);
             } else {
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
+              for (int j = 0; j < kPassCols; ++j)
                 if (n0 + j < p.N)
                   crow[n0 + j] = __ushort_as_half((unsigned short)((j & 1) ? (pk[j >> 1] >> 16) : (pk[j >> 1] & 0xffffu)));
             }
           }
+          bulk_commit();
         }
         tc_fence_before();
         __syncwarp();
@@ -649,6 +666,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();  // the metadata cache is rewritten in the next round
     if (*abort) break;
   }
+  if (warp >= 2 + kGatherWarps) bulk_wait<0>();  // this thread's output copies are complete
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -744,8 +762,8 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
   p.n_tiles = epi == EPI_SWIGLU ? (N + kRows - 1) / kRows : (N + nw * kRows - 1) / (nw * kRows);
   // the token tile is the MMA's A operand with M = 128 rows whatever tile_m is: the instruction reads all of them
   p.stage_bytes = nw * kWTile + kRows * 128;
-  p.stages = std::min(8, (int)((220 * 1024) / p.stage_bytes));
-  const size_t smem = (size_t)p.stages * p.stage_bytes + 1024;
+  p.stages = std::min(8, (int)((225 * 1024 - kEpiStageBytes) / p.stage_bytes));
+  const size_t smem = (size_t)p.stages * p.stage_bytes + kEpiStageBytes + 1024;
   const long long items = (long long)max_blocks * p.n_tiles;
   const int grid = (int)std::max<long long>(1, std::min<long long>(items, ctx->sm_count));
   cudaError_t e;
