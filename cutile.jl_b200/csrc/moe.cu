@@ -535,31 +535,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       constexpr int kRowStep = kGatherThreads / 8;   // block rows between two copies of a thread
       // byte offset of the thread's first chunk inside the B part of a stage: row g/8, 128-byte swizzle
       const uint32_t chunk_off = (uint32_t)((g >> 6) * 1024 + ((g >> 3) & 7) * 128 + ((cch ^ ((g >> 3) & 7)) << 4));
-      for (int n = 0; n < rn; ++n) {
-        if (meta_e[n] < 0) continue;
+      // The slot ids of an item are fetched while the previous item is being gathered (raw[] holds them), so that
+      // the first copies of an item do not wait for a dependent global load.
+      auto fetch_ids = [&](int n, int (&raw)[kQ]) {
+        const int nrows = max(16, (meta_ext[n] + 15) & ~15);
+        const int bm = (blockIdx.x + (r0 + n) * gridDim.x) / p.n_tiles;
+#pragma unroll
+        for (int q = 0; q < kQ; ++q) {
+          const int r = q * kRowStep + (g >> 3);
+          raw[q] = (r < p.tile_m && r < nrows) ? p.sorted_ids[(long long)bm * p.tile_m + r] : 0;
+        }
+      };
+      auto next_valid = [&](int n) {
+        while (n < rn && meta_e[n] < 0) ++n;
+        return n;
+      };
+      int raw[kQ];
+      int n = next_valid(0);
+      if (n < rn) fetch_ids(n, raw);
+      while (n < rn) {
         // rows up to the block's extent carry tokens; the others are not copied: whatever they hold only produces
         // accumulator rows (TMEM lanes) that nobody reads
         const int nrows = max(16, (meta_ext[n] + 15) & ~15);
-        const int it = blockIdx.x + (r0 + n) * gridDim.x;
-        const int bm = it / p.n_tiles;
         const __half* src[kQ];  // row q*kRowStep + g/8 of the block; invalid rows read nothing (zero fill)
         uint32_t nbytes[kQ];
 #pragma unroll
         for (int q = 0; q < kQ; ++q) {
-          const int r = q * kRowStep + (g >> 3);
           src[q] = p.A;
           nbytes[q] = 0;
-          if (r < p.tile_m && r < nrows) {
-            const int id = p.sorted_ids[(long long)bm * p.tile_m + r];
-            if (id >= 1 && id <= p.total) {
-              const int tok = (id - 1) / p.replicas;  // cld(id, replicas) - 1
-              if (tok < p.a_rows) {
-                src[q] = p.A + (long long)tok * p.lda + cch * 8;
-                nbytes[q] = 16;
-              }
+          const int id = raw[q];
+          if (id >= 1 && id <= p.total) {
+            const int tok = (id - 1) / p.replicas;  // cld(id, replicas) - 1
+            if (tok < p.a_rows) {
+              src[q] = p.A + (long long)tok * p.lda + cch * 8;
+              nbytes[q] = 16;
             }
           }
         }
+        const int n_next = next_valid(n + 1);
+        if (n_next < rn) fetch_ids(n_next, raw);
         bool ok = true;
         for (int kb = 0; kb < nk; ++kb) {
           ok = CTB_WARP_WAIT1(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
@@ -577,6 +591,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (++stage == p.stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
+        n = n_next;
       }
     } else {
       // ---- epilogue: thread = slot (TMEM lane), accumulator columns = output rows of the item.  The two warps of

@@ -132,12 +132,6 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, uin
 __device__ __forceinline__ void cp_async16_s(uint32_t smem_dst, const void* gsrc, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(src_bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-// Waits until at most N of this thread's committed cp.async groups are still in flight.
-template <int N>
-__device__ __forceinline__ void cp_async_wait_group() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // Arrive on `bar` once all cp.async issued so far by this thread have landed
 // (counts against the barrier's initial arrival count).
@@ -161,12 +155,6 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, in
       "[%5];" ::"r"(smem_u32(smem_dst)),
       "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
       : "memory");
-}
-// Brings the box of a tiled tensor into the L2 only (no shared-memory destination, nothing to wait for).  The x
-// coordinate obeys the same 16-byte rule as a load.
-__device__ __forceinline__ void tma_prefetch_l2_3d(const void* tmap, int x, int y, int z) {
-  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(x), "r"(y), "r"(z)
-               : "memory");
 }
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, int x, int y, int z, int w,
                                             uint64_t* bar) {
