@@ -124,7 +124,7 @@ class Softmax(Workload):
     def __init__(self, variant):
         self.variant = variant
         self.name = "softmax_tma" if variant == 0 else "softmax_chunked"
-        self.kernel = "softmax_staged_kernel" if variant == 0 else "softmax_chunk_staged_kernel"
+        self.kernel = "softmax_staged_kernel"
 
     def describe(self):
         return f"row softmax f32 {self.M}x{self.N} N(0,4) seed 1, variant={'single-tile' if self.variant == 0 else 'chunked-online'}"

@@ -7,10 +7,12 @@
 //   with a bulk copy shared->global, so loads and stores of neighbouring rows
 //   overlap the arithmetic of the current one.
 // variant 1 ("chunked", the counterpart of softmax_chunked_kernel, :48-100):
-//   a running (max, sum) per thread over chunks of the row.  Rows that fit a
-//   shared-memory stage arrive chunk by chunk through bulk copies (each chunk
-//   is folded in as it lands); longer or unaligned rows use 128-bit loads and
-//   are kept in registers when they fit (one HBM read), else re-read once.
+//   rows that fit the registers of a CTA and are 16-byte aligned take the
+//   variant-0 kernel (one HBM read, one write; a chunk-by-chunk running
+//   (max, sum) over bulk-copied chunks was measured 1.5x slower because it
+//   evaluates two exponentials per element).  Longer or unaligned rows: a
+//   running (max, sum) per thread over chunks with 128-bit loads, the row kept
+//   in registers when it fits (one HBM read), else re-read once.
 //
 // Both compute in f32 (examples/softmax.jl:32-35,92).  exp(x - max) is evaluated
 // as ex2.approx((x - max)*log2(e)) (relative error about 2^-22 plus the rounding
@@ -178,99 +180,6 @@ __global__ void __launch_bounds__(kThreads) softmax_staged_kernel(T* __restrict_
   if (tid == 0) bulk_wait<0>();  // stores complete before the CTA (and its smem) goes away
 }
 
-// ------------------------------------------------------------------ variant 1, staged
-// Chunked online softmax for rows that fit in a shared-memory stage: the row is
-// fetched as up to kMaxChunks bulk copies, each with its own mbarrier, and every
-// thread folds a chunk into its running (max, sum) as soon as that chunk has
-// landed; after the block-wide combine the row is normalised from registers and
-// leaves through one bulk store.  CE = elements per chunk (a multiple of
-// 4*kThreads so that all threads of a step belong to the same chunk).
-constexpr int kMaxChunks = 8;
-template <typename T, int MAXV, int STAGES>
-__global__ void __launch_bounds__(kThreads)
-    softmax_chunk_staged_kernel(T* __restrict__ out, const T* __restrict__ in, int N, int M, long long ld_out,
-                                long long ld_in, int stage_bytes, int CE, int nchunks, int* status) {
-  using P = typename Pack<T>::type;
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full[STAGES][kMaxChunks];
-  __shared__ float red[kWarps];
-  const int tid = threadIdx.x;
-  const uint32_t row_bytes = (uint32_t)N * sizeof(T);
-  const int npack = N / 4;
-  const int steps_per_chunk = CE / (4 * kThreads);
-
-  if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s)
-      for (int c = 0; c < kMaxChunks; ++c) mbar_init(&full[s][c], 1);
-    fence_mbar_init();
-  }
-  __syncthreads();
-  const int first = blockIdx.x, step = gridDim.x;
-  const int nrows = first < M ? (M - first + step - 1) / step : 0;
-  auto issue = [&](int i, int s) {
-    const T* src = in + (long long)(first + i * step) * ld_in;
-    for (int c = 0; c < nchunks; ++c) {
-      const uint32_t off = (uint32_t)c * CE * sizeof(T);
-      const uint32_t bytes = min((uint32_t)CE * (uint32_t)sizeof(T), row_bytes - off);
-      mbar_expect_tx(&full[s][c], bytes);
-      bulk_g2s(smem + (size_t)s * stage_bytes + off, reinterpret_cast<const unsigned char*>(src) + off, bytes,
-               &full[s][c]);
-    }
-  };
-  if (tid == 0)
-    for (int i = 0; i < STAGES && i < nrows; ++i) issue(i, i);
-
-  for (int i = 0; i < nrows; ++i) {
-    const int s = i % STAGES;
-    const uint32_t parity = (i / STAGES) & 1;
-    P* buf = reinterpret_cast<P*>(smem + (size_t)s * stage_bytes);
-    float x[MAXV][4];
-    float m = -FLT_MAX, l = 0.f;
-    bool alive = true;
-#pragma unroll
-    for (int v = 0; v < MAXV; ++v) {
-      if (v * kThreads < npack) {  // uniform: this step exists
-        if (v % steps_per_chunk == 0) alive = alive && CTB_WARP_WAIT1(&full[s][v / steps_per_chunk], parity, status, DEV_TIMEOUT_TMA);
-        const int p = tid + v * kThreads;
-        if (alive && p < npack) {
-          Pack<T>::unpack(buf[p], x[v]);
-          const float cm = fmaxf(fmaxf(x[v][0], x[v][1]), fmaxf(x[v][2], x[v][3]));
-          if (cm > m) {
-            l *= exp_sub(m, cm);
-            m = cm;
-          }
-          l += (exp_sub(x[v][0], m) + exp_sub(x[v][1], m)) + (exp_sub(x[v][2], m) + exp_sub(x[v][3], m));
-        }
-      }
-    }
-    alive = __syncthreads_and(alive);
-    if (!alive) break;
-    const float mg = block_max(m, red);
-    const float inv = 1.0f / block_sum(l * exp_sub(m, mg), red);
-#pragma unroll
-    for (int v = 0; v < MAXV; ++v) {
-      const int p = tid + v * kThreads;
-      if (p < npack) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) x[v][k] = exp_sub(x[v][k], mg) * inv;
-        buf[p] = Pack<T>::pack(x[v]);
-      }
-    }
-    fence_proxy_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      bulk_s2g(out + (long long)(first + i * step) * ld_out, buf, row_bytes);
-      bulk_commit();
-      const int nxt = i - 1 + STAGES;
-      if (i >= 1 && nxt < nrows) {
-        bulk_wait_read<1>();
-        issue(nxt, (i - 1) % STAGES);
-      }
-    }
-  }
-  if (tid == 0) bulk_wait<0>();
-}
-
 // ------------------------------------------------------------------ variant 1
 // VEC = elements per load (4 => Pack<T>, 1 => scalar).  CACHE = register-resident
 // packs per thread; rows with more are re-read from global for the final pass.
@@ -345,16 +254,20 @@ int launch(ctb_ctx* ctx, cudaStream_t st, T* out, const T* in, int N, int M, lon
            int variant, int tile_size) {
   const bool vec_ok = (N % 4 == 0) && (ldo % 4 == 0) && (ldi % 4 == 0) &&
                       ((uintptr_t)out % (4 * sizeof(T)) == 0) && ((uintptr_t)in % (4 * sizeof(T)) == 0);
-  if (variant == 0) {
-    const size_t row_bytes = (size_t)N * sizeof(T);
-    if (row_bytes % 16 || (uintptr_t)out % 16 || (uintptr_t)in % 16 || (ldo * sizeof(T)) % 16 ||
-        (ldi * sizeof(T)) % 16)
-      return fail(CTB_BAD_ALIGN,
-                  "ctb_softmax variant 0: rows must start on 16-byte boundaries and N*elemsize be a multiple of 16");
-    constexpr int STAGES = 3, MAXV = 8;
-    if (N > 4 * kThreads * MAXV)
-      return fail(CTB_UNSUPPORTED, "ctb_softmax variant 0: N=%d exceeds the single-tile limit %d; use variant 1", N,
-                  4 * kThreads * MAXV);
+  const size_t row_bytes = (size_t)N * sizeof(T);
+  const bool bulk_ok = row_bytes % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)in % 16 == 0 &&
+                       (ldo * sizeof(T)) % 16 == 0 && (ldi * sizeof(T)) % 16 == 0;
+  constexpr int STAGES = 3, MAXV = 8;
+  const bool fits = N <= 4 * kThreads * MAXV;
+  if (variant == 0 && !bulk_ok)
+    return fail(CTB_BAD_ALIGN,
+                "ctb_softmax variant 0: rows must start on 16-byte boundaries and N*elemsize be a multiple of 16");
+  if (variant == 0 && !fits)
+    return fail(CTB_UNSUPPORTED, "ctb_softmax variant 0: N=%d exceeds the single-tile limit %d; use variant 1", N,
+                4 * kThreads * MAXV);
+  if (bulk_ok && fits) {
+    // Both variants: a row that fits the registers of one CTA is read once and written once whatever the chunk
+    // size asks for; the chunk loop of the reference (examples/softmax.jl:48-100) only matters for longer rows.
     const int stage_bytes = (int)((row_bytes + 127) & ~size_t(127));
     const size_t smem = (size_t)STAGES * stage_bytes;
     auto k = softmax_staged_kernel<T, MAXV, STAGES>;
@@ -365,24 +278,6 @@ int launch(ctb_ctx* ctx, cudaStream_t st, T* out, const T* in, int N, int M, lon
     if (per_sm < 1) per_sm = 1;
     const int grid = min(M, ctx->sm_count * per_sm);
     k<<<grid, kThreads, smem, st>>>(out, in, N, M, ldo, ldi, stage_bytes, ctx->dev_status);
-  } else if (vec_ok && ((size_t)N * sizeof(T)) % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)in % 16 == 0 &&
-             (ldo * sizeof(T)) % 16 == 0 && (ldi * sizeof(T)) % 16 == 0 && N <= 4 * kThreads * 8) {
-    // chunked online softmax on rows that fit a shared-memory stage: chunks arrive by bulk copies
-    constexpr int STAGES = 3, MAXV = 8;
-    const int unit = 4 * kThreads;  // elements per step of the CTA
-    int CE = ((std::max(tile_size, (N + kMaxChunks - 1) / kMaxChunks) + unit - 1) / unit) * unit;
-    const int nchunks = (N + CE - 1) / CE;
-    const size_t row_bytes = (size_t)N * sizeof(T);
-    const int stage_bytes = (int)((row_bytes + 127) & ~size_t(127));
-    const size_t smem = (size_t)STAGES * stage_bytes;
-    auto k = softmax_chunk_staged_kernel<T, MAXV, STAGES>;
-    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return cuda_fail(e, "ctb_softmax: shared memory opt-in");
-    int per_sm = 0;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, kThreads, smem);
-    if (per_sm < 1) per_sm = 1;
-    const int grid = min(M, ctx->sm_count * per_sm);
-    k<<<grid, kThreads, smem, st>>>(out, in, N, M, ldo, ldi, stage_bytes, CE, nchunks, ctx->dev_status);
   } else {
     int per_sm = 8;
     const int grid = min(M, ctx->sm_count * per_sm);
