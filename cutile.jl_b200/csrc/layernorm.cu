@@ -1,9 +1,11 @@
 // LayerNorm forward and backward for sm_100a.  All three kernels are HBM-bound.
 //
 // forward (counterpart of layer_norm_fwd, examples/layernorm.jl:27-68):
-//   one read of X; the row lives in registers; mean, then variance of the
-//   centred values (the reference's two-pass formula, :45-54), then
-//   y = (x-mean)*rstd*w+b.  Algorithmic bytes: 2*M*N*4 + 2*N*4 + 2*M*4.
+//   persistent CTAs; each row comes into a ring of shared-memory stages by one
+//   bulk async copy, lives in registers for mean, variance of the centred
+//   values (the reference's two-pass formula, :45-54) and
+//   y = (x-mean)*rstd*w+b, and leaves through a bulk store.
+//   Algorithmic bytes: 2*M*N*4 + 2*N*4 + 2*M*4.
 // backward (layer_norm_bwd_dx_partial_dwdb, :118-171): rows of X and dY are
 //   staged into shared memory by bulk async copies, dX leaves through a bulk
 //   store, and dW/dB accumulate in registers.  The reference serialises the
@@ -43,15 +45,37 @@ __device__ __forceinline__ float block_sum1(float v, float* red) {
   return r;
 }
 
-// Fast path: N % 4 == 0, 16-byte aligned rows, N <= 4*kFwdThreads*NV.
+// Fast path: N % 4 == 0, 16-byte aligned rows, N <= 4*kFwdThreads*NV.  Two-pass variance on centred values as the
+// reference (examples/layernorm.jl:45-54); W and B stay in registers across the CTA's rows.
+// Rows are moved by the bulk-copy engine: persistent CTAs, each row comes into a ring of
+// shared-memory stages by one cp.async.bulk (mbarrier completion), is normalised in registers, written back into its
+// stage and leaves by one bulk copy shared -> global, so the loads and stores of neighbouring rows run under the
+// arithmetic of the current one and no thread waits on its own global loads.
+constexpr int kFwdStages = 3;
 template <int NV>
-__global__ void __launch_bounds__(kFwdThreads) ln_fwd_kernel(const float* __restrict__ X, const float* __restrict__ W,
-                                                             const float* __restrict__ B, float* __restrict__ Y,
-                                                             float* __restrict__ Mean, float* __restrict__ Rstd,
-                                                             int N, int M, long long ldx, long long ldy, float eps) {
+__global__ void __launch_bounds__(kFwdThreads)
+    ln_fwd_staged_kernel(const float* __restrict__ X, const float* __restrict__ W, const float* __restrict__ B,
+                         float* __restrict__ Y, float* __restrict__ Mean, float* __restrict__ Rstd, int N, int M,
+                         long long ldx, long long ldy, float eps, int stage_bytes, int* status) {
+  extern __shared__ __align__(128) unsigned char lsm[];
+  __shared__ __align__(8) uint64_t full[kFwdStages];
   __shared__ float red[kFwdThreads / 32];
   const int tid = threadIdx.x;
   const int npack = N >> 2;
+  const uint32_t row_bytes = (uint32_t)N * 4u;
+  if (tid == 0) {
+    for (int s = 0; s < kFwdStages; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const int first = blockIdx.x, step = gridDim.x;
+  const int nrows = first < M ? (M - first + step - 1) / step : 0;
+  if (tid == 0) {
+    for (int i = 0; i < kFwdStages && i < nrows; ++i) {
+      mbar_expect_tx(&full[i], row_bytes);
+      bulk_g2s(lsm + (size_t)i * stage_bytes, X + (long long)(first + i * step) * ldx, row_bytes, &full[i]);
+    }
+  }
   float4 w[NV], b[NV];
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
@@ -62,20 +86,25 @@ __global__ void __launch_bounds__(kFwdThreads) ln_fwd_kernel(const float* __rest
     }
   }
   const float fn = (float)N;
-  for (int row = blockIdx.x; row < M; row += gridDim.x) {
-    const float4* src = reinterpret_cast<const float4*>(X + (long long)row * ldx);
-    float4* dst = reinterpret_cast<float4*>(Y + (long long)row * ldy);
+  bool alive = true;
+  for (int i = 0; i < nrows && alive; ++i) {
+    const int s = i % kFwdStages;
+    const int row = first + i * step;
+    float4* buf = reinterpret_cast<float4*>(lsm + (size_t)s * stage_bytes);
+    if (!mbar_wait(&full[s], (i / kFwdStages) & 1, status, DEV_TIMEOUT_TMA)) alive = false;
+    alive = __syncthreads_and(alive);
+    if (!alive) break;
     float4 x[NV];
-    float s = 0.f;
+    float sum = 0.f;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
       const int p = tid + v * kFwdThreads;
       if (p < npack) {
-        x[v] = __ldcs(src + p);
-        s += (x[v].x + x[v].y) + (x[v].z + x[v].w);
+        x[v] = buf[p];
+        sum += (x[v].x + x[v].y) + (x[v].z + x[v].w);
       }
     }
-    const float mean = block_sum1<kFwdThreads / 32>(s, red) / fn;
+    const float mean = block_sum1<kFwdThreads / 32>(sum, red) / fn;
     float q = 0.f;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
@@ -99,10 +128,25 @@ __global__ void __launch_bounds__(kFwdThreads) ln_fwd_kernel(const float* __rest
         y.y = x[v].y * rstd * w[v].y + b[v].y;
         y.z = x[v].z * rstd * w[v].z + b[v].z;
         y.w = x[v].w * rstd * w[v].w + b[v].w;
-        __stcs(dst + p, y);
+        buf[p] = y;
+      }
+    }
+    fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk store
+    __syncthreads();
+    if (tid == 0) {
+      bulk_s2g(Y + (long long)row * ldy, buf, row_bytes);
+      bulk_commit();
+      // refill the stage of the PREVIOUS row: its store was committed one iteration ago
+      const int nxt = i - 1 + kFwdStages;
+      if (i >= 1 && nxt < nrows) {
+        bulk_wait_read<1>();
+        const int ps = (i - 1) % kFwdStages;
+        mbar_expect_tx(&full[ps], row_bytes);
+        bulk_g2s(lsm + (size_t)ps * stage_bytes, X + (long long)(first + nxt * step) * ldx, row_bytes, &full[ps]);
       }
     }
   }
+  if (tid == 0) bulk_wait<0>();  // stores complete before the CTA (and its shared memory) goes away
 }
 
 // Any N, any alignment: three passes over the row (the later ones hit L1/L2).
@@ -460,11 +504,24 @@ int ctb_layernorm_fwd(ctb_ctx* ctx, void* stream, const float* X, const float* W
   const int n = (int)N, m = (int)M;
   if (fast) {
     const int nv = (n / 4 + kFwdThreads - 1) / kFwdThreads;
-    const int grid = (int)std::min<int64_t>(M, (int64_t)ctx->sm_count * (nv <= 2 ? 8 : nv <= 4 ? 6 : 3));
-    if (nv <= 1) ln_fwd_kernel<1><<<grid, kFwdThreads, 0, st>>>(X, W, B, Y, Mean, Rstd, n, m, ldx, ldy, eps);
-    else if (nv <= 2) ln_fwd_kernel<2><<<grid, kFwdThreads, 0, st>>>(X, W, B, Y, Mean, Rstd, n, m, ldx, ldy, eps);
-    else if (nv <= 4) ln_fwd_kernel<4><<<grid, kFwdThreads, 0, st>>>(X, W, B, Y, Mean, Rstd, n, m, ldx, ldy, eps);
-    else ln_fwd_kernel<8><<<grid, kFwdThreads, 0, st>>>(X, W, B, Y, Mean, Rstd, n, m, ldx, ldy, eps);
+    const int stage_bytes = (int)(((size_t)n * 4 + 127) & ~size_t(127));
+    const size_t smem = (size_t)kFwdStages * stage_bytes;
+#define CTB_LN_FWD(NVV)                                                                                          \
+  {                                                                                                              \
+    auto k = ln_fwd_staged_kernel<NVV>;                                                                          \
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
+    if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_fwd: shared memory opt-in");                        \
+    int per_sm = 0;                                                                                              \
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, kFwdThreads, smem);                                \
+    if (per_sm < 1) per_sm = 1;                                                                                  \
+    const int grid = (int)std::min<int64_t>(M, (int64_t)ctx->sm_count * per_sm);                                 \
+    k<<<grid, kFwdThreads, smem, st>>>(X, W, B, Y, Mean, Rstd, n, m, ldx, ldy, eps, stage_bytes, ctx->dev_status); \
+  }
+    if (nv <= 1) CTB_LN_FWD(1)
+    else if (nv <= 2) CTB_LN_FWD(2)
+    else if (nv <= 4) CTB_LN_FWD(4)
+    else CTB_LN_FWD(8)
+#undef CTB_LN_FWD
   } else {
     const int grid = (int)std::min<int64_t>(M, (int64_t)ctx->sm_count * 8);
     ln_fwd_generic_kernel<<<grid, kFwdThreads, 0, st>>>(X, W, B, Y, Mean, Rstd, n, m, ldx, ldy, eps);

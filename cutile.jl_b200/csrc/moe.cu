@@ -21,6 +21,7 @@
 //                       (fuses silu_and_mul_kernel, :110-128), or weighted f32.
 //   moe_combine_kernel  sum over the top-k slots of a token (:256).
 // At 256 tokens the FFN is bound by streaming 403 MB of expert weights from HBM.
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include "ctx.h"
@@ -28,6 +29,7 @@
 
 using namespace ctb;
 using namespace ctb_internal;
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -228,20 +230,31 @@ __device__ __forceinline__ unsigned same_value_mask(int v, int bits) {
   return m;
 }
 
+// One thread-block cluster of C CTAs (C = 1 for small batches).  CTA r counts and later scatters the ids
+// [r*chunk, (r+1)*chunk); between the two passes every CTA reads the others' per-expert counts through
+// distributed shared memory and derives the same block layout and its own offset inside every expert's range.
+// A single CTA spent its time issuing instructions for 32 warps on one SM; the cluster spreads that over C SMs.
 template <typename IdT>
 __global__ void __launch_bounds__(kAlignThreads)
     moe_align_kernel(const IdT* __restrict__ topk_ids, int T, int topk, int E, int tile_m,
                      int* __restrict__ sorted_token_ids, int* __restrict__ sorted_expert_ids,
                      int* __restrict__ num_blocks, int capacity_blocks, int* status) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
   extern __shared__ int sm[];
   int* wcount = sm;                       // [kAlignWarps][E]: per-warp counts, then running offsets
   int* estart = sm + kAlignWarps * E;     // [E]: first padded position of expert e
   int* bstart = estart + E;               // [E+1]: first block of expert e
-  __shared__ int bad;
+  int* ctot = bstart + E + 1;             // [E]: ids of expert e in this CTA's range (read by the peers)
+  int* coff = ctot + E;                   // [E]: ids of expert e in the ranges of the CTAs before this one
+  int* etot = coff + E;                   // [E]: ids of expert e over all CTAs
+  __shared__ int bad;                     // read by the peers as well
+  __shared__ int bad_any;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int total = T * topk;
-  const int seg = ((total + kAlignWarps - 1) / kAlignWarps + 31) & ~31;  // ids per warp, multiple of 32
-  const int lo = warp * seg, hi = min(total, lo + seg);
+  const int chunk = ((total + C - 1) / C + kAlignThreads - 1) / kAlignThreads * kAlignThreads;  // ids per CTA
+  const int seg = chunk / kAlignWarps;                                                           // ids per warp
+  const int lo = min(total, rank * chunk + warp * seg), hi = min(total, lo + seg);
   const int niter = lo < hi ? (hi - lo + 31) / 32 : 0;
   int ebits = 1;
   while ((1 << ebits) < E) ++ebits;
@@ -258,8 +271,12 @@ __global__ void __launch_bounds__(kAlignThreads)
     const int i = lo + q * 32 + lane;
     ecache[q] = (q < niter && i < hi) ? expert_of(i) : -1;
   }
-  for (int i = tid; i < capacity_blocks * tile_m; i += kAlignThreads) sorted_token_ids[i] = total + 1;
-  for (int i = tid; i < capacity_blocks; i += kAlignThreads) sorted_expert_ids[i] = 0;
+  if (C == 1) {
+    // a single CTA orders its own writes: everything gets the sentinel now, under the latency of the id loads, and
+    // the scatter at the end overwrites the positions that hold ids
+    for (int i = tid; i < capacity_blocks * tile_m; i += kAlignThreads) sorted_token_ids[i] = total + 1;
+    for (int i = tid; i < capacity_blocks; i += kAlignThreads) sorted_expert_ids[i] = 0;
+  }
   __syncthreads();
 #pragma unroll 1
   for (int q0 = 0; q0 < niter; q0 += kAlignRegIds) {
@@ -280,7 +297,7 @@ __global__ void __launch_bounds__(kAlignThreads)
     }
   }
   __syncthreads();
-  // per expert: exclusive prefix over warps; then an exclusive scan over experts of the block counts (warp 0)
+  // per expert: exclusive prefix over this CTA's warps
   if (tid < E) {
     int run = 0;
     for (int w = 0; w < kAlignWarps; ++w) {
@@ -288,10 +305,27 @@ __global__ void __launch_bounds__(kAlignThreads)
       wcount[w * E + tid] = run;
       run += c;
     }
-    estart[tid] = (run + tile_m - 1) / tile_m;  // blocks of this expert, replaced by the start below
+    ctot[tid] = run;
+  }
+  cluster.sync();  // every CTA's counts (and its `bad`) are in place
+  if (tid < E) {
+    int before = 0, all = 0;
+    for (int k = 0; k < C; ++k) {
+      const int c = cluster.map_shared_rank(ctot, k)[tid];
+      if (k < rank) before += c;
+      all += c;
+    }
+    coff[tid] = before;
+    etot[tid] = all;
+    estart[tid] = (all + tile_m - 1) / tile_m;  // blocks of this expert, replaced by the start below
+  }
+  if (tid == 0) {
+    int any = 0;
+    for (int k = 0; k < C; ++k) any |= *cluster.map_shared_rank(&bad, k);
+    bad_any = any;
   }
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 0) {  // exclusive scan over experts of the block counts (the same in every CTA)
     int carry = 0;
     for (int e0 = 0; e0 < E; e0 += 32) {
       const int e = e0 + lane;
@@ -307,28 +341,47 @@ __global__ void __launch_bounds__(kAlignThreads)
     }
     if (lane == 0) {
       bstart[E] = carry;
-      if (carry > capacity_blocks) bad = 1;
-      *num_blocks = min(carry, capacity_blocks);
+      if (carry > capacity_blocks) bad_any = 1;
+      if (rank == 0) *num_blocks = min(carry, capacity_blocks);
     }
   }
-  __syncthreads();
-  if (bad) {
-    if (tid == 0) {
+  cluster.sync();  // the peers have read this CTA's counts: from here on nobody touches remote shared memory
+  const int gtid = rank * kAlignThreads + tid, gthreads = C * kAlignThreads;
+  if (bad_any) {
+    if (gtid == 0) {
       atomicMax(status, DEV_BAD_INDEX);
       *num_blocks = 0;
     }
+    for (int i = gtid; i < capacity_blocks * tile_m; i += gthreads) sorted_token_ids[i] = total + 1;
+    for (int i = gtid; i < capacity_blocks; i += gthreads) sorted_expert_ids[i] = 0;
     return;
   }
   if (tid < E) estart[tid] = bstart[tid] * tile_m;
-  for (int b = tid; b < bstart[E]; b += kAlignThreads) {  // expert of block b: last e with bstart[e] <= b
+  __syncthreads();
+  auto expert_of_block = [&](int b) {  // last e with bstart[e] <= b
     int l = 0, h = E - 1;
     while (l < h) {
       const int mid = (l + h + 1) >> 1;
       if (bstart[mid] <= b) l = mid; else h = mid - 1;
     }
-    sorted_expert_ids[b] = l + 1;
+    return l;
+  };
+  // One warp per block: its expert id, and the sentinel in every position that no id will be written to (each
+  // position has one writer, so this needs no ordering against the scatter below).
+  const int used_blocks = bstart[E];
+  if (C == 1) {
+    for (int b = tid; b < used_blocks; b += kAlignThreads) sorted_expert_ids[b] = expert_of_block(b) + 1;
+    __syncthreads();  // the early sentinel fill of this CTA is ordered before the scatter
   }
-  __syncthreads();
+  for (int b = rank * kAlignWarps + warp; C > 1 && b < capacity_blocks; b += C * kAlignWarps) {
+    int e = -1, valid = 0;
+    if (b < used_blocks) {
+      e = expert_of_block(b);
+      valid = min(tile_m, max(0, etot[e] - (b - bstart[e]) * tile_m));
+    }
+    if (lane == 0) sorted_expert_ids[b] = e + 1;
+    for (int sl = valid + lane; sl < tile_m; sl += 32) sorted_token_ids[(long long)b * tile_m + sl] = total + 1;
+  }
 #pragma unroll 1
   for (int q0 = 0; q0 < niter; q0 += kAlignRegIds) {
 #pragma unroll
@@ -339,8 +392,8 @@ __global__ void __launch_bounds__(kAlignThreads)
         const int e = q0 == 0 ? ecache[qq] : (i < hi ? expert_of(i) : -1);
         const unsigned grp = same_value_mask(e, ebits);
         if (e >= 0) {
-          const int rank = __popc(grp & ((1u << lane) - 1));
-          sorted_token_ids[estart[e] + wcount[warp * E + e] + rank] = i + 1;
+          const int rk = __popc(grp & ((1u << lane) - 1));
+          sorted_token_ids[estart[e] + coff[e] + wcount[warp * E + e] + rk] = i + 1;
         }
         __syncwarp();
         if (e >= 0 && (grp & ((1u << lane) - 1)) == 0) wcount[warp * E + e] += __popc(grp);
@@ -796,15 +849,30 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
 
 int launch_align(ctb_ctx* ctx, cudaStream_t st, const void* topk_ids, int ids_bits, int T, int topk, int E, int tile_m,
                  int* sorted_token_ids, int* sorted_expert_ids, int* num_blocks, int capacity) {
-  const size_t smem = (size_t)(kAlignWarps * E + 2 * E + 1) * sizeof(int);
+  const size_t smem = (size_t)(kAlignWarps * E + 5 * E + 1) * sizeof(int);
+  const long long total = (long long)T * topk;
+  const int C = total >= 4096 ? 8 : total >= 2048 ? 4 : 1;  // CTAs in the cluster: about 1024 ids each at least
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(C);
+  cfg.blockDim = dim3(kAlignThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = C;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.numAttrs = C > 1 ? 1 : 0;  // a single CTA is launched as an ordinary grid (a cluster of one by default)
+  cudaError_t e;
   if (ids_bits == 32)
-    moe_align_kernel<int><<<1, kAlignThreads, smem, st>>>((const int*)topk_ids, T, topk, E, tile_m, sorted_token_ids,
-                                                          sorted_expert_ids, num_blocks, capacity, ctx->dev_status);
+    e = cudaLaunchKernelEx(&cfg, moe_align_kernel<int>, (const int*)topk_ids, T, topk, E, tile_m, sorted_token_ids,
+                           sorted_expert_ids, num_blocks, capacity, ctx->dev_status);
   else
-    moe_align_kernel<long long><<<1, kAlignThreads, smem, st>>>((const long long*)topk_ids, T, topk, E, tile_m,
-                                                                sorted_token_ids, sorted_expert_ids, num_blocks,
-                                                                capacity, ctx->dev_status);
-  CTB_CHECK_LAUNCH("moe align launch");
+    e = cudaLaunchKernelEx(&cfg, moe_align_kernel<long long>, (const long long*)topk_ids, T, topk, E, tile_m,
+                           sorted_token_ids, sorted_expert_ids, num_blocks, capacity, ctx->dev_status);
+  if (e != cudaSuccess) return cuda_fail(e, "moe align launch");
   return CTB_OK;
 }
 
