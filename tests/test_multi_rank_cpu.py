@@ -16,9 +16,24 @@ dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
 ms = bench.max_over_ranks(10.0 + 5.0 * rank, torch, dist, "cpu")   # rank 1 is the slow one
 val = bench.aggregate_value(1e12, world, ms, "TFLOP/s")            # 1 TFLOP per rank per step
-print(json.dumps({"rank": rank, "ms": ms, "value": val}), flush=True)
+os.write(1, (json.dumps({"rank": rank, "ms": ms, "value": val}) + "\n").encode())  # one write: ranks share the pipe
 dist.destroy_process_group()
 """ % ROOT
+
+
+def _json_rows(text):
+    """Every JSON object in `text`, also when two ranks' lines ran together on the shared pipe."""
+    dec, rows, i = json.JSONDecoder(), [], 0
+    while True:
+        i = text.find("{", i)
+        if i < 0:
+            return rows
+        try:
+            obj, end = dec.raw_decode(text, i)
+            rows.append(obj)
+            i = end
+        except json.JSONDecodeError:
+            i += 1
 
 
 def _torchrun(args, timeout=240):
@@ -33,7 +48,7 @@ def test_time_is_max_over_ranks_and_value_aggregates(tmp_path):
     script.write_text(WORKER)
     r = _torchrun([str(script)])
     assert r.returncode == 0, r.stderr[-2000:]
-    rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    rows = _json_rows(r.stdout)
     assert sorted(x["rank"] for x in rows) == [0, 1]
     for x in rows:
         assert x["ms"] == 15.0                      # the slowest rank's time on every rank
@@ -44,7 +59,7 @@ def test_reference_arm_prints_once_under_torchrun():
     r = _torchrun(["bench.py", "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "1",
                    "--headline", "softmax_tma"])
     assert r.returncode == 0, r.stderr[-2000:]
-    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    lines = _json_rows(r.stdout)
     assert len(lines) == 1
     line = lines[0]
     assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["gpu_launches"] == 0
@@ -56,6 +71,6 @@ def test_expert_parallel_dispatch_plan_world2():
     """Dispatch plan + all-to-all of counts and ids over gloo: every rank receives exactly its experts' slots."""
     r = _torchrun([os.path.join(ROOT, "tests", "ep_worker.py"), "plan"])
     assert r.returncode == 0, r.stderr[-2000:]
-    rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    rows = _json_rows(r.stdout)
     assert sorted(x["rank"] for x in rows) == [0, 1] and all(x["ok"] for x in rows)
     assert sum(x["received"] for x in rows) == 64 * 2  # every slot arrives somewhere, exactly once
