@@ -555,7 +555,29 @@ def cpu_time(w, host, repeats=3):
                 sample=sample + f"; best of {repeats}; {best * 1e3:.1f} ms", host_cpus=os.cpu_count())
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """File descriptor 1 carries exactly one JSON line.  Libraries write there as well (NCCL prints its version
+    banner to stdout while a communicator is set up), so descriptor 1 is pointed at stderr for the rest of the run
+    and the result line goes to a private copy of the original."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    fd = _RESULT_FD if _RESULT_FD is not None else 1
+    sys.stdout.flush()
+    os.write(fd, data)
+
+
 def main():
+    keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -586,7 +608,7 @@ def main():
                     gpu_launches=0,
                     note="CPU restatement of the reference's own CPU check path (numpy float32 + OpenBLAS); the "
                          "reference's GPU path needs Julia and tileiras, which are unavailable on this box")
-        print(json.dumps(line))
+        emit(line)
         return
 
     import torch
@@ -597,8 +619,6 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"  # the version banner goes to stdout, which carries the JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     sampler = ClockSampler(local)
     sampler.start()
@@ -650,7 +670,7 @@ def main():
                                         ms_per_step=r["ms_per_step"], roofline=roof(r, reg[n]), e2e=r.get("e2e"),
                                         cpu_baseline=r.get("cpu_baseline"), parity_err=r["parity_err"],
                                         workload=r["workload"], clocks=r["clocks"])) for n, r in others.items()}
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
 
