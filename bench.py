@@ -510,8 +510,9 @@ def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu
 
 def run_moe_ep(torch, ctb, dist, steps, warmup, rank, world):
     """Expert-parallel MoE at N > 1 (strong scaling): 4096 tokens in total, T/N tokens and 32/N experts per rank,
-    router on the local tokens, NCCL all-to-all dispatch and combine around the local expert FFN.  Eager launches
-    (the split sizes of the all-to-all cross the host), timed with CUDA events, max over ranks."""
+    router on the local tokens, token rows and expert outputs cross NVLink as stores into peer memory issued by the
+    dispatch kernel and by the down projection's epilogue (no all-to-all, no host synchronisation).  Eager
+    launches, timed with CUDA events, max over ranks."""
     import numpy as np
     from oracle import inputs
     T, H, E, I, topk = 4096, 1024, 32, 2048, 2
@@ -525,17 +526,20 @@ def run_moe_ep(torch, ctb, dist, steps, warmup, rank, world):
     w1 = (0.02 * torch.randn(El, 2 * I, H, device="cuda", generator=gw)).half()
     w2 = (0.02 * torch.randn(El, H, I, device="cuda", generator=gw)).half()
 
+    bufs = ctb.moe.EpPeerBuffers(Tl, H, topk, X.device)
+
     def step(i):
         w, ids = ctb.moe.moe_router(X, Wr, topk)
-        return ctb.moe.cutile_moe_ep(X, w1, w2, w, ids, E, 128, 128, 64)
+        return ctb.moe.cutile_moe_ep_peer(bufs, X, w1, w2, w, ids, E, 128, 128, 64)
     ms, _, _ = device_time(torch, dist, step, steps, warmup, graph=False)
     ctb.check_device_status(torch.cuda.current_device())
     per = ms / steps
     flops = 2 * T * topk * H * I * 3
     return dict(metric="moe_ffn_tflops", value=flops / (per * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=per,
                 scaling="strong", workload=f"expert-parallel MoE f16, {T} tokens in total ({Tl} per rank), {El} of {E} "
-                "experts per rank, top-2, NCCL all-to-all dispatch + combine; step = router + dispatch + expert FFN + "
-                "combine", timing="eager launches between two CUDA events (not graph-captured)")
+                "experts per rank, top-2; step = router + dispatch kernel storing token rows into the owners' peer "
+                "memory + barrier + expert FFN whose epilogue stores the outputs into the senders' peer memory + "
+                "barrier + sum over top-k", timing="eager launches between two CUDA events (not graph-captured)")
 
 
 def cpu_time(w, host, repeats=3):

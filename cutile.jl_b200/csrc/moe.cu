@@ -238,7 +238,7 @@ template <typename IdT>
 __global__ void __launch_bounds__(kAlignThreads)
     moe_align_kernel(const IdT* __restrict__ topk_ids, int T, int topk, int E, int tile_m,
                      int* __restrict__ sorted_token_ids, int* __restrict__ sorted_expert_ids,
-                     int* __restrict__ num_blocks, int capacity_blocks, int* status) {
+                     int* __restrict__ num_blocks, int capacity_blocks, int skip_empty, int* status) {
   cg::cluster_group cluster = cg::this_cluster();
   const int C = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
   extern __shared__ int sm[];
@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(kAlignThreads)
         const int i = lo + q * 32 + lane;
         int e = q0 == 0 ? ecache[qq] : (i < hi ? expert_of(i) : -1);
         if (i < hi && (e < 0 || e >= E)) {
-          bad = 1;
+          if (!(skip_empty && e == -1)) bad = 1;  // skip_empty: id 0 marks a slot that belongs to nobody here
           e = -1;
         }
         const unsigned grp = same_value_mask(e, ebits);
@@ -430,6 +430,10 @@ struct GemmParams {
   int E, tile_m, total;
   __half* C;              // element (n, id-1) at C[(id-1)*ldc + n]
   int c_vec;              // 1: columns of C start on 16-byte boundaries (ldc % 8 == 0, aligned base)
+  // Expert-parallel down projection: column id-1 lives on rank (id-1) / c_split, at column (id-1) % c_split of that
+  // rank's buffer c_peer[rank] (an address of peer memory mapped into this process).  c_split == 0: plain C.
+  __half* c_peer[CTB_EP_MAX_RANKS];
+  int c_split;
   long long ldc;
   int n_tiles, stages, stage_bytes;
 };
@@ -673,7 +677,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const int f = id - 1;
           wt = __half2float(p.topk_w[p.w_tokens ? (long long)(f % p.w_topk) * p.w_tokens + f / p.w_topk : f]);
         }
-        __half* crow = p.C + (long long)(id ? id - 1 : 0) * p.ldc;
+        const int col = id ? id - 1 : 0;
+        __half* crow = p.c_split ? p.c_peer[col / p.c_split] + (long long)(col % p.c_split) * p.ldc
+                                 : p.C + (long long)col * p.ldc;
         bool ok = CTB_WARP_WAIT1(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
         if (!ok) break;
         tc_fence_after();
@@ -805,11 +811,49 @@ __global__ void moe_silu_and_mul_kernel(const __half* __restrict__ A, const __ha
   C[col * ldc + r] = __float2half_rn(a * sig * b);
 }
 
+// ------------------------------------------------------------------ expert-parallel dispatch over peer memory
+struct EpPtrs {
+  uint4* rows[CTB_EP_MAX_RANKS];
+  int* ids[CTB_EP_MAX_RANKS];
+  __half* gates[CTB_EP_MAX_RANKS];
+};
+// One warp per slot (token t, choice k): the token row goes straight into the receive buffer of the rank that owns
+// the chosen expert (stores to peer memory, 512 contiguous bytes per warp instruction), at row rank*cap + slot, the
+// position that names its sender; every rank's id array gets the local expert id (owner) or 0 (others) for the
+// slot, so receivers need neither counts nor a cleared buffer.
+__global__ void __launch_bounds__(256)
+    moe_ep_dispatch_kernel(const uint4* __restrict__ X, const int* __restrict__ topk_ids,
+                           const __half* __restrict__ topk_w, const EpPtrs pp, int T, int topk, int vecs, int E, int El,
+                           int world, int rank, int* status) {
+  const int lane = threadIdx.x & 31;
+  const int cap = T * topk;
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
+  for (int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); slot < cap; slot += nwarps) {
+    const int t = slot / topk, k = slot - t * topk;
+    const int e = topk_ids[(long long)k * T + t];
+    const long long row = (long long)rank * cap + slot;
+    int owner = -1, le = 0;
+    if (e >= 1 && e <= E) {
+      owner = (e - 1) / El;
+      le = e - owner * El;
+    } else if (lane == 0) {
+      atomicMax(status, DEV_BAD_INDEX);
+    }
+    if (lane < world) pp.ids[lane][row] = lane == owner ? le : 0;
+    if (owner < 0) continue;
+    if (lane == 0) pp.gates[owner][row] = topk_w[(long long)k * T + t];
+    const uint4* src = X + (long long)t * vecs;
+    uint4* dst = pp.rows[owner] + row * vecs;
+    for (int v = lane; v < vecs; v += 32) dst[v] = src[v];
+  }
+}
+
 // ------------------------------------------------------------------ host side
 int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long long lda, int a_rows, const __half* W,
                 int K, int wrows, int N, int E, const __half* topk_w, const int* sorted_ids, const int* expert_ids,
                 const int* nblocks_dev, int nblocks_host, int max_blocks, int replicas, int mul_weight, int tile_m,
-                int total, void* C, long long ldc, int w_tokens = 0, int w_topk = 1) {
+                int total, void* C, long long ldc, int w_tokens = 0, int w_topk = 1, void* const* c_peer = nullptr,
+                int c_split = 0) {
   CUtensorMap tw;
   uint64_t dims[3] = {(uint64_t)K, (uint64_t)wrows, (uint64_t)E};
   uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)K * wrows * 2};
@@ -825,6 +869,11 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
   p.K = K; p.N = N; p.E = E; p.tile_m = tile_m; p.total = total;
   p.C = (__half*)C; p.ldc = ldc;
   p.c_vec = (ldc % 8 == 0 && (uintptr_t)C % 16 == 0) ? 1 : 0;
+  p.c_split = c_split;
+  for (int q = 0; q < CTB_EP_MAX_RANKS; ++q) {
+    p.c_peer[q] = c_peer ? (__half*)c_peer[q] : nullptr;
+    if (c_split && c_peer && c_peer[q] && (uintptr_t)c_peer[q] % 16) p.c_vec = 0;
+  }
   // two 128-row weight tiles per item share one gathered token tile (MMA N = 256)
   const int nw = (epi == EPI_SWIGLU || N >= 2 * kRows) ? 2 : 1;
   p.n_tiles = epi == EPI_SWIGLU ? (N + kRows - 1) / kRows : (N + nw * kRows - 1) / (nw * kRows);
@@ -848,7 +897,7 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
 }
 
 int launch_align(ctb_ctx* ctx, cudaStream_t st, const void* topk_ids, int ids_bits, int T, int topk, int E, int tile_m,
-                 int* sorted_token_ids, int* sorted_expert_ids, int* num_blocks, int capacity) {
+                 int* sorted_token_ids, int* sorted_expert_ids, int* num_blocks, int capacity, int skip_empty = 0) {
   const size_t smem = (size_t)(kAlignWarps * E + 5 * E + 1) * sizeof(int);
   const long long total = (long long)T * topk;
   const int C = total >= 4096 ? 8 : total >= 2048 ? 4 : 1;  // CTAs in the cluster: about 1024 ids each at least
@@ -868,10 +917,10 @@ int launch_align(ctb_ctx* ctx, cudaStream_t st, const void* topk_ids, int ids_bi
   cudaError_t e;
   if (ids_bits == 32)
     e = cudaLaunchKernelEx(&cfg, moe_align_kernel<int>, (const int*)topk_ids, T, topk, E, tile_m, sorted_token_ids,
-                           sorted_expert_ids, num_blocks, capacity, ctx->dev_status);
+                           sorted_expert_ids, num_blocks, capacity, skip_empty, ctx->dev_status);
   else
     e = cudaLaunchKernelEx(&cfg, moe_align_kernel<long long>, (const long long*)topk_ids, T, topk, E, tile_m,
-                           sorted_token_ids, sorted_expert_ids, num_blocks, capacity, ctx->dev_status);
+                           sorted_token_ids, sorted_expert_ids, num_blocks, capacity, skip_empty, ctx->dev_status);
   if (e != cudaSuccess) return cuda_fail(e, "moe align launch");
   return CTB_OK;
 }
@@ -1036,6 +1085,89 @@ int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, 
   moe_combine_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(slots, (__half*)out, (int)T, (int)H, (int)topk);
   CTB_CHECK_LAUNCH("ctb_moe_ffn combine launch");
   return CTB_OK;
+}
+
+static int check_ep(const char* who, const ctb_ep_buffers* b) {
+  if (!b) return fail(CTB_BAD_ARG, "%s: null buffer table", who);
+  if (b->world < 1 || b->world > CTB_EP_MAX_RANKS || b->rank < 0 || b->rank >= b->world)
+    return fail(CTB_BAD_ARG, "%s: world %d / rank %d out of range (at most %d ranks)", who, b->world, b->rank,
+                CTB_EP_MAX_RANKS);
+  for (int q = 0; q < b->world; ++q) {
+    if (!b->recv_rows[q] || !b->recv_ids[q] || !b->recv_gates[q] || !b->slot_out[q])
+      return fail(CTB_BAD_ARG, "%s: null buffer of rank %d", who, q);
+    if ((uintptr_t)b->recv_rows[q] % 16 || (uintptr_t)b->slot_out[q] % 16)
+      return fail(CTB_BAD_ALIGN, "%s: row buffers of rank %d must be 16-byte aligned", who, q);
+  }
+  return CTB_OK;
+}
+
+int ctb_moe_ep_dispatch(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, const void* hidden,
+                        const int32_t* topk_ids, const void* topk_weights, int64_t T, int64_t H, int64_t E,
+                        int64_t topk) {
+  CTB_CHECK_CTX(ctx);
+  int r = check_ep("ctb_moe_ep_dispatch", bufs);
+  if (r) return r;
+  if (T < 0 || H <= 0 || E <= 0 || topk <= 0 || T * topk > (1 << 24)) return fail(CTB_BAD_ARG, "ctb_moe_ep_dispatch: bad shape");
+  if (E % bufs->world) return fail(CTB_BAD_ARG, "ctb_moe_ep_dispatch: the experts must divide evenly over the ranks");
+  if (H % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_ep_dispatch: H must be a multiple of 8");
+  if (T == 0) return CTB_OK;
+  CTB_CHECK_DEV(hidden); CTB_CHECK_DEV(topk_ids); CTB_CHECK_DEV(topk_weights);
+  if ((uintptr_t)hidden % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_ep_dispatch: 16-byte alignment of hidden");
+  EpPtrs pp;
+  for (int q = 0; q < CTB_EP_MAX_RANKS; ++q) {
+    const bool on = q < bufs->world;
+    pp.rows[q] = on ? (uint4*)bufs->recv_rows[q] : nullptr;
+    pp.ids[q] = on ? bufs->recv_ids[q] : nullptr;
+    pp.gates[q] = on ? (__half*)bufs->recv_gates[q] : nullptr;
+  }
+  const long long cap = T * topk;
+  const int grid = (int)std::min<long long>((cap + 7) / 8, (long long)ctx->sm_count * 8);
+  moe_ep_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const uint4*)hidden, topk_ids, (const __half*)topk_weights, pp, (int)T, (int)topk, (int)(H / 8), (int)E,
+      (int)(E / bufs->world), bufs->world, bufs->rank, ctx->dev_status);
+  CTB_CHECK_LAUNCH("ctb_moe_ep_dispatch launch");
+  return CTB_OK;
+}
+
+int ctb_moe_ep_experts(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, const void* w1_local,
+                       const void* w2_local, int64_t cap, int64_t H, int64_t I, int64_t E_local, int tile_m, int tile_n,
+                       int tile_k) {
+  CTB_CHECK_CTX(ctx);
+  int r = check_ep("ctb_moe_ep_experts", bufs);
+  if (r) return r;
+  r = check_tile("ctb_moe_ep_experts", tile_m, tile_n, tile_k);
+  if (r) return r;
+  const long long R = cap * bufs->world;  // columns of the receive buffers
+  if (cap <= 0 || H <= 0 || I <= 0 || E_local <= 0 || R > (1 << 24)) return fail(CTB_BAD_ARG, "ctb_moe_ep_experts: bad shape");
+  if (E_local > kMaxExperts) return fail(CTB_UNSUPPORTED, "ctb_moe_ep_experts: at most %d local experts", kMaxExperts);
+  if (H % 8 || I % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_ep_experts: hidden and intermediate sizes must be multiples of 8");
+  CTB_CHECK_DEV(w1_local); CTB_CHECK_DEV(w2_local);
+  if ((uintptr_t)w1_local % 16 || (uintptr_t)w2_local % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_ep_experts: 16-byte alignment of the weights");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int me = bufs->rank;
+  const int blocks_cap = (int)ctb_moe_max_blocks(R, 1, E_local, tile_m);
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  const size_t o_tok = 0, o_exp = up((size_t)blocks_cap * tile_m * 4), o_nb = o_exp + up((size_t)blocks_cap * 4),
+               o_act = o_nb + 256, bytes = o_act + up((size_t)R * I * 2);
+  void* ws;
+  r = workspace(ctx, bytes, &ws);
+  if (r) return r;
+  unsigned char* w = (unsigned char*)ws;
+  int* s_tok = (int*)(w + o_tok);
+  int* s_exp = (int*)(w + o_exp);
+  int* s_nb = (int*)(w + o_nb);
+  __half* act = (__half*)(w + o_act);
+  // every received column is one token with a single choice; id 0 = the slot went to another rank
+  r = launch_align(ctx, st, bufs->recv_ids[me], 32, (int)R, 1, (int)E_local, tile_m, s_tok, s_exp, s_nb, blocks_cap,
+                   /*skip_empty=*/1);
+  if (r) return r;
+  r = launch_gemm(ctx, st, EPI_SWIGLU, (const __half*)bufs->recv_rows[me], H, (int)R, (const __half*)w1_local, (int)H,
+                  (int)(2 * I), (int)I, (int)E_local, nullptr, s_tok, s_exp, s_nb, -1, blocks_cap, 1, 0, tile_m,
+                  (int)R, act, I);
+  if (r) return r;
+  return launch_gemm(ctx, st, EPI_F16, act, I, (int)R, (const __half*)w2_local, (int)I, (int)H, (int)H, (int)E_local,
+                     (const __half*)bufs->recv_gates[me], s_tok, s_exp, s_nb, -1, blocks_cap, 1, 1, tile_m, (int)R,
+                     bufs->slot_out[me], H, 0, 1, bufs->slot_out, (int)cap);
 }
 
 int ctb_moe_gather_rows(ctb_ctx* ctx, void* stream, void* dst, const void* src, const int32_t* ids, int64_t n_ids,

@@ -33,6 +33,15 @@ lib = C.CDLL(LIB_PATH)
 
 _p, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 
+EP_MAX_RANKS = 8
+
+
+class EpBuffers(C.Structure):
+    """ctb_ep_buffers: addresses of every rank's receive / output buffers, valid on the calling device."""
+    _fields_ = [("world", _i), ("rank", _i), ("recv_rows", _p * EP_MAX_RANKS), ("recv_ids", _p * EP_MAX_RANKS),
+                ("recv_gates", _p * EP_MAX_RANKS), ("slot_out", _p * EP_MAX_RANKS)]
+
+
 # name -> argument types (return type is int unless listed in _RESTYPES)
 SIGNATURES = {
     "ctb_create": [C.POINTER(_p), _i],
@@ -61,6 +70,8 @@ SIGNATURES = {
     "ctb_moe_scatter_rows": [_p, _p, _p, _p, _p, _i64, _i64, _i64],
     "ctb_moe_combine": [_p, _p, _p, _p, _i64, _i64, _i64],
     "ctb_moe_ffn": [_p, _p, _p, _p, _p, _p, _p, _i, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i],
+    "ctb_moe_ep_dispatch": [_p, _p, C.POINTER(EpBuffers), _p, _p, _p, _i64, _i64, _i64, _i64],
+    "ctb_moe_ep_experts": [_p, _p, C.POINTER(EpBuffers), _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
 }
 _RESTYPES = {"ctb_destroy": None, "ctb_last_error": C.c_char_p, "ctb_status_string": C.c_char_p,
              "ctb_moe_max_blocks": _i64}

@@ -177,3 +177,74 @@ def cutile_moe_ep(hidden_states, w1_local, w2_local, topk_weights, topk_ids, num
     out = torch.empty((T, H), dtype=torch.float16, device=dev)
     _lib.check(_lib.lib.ctb_moe_combine(ctx, stream, ptr(slots), ptr(out), T, H, topk))
     return out
+
+
+class EpPeerBuffers:
+    """Receive and output buffers of the peer-memory expert-parallel path, allocated once per (T_local, H, topk) in
+    symmetric memory (torch.distributed._symmetric_memory: the same allocation on every rank, each rank's copy mapped
+    into every process), so that kernels on one GPU can store straight into another GPU's buffers over NVLink."""
+
+    def __init__(self, T_local, H, topk, device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > _lib.EP_MAX_RANKS:
+            raise _lib.CtbError(_lib.UNSUPPORTED, f"at most {_lib.EP_MAX_RANKS} ranks")
+        self.T, self.H, self.topk = T_local, H, topk
+        self.cap = T_local * topk
+        R = self.cap * self.world
+        self.table = _lib.EpBuffers()
+        self.table.world, self.table.rank = self.world, self.rank
+        self._keep = []
+        for field, shape, dtype in (("recv_rows", (R, H), torch.float16), ("recv_ids", (R,), torch.int32),
+                                    ("recv_gates", (R,), torch.float16), ("slot_out", (self.cap, H), torch.float16)):
+            t = symm.empty(*shape, dtype=dtype, device=device)
+            hdl = symm.rendezvous(t, self.group)
+            self._keep.append((t, hdl))
+            arr = getattr(self.table, field)
+            for q in range(self.world):
+                arr[q] = int(hdl.buffer_ptrs[q])
+            setattr(self, field, t)
+        self._token = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def barrier(self):
+        """Every rank's kernels issued so far have completed before any rank's later kernels start (stream-ordered:
+        a one-element all-reduce on the current stream)."""
+        import torch.distributed as dist
+        dist.all_reduce(self._token, group=self.group)
+
+
+def cutile_moe_ep_peer(bufs, hidden_states, w1_local, w2_local, topk_weights, topk_ids, num_experts, tile_m, tile_n,
+                       tile_k):
+    """Expert-parallel cutile_moe over peer memory.  This rank holds T_local tokens and the expert shard
+    [rank*E/N, (rank+1)*E/N).  Token rows are stored straight into the owning rank's receive buffer by the dispatch
+    kernel (no sort, no counts, no host synchronisation); after a barrier every rank runs align + gate/up + down on
+    what it received, and the down projection's epilogue stores each weighted output row into the buffer of the
+    rank that sent the slot; after a second barrier the slots of every token are summed locally.  Each row crosses
+    NVLink once in each direction.  Returns [T_local, H] f16; bit-identical to cutile_moe on the gathered problem."""
+    ctx, stream = handles(hidden_states)
+    T, H = hidden_states.shape
+    topk = topk_ids.shape[0]
+    El, H2, I = w2_local.shape
+    if (T, H, topk) != (bufs.T, bufs.H, bufs.topk) or H2 != H or w1_local.shape != (El, 2 * I, H):
+        raise _lib.CtbError(_lib.BAD_ARG, "cutile_moe_ep_peer: shapes do not match the buffers")
+    if El * bufs.world != num_experts:
+        raise _lib.CtbError(_lib.BAD_ARG, "cutile_moe_ep_peer: the expert shard must hold E / world experts")
+    if topk_ids.dtype != torch.int32 or topk_weights.dtype != torch.float16 or hidden_states.dtype != torch.float16:
+        raise _lib.CtbError(_lib.BAD_ARG, "cutile_moe_ep_peer: ids must be Int32, gates and tokens Float16")
+    for t in (hidden_states, w1_local, w2_local, topk_weights, topk_ids):
+        if not t.is_contiguous():
+            raise _lib.CtbError(_lib.BAD_ARG, "cutile_moe_ep_peer: arrays must be dense")
+    import ctypes as C
+    tab = C.byref(bufs.table)
+    _lib.check(_lib.lib.ctb_moe_ep_dispatch(ctx, stream, tab, ptr(hidden_states), ptr(topk_ids), ptr(topk_weights), T,
+                                            H, num_experts, topk))
+    bufs.barrier()   # every rank's rows have landed
+    _lib.check(_lib.lib.ctb_moe_ep_experts(ctx, stream, tab, ptr(w1_local), ptr(w2_local), bufs.cap, H, I, El,
+                                           int(tile_m), int(tile_n), int(tile_k)))
+    bufs.barrier()   # every rank's outputs have landed (and nobody reads its receive buffer any more)
+    out = torch.empty((T, H), dtype=torch.float16, device=hidden_states.device)
+    _lib.check(_lib.lib.ctb_moe_combine(ctx, stream, ptr(bufs.slot_out), ptr(out), T, H, topk))
+    return out

@@ -194,6 +194,44 @@ int ctb_moe_scatter_rows(ctb_ctx* ctx, void* stream, void* dst, const void* src,
                          int64_t row_elems, int64_t dst_rows);
 int ctb_moe_combine(ctb_ctx* ctx, void* stream, const void* slots, void* out, int64_t T, int64_t H, int64_t topk);
 
+/* ---- Expert-parallel MoE over peer memory ---------------------------------------- */
+/* The reference's MoE is single-GPU (examples/moe.jl); the sharding (one process per
+ * GPU, experts [r*E/N, (r+1)*E/N) on rank r, tokens sharded by rank) comes from the
+ * benchmark configuration.  Every pointer below is an address that is valid on the
+ * calling device: rank q's buffers are peer memory mapped into this process (NVLink
+ * peer access or a CUDA VMM mapping; the host binding obtains them, e.g. from a
+ * symmetric-memory allocator).  cap = T * topk is the number of slots per rank.
+ *   recv_rows[q] : (H, N*cap) f16 on rank q; column r*cap + s holds the token row of
+ *                  slot s of rank r when the slot's expert lives on q
+ *   recv_ids[q]  : (N*cap) int32 on rank q; the local expert id (1-based) of that
+ *                  column, 0 when the slot belongs to another rank
+ *   recv_gates[q]: (N*cap) f16 routing weights of the columns
+ *   slot_out[q]  : (H, cap) f16 on rank q: the weighted expert outputs of its own
+ *                  slots, summed over topk by ctb_moe_combine
+ * ctb_moe_ep_dispatch: for every local slot writes the token row (the gather half of
+ *   fused_moe_kernel, examples/moe.jl:62-70), its gate and its id entries straight
+ *   into the owners' buffers.  Needs a barrier over the ranks before
+ *   ctb_moe_ep_experts, and another one between ctb_moe_ep_experts and
+ *   ctb_moe_combine(slot_out[rank]) (the host binding's collective library).
+ * ctb_moe_ep_experts : align + gate/up GEMM with SwiGLU + down GEMM of the received
+ *   columns with the local experts; the down projection's epilogue writes each
+ *   weighted output row into slot_out of the rank that sent the slot (the scatter
+ *   half, examples/moe.jl:99-102, as bulk stores to peer memory). */
+#define CTB_EP_MAX_RANKS 8
+typedef struct ctb_ep_buffers {
+  int world, rank;
+  void* recv_rows[CTB_EP_MAX_RANKS];
+  int32_t* recv_ids[CTB_EP_MAX_RANKS];
+  void* recv_gates[CTB_EP_MAX_RANKS];
+  void* slot_out[CTB_EP_MAX_RANKS];
+} ctb_ep_buffers;
+int ctb_moe_ep_dispatch(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, const void* hidden,
+                        const int32_t* topk_ids, const void* topk_weights, int64_t T, int64_t H, int64_t E,
+                        int64_t topk);
+int ctb_moe_ep_experts(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, const void* w1_local,
+                       const void* w2_local, int64_t cap, int64_t H, int64_t I, int64_t E_local, int tile_m, int tile_n,
+                       int tile_k);
+
 /* ---- LayerNorm backward without any allocation --------------------------------- */
 /* No counterpart in the reference.  For callers that cannot obtain device memory
  * at the point where the backward pass runs (a plug-in inside another runtime's

@@ -69,8 +69,18 @@ def main():
         torch.cuda.synchronize()
         ctb.check_device_status(torch.cuda.current_device())
         same = bool(torch.equal(out, full[my]))
-        _emit({"rank": rank, "ok": same})
-        assert same
+        # the same problem through the peer-memory path (stores into the other rank's buffers, no all-to-all);
+        # twice, to cover the reuse of the buffers from one step to the next
+        bufs = ctb.moe.EpPeerBuffers(Tl, H, topk, torch.device("cuda", torch.cuda.current_device()))
+        args = (dev(d["X"][my]), dev(d["w1"][rank * El:(rank + 1) * El]), dev(d["w2"][rank * El:(rank + 1) * El]),
+                dev(w[:, my]), dev(ids[:, my]), E, 128, 128, 64)
+        peer1 = ctb.moe.cutile_moe_ep_peer(bufs, *args)
+        peer2 = ctb.moe.cutile_moe_ep_peer(bufs, *args)
+        torch.cuda.synchronize()
+        ctb.check_device_status(torch.cuda.current_device())
+        same_peer = bool(torch.equal(peer1, full[my])) and bool(torch.equal(peer2, full[my]))
+        _emit({"rank": rank, "ok": same and same_peer, "nccl": same, "peer": same_peer})
+        assert same and same_peer
     dist.destroy_process_group()
 
 

@@ -1,4 +1,5 @@
-"""Expert-parallel MoE on 2 GPUs (NCCL all-to-all dispatch/combine): bit-identical to the single-GPU result.
+"""Expert-parallel MoE on 2 GPUs, both through NCCL all-to-all dispatch/combine and through stores into peer
+memory: bit-identical to the single-GPU result.
 Skipped on a box with fewer than two GPUs."""
 import json
 import os
@@ -21,4 +22,5 @@ def test_moe_ep_matches_single_gpu():
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-2500:]
     rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert all(x.get("peer") for x in rows), rows
     assert sorted(x["rank"] for x in rows) == [0, 1] and all(x["ok"] for x in rows)
