@@ -848,6 +848,37 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Barrier over the ranks (one launch per rank, on different GPUs).  Lane q publishes this rank's new epoch in
+// rank q's flag array and then waits for rank q's epoch in its own array.  The release store follows the kernels
+// that ran before this one on the stream, whose stores to peer memory are complete at that point; the acquire load
+// precedes the kernels after it.  Epochs only grow, so a replayed CUDA graph needs no host-side state.
+struct EpFlags {
+  uint32_t* flags[CTB_EP_MAX_RANKS];
+};
+__global__ void moe_ep_barrier_kernel(const EpFlags f, uint32_t* epoch, int world, int rank, int* status) {
+  const int lane = threadIdx.x;
+  uint32_t e = 0;
+  if (lane == 0) {
+    e = *epoch + 1;
+    *epoch = e;
+  }
+  e = __shfl_sync(0xffffffffu, e, 0);
+  if (lane < world) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f.flags[lane] + rank), "r"(e) : "memory");
+    const uint32_t* mine = f.flags[rank] + lane;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 0;; ++it) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int32_t)(v - e) >= 0) break;
+      if ((it & 255u) == 255u && globaltimer_ns() - t0 > kWaitLimitNs) {
+        atomicMax(status, DEV_TIMEOUT_SLOT);
+        break;
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ host side
 int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long long lda, int a_rows, const __half* W,
                 int K, int wrows, int N, int E, const __half* topk_w, const int* sorted_ids, const int* expert_ids,
@@ -1126,6 +1157,22 @@ int ctb_moe_ep_dispatch(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, 
       (const uint4*)hidden, topk_ids, (const __half*)topk_weights, pp, (int)T, (int)topk, (int)(H / 8), (int)E,
       (int)(E / bufs->world), bufs->world, bufs->rank, ctx->dev_status);
   CTB_CHECK_LAUNCH("ctb_moe_ep_dispatch launch");
+  return CTB_OK;
+}
+
+int ctb_moe_ep_barrier(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs) {
+  CTB_CHECK_CTX(ctx);
+  int r = check_ep("ctb_moe_ep_barrier", bufs);
+  if (r) return r;
+  if (!bufs->epoch) return fail(CTB_BAD_ARG, "ctb_moe_ep_barrier: null epoch counter");
+  EpFlags f;
+  for (int q = 0; q < CTB_EP_MAX_RANKS; ++q) {
+    f.flags[q] = q < bufs->world ? bufs->flags[q] : nullptr;
+    if (q < bufs->world && !f.flags[q]) return fail(CTB_BAD_ARG, "ctb_moe_ep_barrier: null flag array of rank %d", q);
+  }
+  moe_ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, bufs->epoch, bufs->world, bufs->rank,
+                                                                        ctx->dev_status);
+  CTB_CHECK_LAUNCH("ctb_moe_ep_barrier launch");
   return CTB_OK;
 }
 

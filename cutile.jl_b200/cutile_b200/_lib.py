@@ -39,7 +39,8 @@ EP_MAX_RANKS = 8
 class EpBuffers(C.Structure):
     """ctb_ep_buffers: addresses of every rank's receive / output buffers, valid on the calling device."""
     _fields_ = [("world", _i), ("rank", _i), ("recv_rows", _p * EP_MAX_RANKS), ("recv_ids", _p * EP_MAX_RANKS),
-                ("recv_gates", _p * EP_MAX_RANKS), ("slot_out", _p * EP_MAX_RANKS)]
+                ("recv_gates", _p * EP_MAX_RANKS), ("slot_out", _p * EP_MAX_RANKS), ("flags", _p * EP_MAX_RANKS),
+                ("epoch", _p)]
 
 
 # name -> argument types (return type is int unless listed in _RESTYPES)
@@ -71,6 +72,7 @@ SIGNATURES = {
     "ctb_moe_combine": [_p, _p, _p, _p, _i64, _i64, _i64],
     "ctb_moe_ffn": [_p, _p, _p, _p, _p, _p, _p, _i, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i],
     "ctb_moe_ep_dispatch": [_p, _p, C.POINTER(EpBuffers), _p, _p, _p, _i64, _i64, _i64, _i64],
+    "ctb_moe_ep_barrier": [_p, _p, C.POINTER(EpBuffers)],
     "ctb_moe_ep_experts": [_p, _p, C.POINTER(EpBuffers), _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
 }
 _RESTYPES = {"ctb_destroy": None, "ctb_last_error": C.c_char_p, "ctb_status_string": C.c_char_p,

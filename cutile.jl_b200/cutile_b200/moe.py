@@ -199,7 +199,8 @@ class EpPeerBuffers:
         self.table.world, self.table.rank = self.world, self.rank
         self._keep = []
         for field, shape, dtype in (("recv_rows", (R, H), torch.float16), ("recv_ids", (R,), torch.int32),
-                                    ("recv_gates", (R,), torch.float16), ("slot_out", (self.cap, H), torch.float16)):
+                                    ("recv_gates", (R,), torch.float16), ("slot_out", (self.cap, H), torch.float16),
+                                    ("flags", (max(self.world, 4),), torch.int32)):
             t = symm.empty(*shape, dtype=dtype, device=device)
             hdl = symm.rendezvous(t, self.group)
             self._keep.append((t, hdl))
@@ -207,13 +208,17 @@ class EpPeerBuffers:
             for q in range(self.world):
                 arr[q] = int(hdl.buffer_ptrs[q])
             setattr(self, field, t)
-        self._token = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.table.epoch = self.epoch.data_ptr()
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)  # every rank's flags are zero before anyone's first barrier kernel
 
-    def barrier(self):
-        """Every rank's kernels issued so far have completed before any rank's later kernels start (stream-ordered:
-        a one-element all-reduce on the current stream)."""
-        import torch.distributed as dist
-        dist.all_reduce(self._token, group=self.group)
+    def barrier(self, ctx, stream):
+        """Every rank's kernels issued so far have completed before any rank's later kernels start: one small kernel
+        per rank that publishes an epoch in the peers' flag arrays and waits (bounded) for theirs."""
+        import ctypes as C
+        _lib.check(_lib.lib.ctb_moe_ep_barrier(ctx, stream, C.byref(self.table)))
 
 
 def cutile_moe_ep_peer(bufs, hidden_states, w1_local, w2_local, topk_weights, topk_ids, num_experts, tile_m, tile_n,
@@ -241,10 +246,10 @@ def cutile_moe_ep_peer(bufs, hidden_states, w1_local, w2_local, topk_weights, to
     tab = C.byref(bufs.table)
     _lib.check(_lib.lib.ctb_moe_ep_dispatch(ctx, stream, tab, ptr(hidden_states), ptr(topk_ids), ptr(topk_weights), T,
                                             H, num_experts, topk))
-    bufs.barrier()   # every rank's rows have landed
+    bufs.barrier(ctx, stream)   # every rank's rows have landed
     _lib.check(_lib.lib.ctb_moe_ep_experts(ctx, stream, tab, ptr(w1_local), ptr(w2_local), bufs.cap, H, I, El,
                                            int(tile_m), int(tile_n), int(tile_k)))
-    bufs.barrier()   # every rank's outputs have landed (and nobody reads its receive buffer any more)
+    bufs.barrier(ctx, stream)   # every rank's outputs have landed (and nobody reads its receive buffer any more)
     out = torch.empty((T, H), dtype=torch.float16, device=hidden_states.device)
     _lib.check(_lib.lib.ctb_moe_combine(ctx, stream, ptr(bufs.slot_out), ptr(out), T, H, topk))
     return out

@@ -212,7 +212,15 @@ int ctb_moe_combine(ctb_ctx* ctx, void* stream, const void* slots, void* out, in
  *   fused_moe_kernel, examples/moe.jl:62-70), its gate and its id entries straight
  *   into the owners' buffers.  Needs a barrier over the ranks before
  *   ctb_moe_ep_experts, and another one between ctb_moe_ep_experts and
- *   ctb_moe_combine(slot_out[rank]) (the host binding's collective library).
+ *   ctb_moe_combine(slot_out[rank]): ctb_moe_ep_barrier, or any collective of the
+ *   host binding's library.
+ * ctb_moe_ep_barrier : one small kernel per rank: it advances the rank's epoch
+ *   counter, stores the epoch into entry `rank` of every rank's flag array
+ *   (flags[q], N uint32 each, zero before the first use) and waits until all N
+ *   entries of its own array have reached the epoch.  The wait is bounded (2 s);
+ *   when it runs out the kernel records CTB_TIMEOUT in the context's status word
+ *   and returns.  Stream-ordered and free of host state, so it can be captured in
+ *   a CUDA graph and replayed.
  * ctb_moe_ep_experts : align + gate/up GEMM with SwiGLU + down GEMM of the received
  *   columns with the local experts; the down projection's epilogue writes each
  *   weighted output row into slot_out of the rank that sent the slot (the scatter
@@ -224,10 +232,13 @@ typedef struct ctb_ep_buffers {
   int32_t* recv_ids[CTB_EP_MAX_RANKS];
   void* recv_gates[CTB_EP_MAX_RANKS];
   void* slot_out[CTB_EP_MAX_RANKS];
+  uint32_t* flags[CTB_EP_MAX_RANKS]; /* barrier flags of every rank (peer memory), N entries each */
+  uint32_t* epoch;                   /* this rank's barrier counter (one uint32 in its own memory) */
 } ctb_ep_buffers;
 int ctb_moe_ep_dispatch(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, const void* hidden,
                         const int32_t* topk_ids, const void* topk_weights, int64_t T, int64_t H, int64_t E,
                         int64_t topk);
+int ctb_moe_ep_barrier(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs);
 int ctb_moe_ep_experts(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, const void* w1_local,
                        const void* w2_local, int64_t cap, int64_t H, int64_t I, int64_t E_local, int tile_m, int tile_n,
                        int tile_k);
