@@ -210,4 +210,36 @@ function layer_norm_bwd_static(DX, DY, X, W, Mean, Rstd, FINAL_DW, FINAL_DB)
         N, M, stride(X, 2), stride(DY, 2), stride(DX, 2)))
 end
 
+# ---- expert-parallel MoE over peer memory (one process per GPU) ----
+# Mirrors `ctb_ep_buffers`: addresses of every rank's buffers, valid on the calling device (the host obtains them from
+# a symmetric-memory allocator or from CUDA IPC / VMM mappings).
+struct EpBuffers
+    world::Cint
+    rank::Cint
+    recv_rows::NTuple{8,Ptr{Cvoid}}
+    recv_ids::NTuple{8,Ptr{Cvoid}}
+    recv_gates::NTuple{8,Ptr{Cvoid}}
+    slot_out::NTuple{8,Ptr{Cvoid}}
+    flags::NTuple{8,Ptr{Cvoid}}
+    epoch::Ptr{Cvoid}
+end
+
+function moe_ep_dispatch(bufs::EpBuffers, hidden_states::CuArray{Float16,2}, topk_ids::CuArray{Int32,2},
+                         topk_weights::CuArray{Float16,2}, num_experts::Int)
+    H, T = size(hidden_states); topk = size(topk_ids, 2)
+    check(ccall((:ctb_moe_ep_dispatch, LIB), Cint,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ref{EpBuffers}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int64, Int64, Int64, Int64),
+        context(), stream(), Ref(bufs), dptr(hidden_states), dptr(topk_ids), dptr(topk_weights), T, H, num_experts, topk))
+end
+
+moe_ep_barrier(bufs::EpBuffers) =
+    check(ccall((:ctb_moe_ep_barrier, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}, Ref{EpBuffers}), context(), stream(), Ref(bufs)))
+
+function moe_ep_experts(bufs::EpBuffers, w1_local, w2_local, cap::Int, tile_m::Int, tile_n::Int, tile_k::Int)
+    I, H, El = size(w2_local)
+    check(ccall((:ctb_moe_ep_experts, LIB), Cint,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ref{EpBuffers}, Ptr{Cvoid}, Ptr{Cvoid}, Int64, Int64, Int64, Int64, Cint, Cint, Cint),
+        context(), stream(), Ref(bufs), dptr(w1_local), dptr(w2_local), cap, H, I, El, tile_m, tile_n, tile_k))
+end
+
 end # module
