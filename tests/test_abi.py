@@ -53,3 +53,18 @@ def test_null_context_and_host_arrays_rejected():
     with pytest.raises(cutile_b200.CtbError) as e:  # host array, like the reference's ArgumentError
         cutile_b200.softmax.softmax_tma_kernel(np.zeros((2, 4), np.float32), np.zeros((2, 4), np.float32), 4)
     assert e.value.status == _lib.BAD_ARG
+
+
+def test_expert_parallel_entry_points_validate_their_table():
+    """The peer-memory MoE entry points reject a missing context, a missing buffer table and out-of-range ranks
+    before touching any device (host-side checks only; the compute path is covered by the 2-GPU test)."""
+    from cutile_b200 import _lib
+    tab = _lib.EpBuffers()
+    tab.world, tab.rank = 2, 0
+    st = _lib.lib.ctb_moe_ep_dispatch(None, None, ctypes.byref(tab), None, None, None, 8, 64, 8, 2)
+    assert st == _lib.BAD_ARG and "null context" in _lib.last_error()
+    st = _lib.lib.ctb_moe_ep_barrier(None, None, ctypes.byref(tab))
+    assert st == _lib.BAD_ARG
+    st = _lib.lib.ctb_moe_ep_experts(None, None, ctypes.byref(tab), None, None, 16, 64, 128, 4, 128, 128, 64)
+    assert st == _lib.BAD_ARG
+    assert ctypes.sizeof(_lib.EpBuffers) == 8 + 5 * 8 * _lib.EP_MAX_RANKS + 8  # layout of ctb_ep_buffers
