@@ -36,29 +36,74 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples the SM clock and the clock-event reasons while the timed regions run (read-only queries).  NVML is
+    polled from a thread every 2 ms when the Python binding is there (timed regions of this suite last 5-50 ms);
+    otherwise `nvidia-smi -lms 100` is read, the query of the profiling recipe."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
-        self.rows = []
+        self.rows = []          # (time, sm_mhz, max_mhz, set of reasons)
         self.proc = None
+        self.source = None
+        self._stop = threading.Event()
 
     def start(self):
         try:
+            import pynvml as nv
+            nv.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = self.gpu
+            if vis:
+                ids = [v for v in vis.split(",") if v.strip() != ""]
+                if self.gpu < len(ids) and ids[self.gpu].strip().isdigit():
+                    phys = int(ids[self.gpu])
+            h = nv.nvmlDeviceGetHandleByIndex(phys)
+            mx = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            names = (("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown),
+                     ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown),
+                     ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap))
+
+            def poll():
+                while not self._stop.is_set():
+                    try:
+                        mhz = float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                        bits = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                        self.rows.append((time.time(), mhz, mx, {n for n, b in names if bits & b}))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)  # raises here if the query is not supported
+            self.source = "nvml, 2 ms"
+            threading.Thread(target=poll, daemon=True).start()
+            return
+        except Exception:
+            pass
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.source = "nvidia-smi, 100 ms"
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                reasons = {n for n, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                                            ("sw_power_cap", 8)) if c[col].lower().startswith("active")}
+                self.rows.append((time.time(), float(c[1]), float(c[2]), reasons))
+            except ValueError:
+                pass
 
     def stop(self):
+        self._stop.set()
         if self.proc:
             self.proc.terminate()
             try:
@@ -67,19 +112,16 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self, t0, t1):
-        rows = [r for t, r in self.rows if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 9] or \
-               [r for _, r in self.rows if len(r) >= 9]
+        inside = [r for r in self.rows if t0 <= r[0] <= t1]
+        rows = inside or [r for r in self.rows if t0 - 0.05 <= r[0] <= t1 + 0.15] or list(self.rows)
         if not rows:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        sm = sorted(float(r[1]) for r in rows)
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock query unavailable"]}
+        sm = sorted(r[1] for r in rows)
         reasons = set()
         for r in rows:
-            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
-                              ("sw_power_cap", 8)):
-                if r[col].lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons),
-                "samples": len(rows)}
+            reasons |= r[3]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_min_mhz": sm[0], "sm_max_mhz": rows[0][2], "reasons": sorted(reasons),
+                "samples": len(rows), "samples_inside_timed_region": len(inside), "source": self.source}
 
 
 # --------------------------------------------------------------------------- workloads
