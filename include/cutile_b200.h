@@ -68,7 +68,9 @@ int ctb_check_device_status(ctb_ctx* ctx, void* stream);
  * input/output (N, M): M rows of N contiguous elements, row stride ld.
  * variant 0: whole row staged in shared memory by bulk async copies (needs
  *            tile_size >= N, N*elemsize % 16 == 0, 16-byte aligned rows);
- * variant 1: chunks of tile_size with running max/sum (any N).
+ * variant 1: any N; tile_size is advisory: rows that qualify for variant 0's
+ *            kernel (N <= 8192, aligned) take it, longer or unaligned rows run
+ *            chunks with a running max/sum per thread.
  * dtype: CTB_F32 or CTB_F16 (computes in f32, like the reference). */
 int ctb_softmax(ctb_ctx* ctx, void* stream, void* output, const void* input, int64_t N, int64_t M, int64_t ld_out,
                 int64_t ld_in, int variant, int tile_size, int dtype);
