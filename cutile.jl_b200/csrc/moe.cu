@@ -490,11 +490,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const uint32_t tmem = tmem_base_s;
   volatile int* abort = &abort_s;
   const int nblocks = p.num_blocks_host >= 0 ? p.num_blocks_host : *p.num_blocks_dev;
-  const int items = nblocks * p.n_tiles;
+  const int base_items = nblocks * p.n_tiles;
+  // Work items [0, split_from) are whole (block, NW weight tiles) pairs; item split_from + q is weight tile q & 1 of
+  // pair split_from + q / 2.  The pairs of a last, less than half-filled round over the CTAs are handed out as
+  // single tiles, so that the round costs about half an item instead of a whole one (320 pairs on 148 SMs are the
+  // down projection at 4096 tokens: 2.6 rounds instead of 3).
+  int split_from = base_items;
+  if (EPI == EPI_F16 && NW == 2) {
+    const int rest = base_items % (int)gridDim.x;
+    if (rest > 0 && base_items > (int)gridDim.x && 2 * rest <= (int)gridDim.x) split_from = base_items - rest;
+  }
+  const int items = base_items + (base_items - split_from);
   const int my_items = (int)blockIdx.x < items ? (items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int nk = (p.K + kBK - 1) / kBK;
-  constexpr int wbytes = NW * kWTile;
+  constexpr int wbytes = NW * kWTile;    // offset of the token tile inside a stage
   constexpr int kRowsItem = NW * kRows;  // for SwiGLU: 128 gate rows + the matching 128 up rows
+  // item index -> block, weight-tile pair, first weight tile inside the pair and number of weight tiles
+  auto decode = [&](int it, int& bm, int& nt, int& w0, int& nw) {
+    int pair = it;
+    w0 = 0;
+    nw = NW;
+    if (it >= split_from) {
+      const int q = it - split_from;
+      pair = split_from + (q >> 1);
+      w0 = q & 1;
+      nw = 1;
+    }
+    bm = pair / p.n_tiles;
+    nt = pair - bm * p.n_tiles;
+  };
 
   // pipeline state of each role persists across rounds
   int stage = 0, nacc = 0;
@@ -504,8 +528,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     const int rn = min(kMetaItems, my_items - r0);
     // ---- every warp: cache the metadata of this round's items (global-load latency paid once, in parallel)
     for (int n = warp; n < rn; n += kGemmThreads / 32) {
-      const int it = blockIdx.x + (r0 + n) * gridDim.x;
-      const int bm = it / p.n_tiles;
+      int bm, nt_, w0_, nw_;
+      decode(blockIdx.x + (r0 + n) * gridDim.x, bm, nt_, w0_, nw_);
       int e = p.expert_ids[bm] - 1;
       if (e < 0 || e >= p.E) e = -1;
       const int ext = block_extent(p.sorted_ids + (long long)bm * p.tile_m, p.tile_m, p.total, lane);
@@ -521,22 +545,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       for (int n = 0; n < rn && !*abort; ++n) {
         const int e = meta_e[n];
         if (e < 0) continue;
-        const int it = blockIdx.x + (r0 + n) * gridDim.x;
-        const int nt = it % p.n_tiles;
+        int bm_, nt, w0, nw;
+        decode(blockIdx.x + (r0 + n) * gridDim.x, bm_, nt, w0, nw);
         bool ok = true;
         for (int kb = 0; kb < nk; ++kb) {
           ok = CTB_WARP_WAIT(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
           if (!ok) break;
           unsigned char* dst = smem + (size_t)stage * p.stage_bytes;
           if (elect_one()) {
-            mbar_expect_tx(&full[stage], wbytes);
+            mbar_expect_tx(&full[stage], nw * kWTile);
             if (EPI == EPI_SWIGLU) {
               tma_load_3d(dst, &tmW, kb * kBK, nt * kRows, e, &full[stage]);
               tma_load_3d(dst + kWTile, &tmW, kb * kBK, p.N + nt * kRows, e, &full[stage]);
             } else {
 #pragma unroll
               for (int w = 0; w < NW; ++w)
-                tma_load_3d(dst + w * kWTile, &tmW, kb * kBK, nt * kRowsItem + w * kRows, e, &full[stage]);
+                if (w < nw) tma_load_3d(dst + w * kWTile, &tmW, kb * kBK, nt * kRowsItem + (w0 + w) * kRows, e, &full[stage]);
             }
           }
           __syncwarp();
@@ -548,9 +572,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // ---- MMA issuer: the whole warp walks the loop, one elected lane issues.
       // The gathered token tile is the A operand (M = 128 slots = TMEM lanes), the weight tile(s) the B operand
       // (N = NW * 128 weight rows = accumulator columns): one 128 x N x 16 instruction per k-step.
-      constexpr uint32_t idesc = make_idesc(FMT_F16, kRows, (uint32_t)(NW * kRows), 0, 0);
+      constexpr uint32_t idesc_pair = make_idesc(FMT_F16, kRows, (uint32_t)(NW * kRows), 0, 0);
+      constexpr uint32_t idesc_one = make_idesc(FMT_F16, kRows, (uint32_t)kRows, 0, 0);
       for (int n = 0; n < rn && !*abort; ++n) {
         if (meta_e[n] < 0) continue;
+        const uint32_t idesc = (int)(blockIdx.x + (r0 + n) * gridDim.x) >= split_from ? idesc_one : idesc_pair;
         const int acc = nacc & 1;
         const uint32_t acc_phase = (nacc >> 1) & 1;
         ++nacc;
@@ -596,7 +622,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       // the first copies of an item do not wait for a dependent global load.
       auto fetch_ids = [&](int n, int (&raw)[kQ]) {
         const int nrows = max(16, (meta_ext[n] + 15) & ~15);
-        const int bm = (blockIdx.x + (r0 + n) * gridDim.x) / p.n_tiles;
+        int bm, nt_, w0_, nw_;
+        decode(blockIdx.x + (r0 + n) * gridDim.x, bm, nt_, w0_, nw_);
 #pragma unroll
         for (int q = 0; q < kQ; ++q) {
           const int r = q * kRowStep + (g >> 3);
@@ -664,8 +691,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                            ((size_t)(warp - (2 + kGatherWarps)) * 32 + lane) * kStagePitch;
       for (int n = 0; n < rn; ++n) {
         if (meta_e[n] < 0) continue;
-        const int it = blockIdx.x + (r0 + n) * gridDim.x;
-        const int bm = it / p.n_tiles, nt = it - bm * p.n_tiles;
+        int bm, nt, w0, nw;
+        decode(blockIdx.x + (r0 + n) * gridDim.x, bm, nt, w0, nw);
+        // output columns this warp writes: half of the item's (a single-tile item has half the columns of a pair)
+        const int my_cols = EPI == EPI_SWIGLU ? kMyCols : nw * (kRows / 2);
         const int acc = nacc & 1;
         const uint32_t acc_phase = (nacc >> 1) & 1;
         ++nacc;
@@ -684,17 +713,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         if (!ok) break;
         tc_fence_after();
         const uint32_t taddr = tmem + lane_addr + acc * 256;
-        const int n_base = nt * kOutCols + half * kMyCols;
+        const int n_base = nt * kOutCols + w0 * kRows + half * my_cols;
         // kPassCols outputs at a time: registers -> this thread's row of the staging tile -> one bulk copy to the
         // slot's row of C.  (Stored straight from registers, 32 lanes hit 32 different rows of C with every
         // instruction; those scattered stores kept the load/store unit busy for about 2000 clocks per item, during
         // which the gather's copies and the MMA warp's proxy fence queued up behind them.)
 #pragma unroll 1
-        for (int ps = 0; ps < kMyCols / kPassCols; ++ps) {
+        for (int ps = 0; ps < my_cols / kPassCols; ++ps) {
           uint32_t pk[kPassCols / 2];
 #pragma unroll
           for (int c = 0; c < kPassCols / 16; ++c) {
-            const int col = half * kMyCols + ps * kPassCols + c * 16;
+            const int col = half * my_cols + ps * kPassCols + c * 16;
             uint32_t ga[16], up[16];
             tmem_ld16(taddr + col, ga);
             if (EPI == EPI_SWIGLU) tmem_ld16(taddr + kRows + col, up);
