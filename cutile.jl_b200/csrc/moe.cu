@@ -92,7 +92,7 @@ __device__ __forceinline__ void route_one(float (&mine)[kRouterEPL], int t, int*
   }
 }
 
-constexpr int kRouterWarps = 8;
+constexpr int kRouterWarps = 16;  // four per scheduler: the logit loop is latency-bound with fewer
 constexpr int kRouterThreads = kRouterWarps * 32;
 constexpr int kMaxRouterE = 256;
 constexpr int kRouterTE = 4;  // experts a warp carries through the hidden dimension at a time
@@ -107,7 +107,7 @@ __device__ __forceinline__ void cvt8(const uint4& u, float* f) {
   }
 }
 
-// A CTA works on groups of G = TT * tw tokens.  Its 8 warps form tw token-warps x ew expert-warps (tw * ew = 8):
+// A CTA works on groups of G = TT * tw tokens.  Its 16 warps form tw token-warps x ew expert-warps (tw * ew = 16):
 // a warp owns TT tokens and every ew-th block of four experts, computes those logits in the fixed order (lane l
 // = partial sum l, its 8 elements of each 256-chunk are one 16-byte shared-memory read, conflict-free without any
 // permutation) and leaves them in shared memory; after a barrier the warps take the group's tokens in turn for
