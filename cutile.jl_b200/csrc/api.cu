@@ -53,6 +53,11 @@ int workspace(ctb_ctx* ctx, size_t bytes, void** out) {
   return CTB_OK;
 }
 
+int* sched_slot(ctb_ctx* ctx) {
+  const unsigned n = __atomic_fetch_add(&ctx->sched_next, 1u, __ATOMIC_RELAXED);
+  return ctx->sched_pool + 2 * (n % kSchedSlots);
+}
+
 EncodeTiledFn encode_tiled() {
   static EncodeTiledFn fn = nullptr;
   static std::once_flag once;
@@ -122,9 +127,12 @@ int ctb_create(ctb_ctx** out, int device) {
   c->cc_minor = p.minor;
   c->workspace = nullptr;
   c->workspace_bytes = 0;
-  c->nccl = nullptr;
+  c->sched_pool = nullptr;
+  c->sched_next = 0;
   e = cudaMalloc(&c->dev_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(c->dev_status, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(&c->sched_pool, 2 * kSchedSlots * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(c->sched_pool, 0, 2 * kSchedSlots * sizeof(int));
   if (e != cudaSuccess) {
     delete c;
     return cuda_fail(e, "ctb_create: status word");
@@ -138,6 +146,7 @@ void ctb_destroy(ctb_ctx* ctx) {
   cudaSetDevice(ctx->device);
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->sched_pool) cudaFree(ctx->sched_pool);
   delete ctx;
 }
 

@@ -16,7 +16,11 @@ struct ctb_ctx {
   int* dev_status;        // one int in device memory; kernels atomicMax error codes into it
   void* workspace;        // grown on demand (ctb_internal::workspace)
   size_t workspace_bytes;
-  void* nccl;             // ctb_internal::Comm* when a communicator is attached
+  // Work counters of kernels that hand out work items dynamically: kSchedSlots pairs of ints, zero between
+  // launches (the last CTA of a launch clears its pair).  Launches take the pairs in turn, so that launches
+  // that overlap on the device (different streams) do not share one.
+  int* sched_pool;
+  unsigned sched_next;
 };
 
 namespace ctb_internal {
@@ -28,6 +32,9 @@ bool is_pow2(long long v);
 bool is_device_ptr(const void* p);
 // Returns ctx scratch of at least `bytes` (may reallocate => synchronises the device).
 int workspace(ctb_ctx* ctx, size_t bytes, void** out);
+constexpr int kSchedSlots = 256;
+// The next pair of work counters of the context (see ctb_ctx::sched_pool).
+int* sched_slot(ctb_ctx* ctx);
 
 // cuTensorMapEncodeTiled, resolved through the runtime so that the library has
 // no link-time dependency on libcuda and loads on machines without a driver.

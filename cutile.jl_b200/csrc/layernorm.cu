@@ -700,3 +700,25 @@ extern "C" int ctb_layernorm_bwd_static(void* stream, float* DX, const float* DY
   CTB_CHECK_LAUNCH("ctb_layernorm_bwd_static reduce launch");
   return CTB_OK;
 }
+
+// Reads and clears the status word of the allocation-free entry point on the current device (the word lives in the
+// library image next to the scratch; its address comes from the same one-time cudaGetSymbolAddress set-up).
+extern "C" int ctb_layernorm_bwd_static_status(void* stream) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static_status: cudaGetDevice");
+  StaticDev* d = nullptr;
+  int r = static_setup(dev, &d);
+  if (r) return r;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int v = 0;
+  e = cudaMemcpyAsync(&v, d->status, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static_status");
+  if (v == 0) return CTB_OK;
+  e = cudaMemsetAsync(d->status, 0, sizeof(int), st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cuda_fail(e, "ctb_layernorm_bwd_static_status: clearing the word");
+  return fail(CTB_TIMEOUT, "ctb_layernorm_bwd_static: a kernel gave up a bounded wait (device code %d); DX, FINAL_DW "
+              "and FINAL_DB of the calls since the last check are not valid", v);
+}

@@ -165,6 +165,13 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, in
       : "memory");
 }
 
+// Tiled bulk store shared -> global (tracked by the bulk async-group); rows/columns outside the tensor are clipped.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(tmap), "r"(x),
+               "r"(y), "r"(z), "r"(smem_u32(smem_src))
+               : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_out, uint32_t ncols) {  // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_out)),

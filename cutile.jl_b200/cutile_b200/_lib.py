@@ -62,6 +62,7 @@ SIGNATURES = {
     "ctb_fmha_fwd": [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _f, C.c_int32, _i, _i, _i, _i,
                      _i],
     "ctb_layernorm_bwd_static": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64],
+    "ctb_layernorm_bwd_static_status": [_p],
     "ctb_moe_max_blocks": [_i64, _i64, _i64, _i],
     "ctb_moe_router": [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i],
     "ctb_moe_align": [_p, _p, _p, _i, _i64, _i64, _i64, _i, _p, _p, _p, _i64],

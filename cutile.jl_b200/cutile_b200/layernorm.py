@@ -64,3 +64,13 @@ def layer_norm_bwd_static(DX, DY, X, W, Mean, Rstd, FINAL_DW, FINAL_DB):
         stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
         _lib.check(_lib.lib.ctb_layernorm_bwd_static(stream, ptr(DX), ptr(DY), ptr(X), ptr(W), ptr(Mean), ptr(Rstd),
                                                      ptr(FINAL_DW), ptr(FINAL_DB), N, M, ldx, lddy, lddx))
+
+
+def layer_norm_bwd_static_status(device=None):
+    """Synchronises the current stream and reads-and-clears the status word of layer_norm_bwd_static on `device`
+    (default: the current one).  Raises CtbError(TIMEOUT) when one of its kernels gave up a bounded wait since the
+    last check; allocates nothing."""
+    import ctypes as C
+    import torch
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        _lib.check(_lib.lib.ctb_layernorm_bwd_static_status(C.c_void_p(torch.cuda.current_stream().cuda_stream)))

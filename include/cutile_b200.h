@@ -268,6 +268,12 @@ int ctb_moe_ep_experts(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, c
 int ctb_layernorm_bwd_static(void* stream, float* DX, const float* DY, const float* X, const float* W,
                              const float* Mean, const float* Rstd, float* FINAL_DW, float* FINAL_DB, int64_t N,
                              int64_t M, int64_t ldx, int64_t lddy, int64_t lddx);
+/* No counterpart in the reference.  The allocation-free call above has no context, so the bounded waits of its
+ * kernels report into a status word that lives next to the scratch inside the library.  This call synchronises
+ * `stream`, reads that word on the current device and clears it: CTB_OK, or CTB_TIMEOUT when a kernel of
+ * ctb_layernorm_bwd_static gave up a wait since the last check (its outputs are then not valid).  It allocates
+ * nothing either. */
+int ctb_layernorm_bwd_static_status(void* stream);
 
 #ifdef __cplusplus
 }
