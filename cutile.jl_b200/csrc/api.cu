@@ -35,8 +35,13 @@ bool is_device_ptr(const void* p) {
   return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
 
-int workspace(ctb_ctx* ctx, size_t bytes, void** out) {
+int workspace(ctb_ctx* ctx, size_t bytes, void** out, cudaStream_t stream) {
   if (bytes > ctx->workspace_bytes) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(CTB_UNSUPPORTED, "the context's scratch would have to grow to %zu bytes while the stream is being "
+                  "captured; call ctb_reserve_workspace before the capture", bytes);
     if (ctx->workspace) {
       cudaError_t e = cudaDeviceSynchronize();
       if (e != cudaSuccess) return cuda_fail(e, "workspace: synchronize before regrow");
@@ -129,6 +134,7 @@ int ctb_create(ctb_ctx** out, int device) {
   c->workspace_bytes = 0;
   c->sched_pool = nullptr;
   c->sched_next = 0;
+  c->comm = nullptr;
   e = cudaMalloc(&c->dev_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(c->dev_status, 0, sizeof(int));
   if (e == cudaSuccess) e = cudaMalloc(&c->sched_pool, 2 * kSchedSlots * sizeof(int));
@@ -144,6 +150,7 @@ int ctb_create(ctb_ctx** out, int device) {
 void ctb_destroy(ctb_ctx* ctx) {
   if (!ctx) return;
   cudaSetDevice(ctx->device);
+  comm_release(ctx);
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
   if (ctx->sched_pool) cudaFree(ctx->sched_pool);

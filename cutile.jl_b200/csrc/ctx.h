@@ -21,6 +21,7 @@ struct ctb_ctx {
   // that overlap on the device (different streams) do not share one.
   int* sched_pool;
   unsigned sched_next;
+  void* comm;             // ctb_internal::Comm* once an NCCL communicator is attached (multi.cu)
 };
 
 namespace ctb_internal {
@@ -30,8 +31,16 @@ int cuda_fail(cudaError_t e, const char* what);
 bool is_pow2(long long v);
 // True when p looks like device (or managed) memory of the current context.
 bool is_device_ptr(const void* p);
-// Returns ctx scratch of at least `bytes` (may reallocate => synchronises the device).
-int workspace(ctb_ctx* ctx, size_t bytes, void** out);
+// Returns ctx scratch of at least `bytes`.  Growing it frees and reallocates (after a device synchronise), which is
+// refused while `stream` is being captured; ctb_reserve_workspace sizes it up front.
+int workspace(ctb_ctx* ctx, size_t bytes, void** out, cudaStream_t stream);
+// Destroys the NCCL communicator attached to the context, if any (multi.cu).
+void comm_release(ctb_ctx* ctx);
+// Expert phase shared by the expert-parallel MoE paths (defined with the MoE kernels).
+size_t moe_experts_rows_workspace(int64_t R, int64_t I, int64_t E_local, int tile_m);
+int moe_experts_rows(ctb_ctx* ctx, cudaStream_t st, const void* rows, int64_t ld_rows, const int32_t* ids,
+                     const void* gates, int64_t R, int64_t H, int64_t I, int64_t E_local, const void* w1_local,
+                     const void* w2_local, int tile_m, void* C, int64_t ldc, void* const* c_peer, int64_t c_split);
 constexpr int kSchedSlots = 256;
 // The next pair of work counters of the context (see ctb_ctx::sched_pool).
 int* sched_slot(ctb_ctx* ctx);

@@ -995,6 +995,52 @@ int check_tile(const char* who, int tile_m, int tile_n, int tile_k) {
 
 }  // namespace
 
+namespace ctb_internal {
+
+size_t moe_experts_rows_workspace(int64_t R, int64_t I, int64_t E_local, int tile_m) {
+  const int64_t blocks_cap = ctb_moe_max_blocks(R, 1, E_local, tile_m);
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  return up((size_t)blocks_cap * tile_m * 4) + up((size_t)blocks_cap * 4) + 256 + up((size_t)R * I * 2);
+}
+
+// The expert phase of the expert-parallel paths: `R` token rows (row i at rows + i*ld_rows, H f16 each) that made ONE
+// choice each, ids[i] = local expert (1-based; 0 = the row is not for this rank), gates[i] = its routing weight.
+// align + gate/up GEMM with SwiGLU + down GEMM; the weighted output row of token i goes to C + i*ldc, or, with
+// c_split > 0, to c_peer[i / c_split] + (i % c_split)*ldc (peer memory: the buffer of the rank that sent the row).
+int moe_experts_rows(ctb_ctx* ctx, cudaStream_t st, const void* rows, int64_t ld_rows, const int32_t* ids,
+                     const void* gates, int64_t R, int64_t H, int64_t I, int64_t E_local, const void* w1_local,
+                     const void* w2_local, int tile_m, void* C, int64_t ldc, void* const* c_peer, int64_t c_split) {
+  if (R <= 0 || H <= 0 || I <= 0 || E_local <= 0 || R > (1 << 24)) return fail(CTB_BAD_ARG, "expert phase: bad shape");
+  if (E_local > kMaxExperts) return fail(CTB_UNSUPPORTED, "expert phase: at most %d local experts", kMaxExperts);
+  if (H % 8 || I % 8 || ld_rows % 8) return fail(CTB_BAD_ALIGN, "expert phase: hidden and intermediate sizes must be multiples of 8");
+  CTB_CHECK_DEV(w1_local); CTB_CHECK_DEV(w2_local);
+  if ((uintptr_t)w1_local % 16 || (uintptr_t)w2_local % 16 || (uintptr_t)rows % 16)
+    return fail(CTB_BAD_ALIGN, "expert phase: 16-byte alignment of the weights and token rows");
+  const int blocks_cap = (int)ctb_moe_max_blocks(R, 1, E_local, tile_m);
+  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+  const size_t o_tok = 0, o_exp = up((size_t)blocks_cap * tile_m * 4), o_nb = o_exp + up((size_t)blocks_cap * 4),
+               o_act = o_nb + 256, bytes = o_act + up((size_t)R * I * 2);
+  void* ws;
+  int r = workspace(ctx, bytes, &ws, st);
+  if (r) return r;
+  unsigned char* w = (unsigned char*)ws;
+  int* s_tok = (int*)(w + o_tok);
+  int* s_exp = (int*)(w + o_exp);
+  int* s_nb = (int*)(w + o_nb);
+  __half* act = (__half*)(w + o_act);
+  r = launch_align(ctx, st, ids, 32, (int)R, 1, (int)E_local, tile_m, s_tok, s_exp, s_nb, blocks_cap, /*skip_empty=*/1);
+  if (r) return r;
+  r = launch_gemm(ctx, st, EPI_SWIGLU, (const __half*)rows, ld_rows, (int)R, (const __half*)w1_local, (int)H,
+                  (int)(2 * I), (int)I, (int)E_local, nullptr, s_tok, s_exp, s_nb, -1, blocks_cap, 1, 0, tile_m, (int)R,
+                  act, I);
+  if (r) return r;
+  return launch_gemm(ctx, st, EPI_F16, act, I, (int)R, (const __half*)w2_local, (int)I, (int)H, (int)H, (int)E_local,
+                     (const __half*)gates, s_tok, s_exp, s_nb, -1, blocks_cap, 1, 1, tile_m, (int)R, C, ldc, 0, 1, c_peer,
+                     (int)c_split);
+}
+
+}  // namespace ctb_internal
+
 extern "C" {
 
 int64_t ctb_moe_max_blocks(int64_t T, int64_t topk, int64_t E, int tile_m) {
@@ -1122,7 +1168,7 @@ int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, 
   const size_t o_tok = 0, o_exp = up((size_t)cap * tile_m * 4), o_nb = o_exp + up((size_t)cap * 4), o_act = o_nb + 256,
                o_slots = o_act + up((size_t)total * I * 2), bytes = o_slots + up((size_t)total * H * 2);
   void* ws;
-  r = workspace(ctx, bytes, &ws);
+  r = workspace(ctx, bytes, &ws, st);
   if (r) return r;
   unsigned char* w = (unsigned char*)ws;
   int* s_tok = (int*)(w + o_tok);
@@ -1214,36 +1260,12 @@ int ctb_moe_ep_experts(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, c
   r = check_tile("ctb_moe_ep_experts", tile_m, tile_n, tile_k);
   if (r) return r;
   const long long R = cap * bufs->world;  // columns of the receive buffers
-  if (cap <= 0 || H <= 0 || I <= 0 || E_local <= 0 || R > (1 << 24)) return fail(CTB_BAD_ARG, "ctb_moe_ep_experts: bad shape");
-  if (E_local > kMaxExperts) return fail(CTB_UNSUPPORTED, "ctb_moe_ep_experts: at most %d local experts", kMaxExperts);
-  if (H % 8 || I % 8) return fail(CTB_BAD_ALIGN, "ctb_moe_ep_experts: hidden and intermediate sizes must be multiples of 8");
-  CTB_CHECK_DEV(w1_local); CTB_CHECK_DEV(w2_local);
-  if ((uintptr_t)w1_local % 16 || (uintptr_t)w2_local % 16) return fail(CTB_BAD_ALIGN, "ctb_moe_ep_experts: 16-byte alignment of the weights");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cap <= 0) return fail(CTB_BAD_ARG, "ctb_moe_ep_experts: bad shape");
   const int me = bufs->rank;
-  const int blocks_cap = (int)ctb_moe_max_blocks(R, 1, E_local, tile_m);
-  auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
-  const size_t o_tok = 0, o_exp = up((size_t)blocks_cap * tile_m * 4), o_nb = o_exp + up((size_t)blocks_cap * 4),
-               o_act = o_nb + 256, bytes = o_act + up((size_t)R * I * 2);
-  void* ws;
-  r = workspace(ctx, bytes, &ws);
-  if (r) return r;
-  unsigned char* w = (unsigned char*)ws;
-  int* s_tok = (int*)(w + o_tok);
-  int* s_exp = (int*)(w + o_exp);
-  int* s_nb = (int*)(w + o_nb);
-  __half* act = (__half*)(w + o_act);
   // every received column is one token with a single choice; id 0 = the slot went to another rank
-  r = launch_align(ctx, st, bufs->recv_ids[me], 32, (int)R, 1, (int)E_local, tile_m, s_tok, s_exp, s_nb, blocks_cap,
-                   /*skip_empty=*/1);
-  if (r) return r;
-  r = launch_gemm(ctx, st, EPI_SWIGLU, (const __half*)bufs->recv_rows[me], H, (int)R, (const __half*)w1_local, (int)H,
-                  (int)(2 * I), (int)I, (int)E_local, nullptr, s_tok, s_exp, s_nb, -1, blocks_cap, 1, 0, tile_m,
-                  (int)R, act, I);
-  if (r) return r;
-  return launch_gemm(ctx, st, EPI_F16, act, I, (int)R, (const __half*)w2_local, (int)I, (int)H, (int)H, (int)E_local,
-                     (const __half*)bufs->recv_gates[me], s_tok, s_exp, s_nb, -1, blocks_cap, 1, 1, tile_m, (int)R,
-                     bufs->slot_out[me], H, 0, 1, bufs->slot_out, (int)cap);
+  return moe_experts_rows(ctx, static_cast<cudaStream_t>(stream), bufs->recv_rows[me], H, bufs->recv_ids[me],
+                          bufs->recv_gates[me], R, H, I, E_local, w1_local, w2_local, tile_m, bufs->slot_out[me], H,
+                          bufs->slot_out, cap);
 }
 
 int ctb_moe_gather_rows(ctb_ctx* ctx, void* stream, void* dst, const void* src, const int32_t* ids, int64_t n_ids,

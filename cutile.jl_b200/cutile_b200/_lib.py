@@ -32,6 +32,7 @@ if not os.path.exists(LIB_PATH):
 lib = C.CDLL(LIB_PATH)
 
 _p, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+_pp = C.POINTER(C.c_void_p)
 
 EP_MAX_RANKS = 8
 
@@ -75,9 +76,35 @@ SIGNATURES = {
     "ctb_moe_ep_dispatch": [_p, _p, C.POINTER(EpBuffers), _p, _p, _p, _i64, _i64, _i64, _i64],
     "ctb_moe_ep_barrier": [_p, _p, C.POINTER(EpBuffers)],
     "ctb_moe_ep_experts": [_p, _p, C.POINTER(EpBuffers), _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
+    "ctb_create_multi": [C.POINTER(_p), C.POINTER(_i), _i],
+    "ctb_destroy_multi": [_p],
+    "ctb_group_size": [_p],
+    "ctb_group_ctx": [_p, _i],
+    "ctb_comm_unique_id": [_p],
+    "ctb_comm_init_rank": [_p, _p, _i, _i],
+    "ctb_comm_abort": [_p],
+    "ctb_comm_info": [_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)],
+    "ctb_gemm_batched_sharded": [_p, _pp, _pp, _pp, _pp, _i64, _i64, _i64, C.POINTER(_i64), _i64, _i64, _i64, _i64, _i64,
+                                 _i64, _i, _i, _i, _i],
+    "ctb_fmha_fwd_sharded": [_p, _pp, _pp, _pp, _pp, _pp, _i64, _i64, _i64, _i64, _i64, _i64, C.POINTER(_i64), _f,
+                             C.c_int32, _i, _i, _i, _i, _i],
+    "ctb_ep_create": [_p, _i, _i, _i64, _i64, _i64, C.POINTER(_p)],
+    "ctb_ep_destroy": [_p],
+    "ctb_ep_export": [_p, _p],
+    "ctb_ep_import": [_p, _i, _p],
+    "ctb_ep_connect_local": [_pp, _i],
+    "ctb_ep_table": [_p],
+    "ctb_moe_ffn_ep": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i],
+    "ctb_moe_ffn_ep_group": [_p, _pp, _pp, _pp, _pp, _pp, _pp, _pp, _pp, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i],
+    "ctb_workspace_bytes": [_i, C.POINTER(_i64), _i],
+    "ctb_reserve_workspace": [_p, _p, C.c_size_t],
 }
 _RESTYPES = {"ctb_destroy": None, "ctb_last_error": C.c_char_p, "ctb_status_string": C.c_char_p,
-             "ctb_moe_max_blocks": _i64}
+             "ctb_moe_max_blocks": _i64, "ctb_destroy_multi": None, "ctb_ep_destroy": None, "ctb_group_ctx": _p,
+             "ctb_ep_table": C.POINTER(EpBuffers), "ctb_workspace_bytes": C.c_size_t}
+UNIQUE_ID_BYTES, EP_HANDLE_BYTES = 128, 64
+A2A_NCCL, A2A_PEER = 0, 1
+OP_MOE_FFN, OP_MOE_EP = 1, 2
 
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)  # AttributeError here = header and library disagree

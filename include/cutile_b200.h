@@ -131,7 +131,10 @@ int64_t ctb_moe_max_blocks(int64_t T, int64_t topk, int64_t E, int tile_m);
 
 /* Router of the benchmark configuration (no counterpart kernel in the reference,
  * which draws ids with randperm, examples/moe.jl:323-332).  hidden (H, T) f16,
- * W_r (H, E) f16.  logits accumulate in f32 in ascending k; top-k by value, ties
+ * W_r (H, E) f16.  Each logit is summed in f32 in a fixed order that a CPU loop can
+ * reproduce bit for bit: 32 partial sums, partial l taking the hidden indices k with
+ * (k mod 256) in [8l, 8l+8) in ascending k, then v += v[l xor o] for o = 16, 8, 4, 2, 1 over
+ * the partials (every f16*f16 product is exact in f32).  Top-k by value, ties
  * to the smallest index (the reference's arg-reduction rule,
  * src/language/operations.jl:1675-1677); gates = softmax over the chosen logits.
  * Outputs: topk_ids (T, topk) int32, 1-based; topk_weights (T, topk) f16;
@@ -244,6 +247,90 @@ int ctb_moe_ep_barrier(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs);
 int ctb_moe_ep_experts(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs, const void* w1_local,
                        const void* w2_local, int64_t cap, int64_t H, int64_t I, int64_t E_local, int tile_m, int tile_n,
                        int tile_k);
+
+/* ---- Several GPUs ------------------------------------------------------------------ */
+/* The reference is single-GPU; the partitioning below is that of the benchmark configuration (batched GEMM and
+ * FMHA split by batch with no communication; MoE expert-parallel with experts [r*E/N, (r+1)*E/N) on rank r and
+ * the tokens sharded by rank).  The host wrapper that a multi-GPU cutile_moe replaces is examples/moe.jl:218-257.
+ *
+ * One process, several devices: ctb_create_multi creates one context per listed device, enables peer access
+ * between all of them and, for more than one device, an NCCL communicator per device (ncclCommInitAll).  The
+ * group owns its contexts: ctb_group_ctx(g, i) is the context to pass to the single-device entry points for
+ * device i (make that device current first); ctb_destroy_multi frees everything. */
+typedef struct ctb_group ctb_group;
+int ctb_create_multi(ctb_group** out, const int* devices, int ndev);
+void ctb_destroy_multi(ctb_group* g);
+int ctb_group_size(const ctb_group* g);
+ctb_ctx* ctb_group_ctx(ctb_group* g, int i);
+
+/* One process per GPU: rank 0 draws an id (ncclGetUniqueId), the host language's own means carry the
+ * CTB_UNIQUE_ID_BYTES bytes to the other processes, and every rank attaches a communicator to its context
+ * (ncclCommInitRank; collective: all ranks must call).  ctb_destroy destroys the communicator;
+ * ctb_comm_abort tears it down without waiting for outstanding operations (after a host-side failure of
+ * another rank).  NCCL is loaded at run time (libnccl.so.2); CTB_NCCL_ERROR when it is missing or fails. */
+#define CTB_UNIQUE_ID_BYTES 128
+int ctb_comm_unique_id(void* id);
+int ctb_comm_init_rank(ctb_ctx* ctx, const void* id, int rank, int world);
+int ctb_comm_abort(ctb_ctx* ctx);
+int ctb_comm_info(ctb_ctx* ctx, int* rank, int* world, int* nccl_version);
+
+/* batch_matmul_kernel (examples/batchmatmul.jl:15-56) over the devices of a group: device i runs the
+ * batch_per_dev[i] batches whose arrays are A[i], B[i], C[i] (device pointers on device i; batch-last layout makes a
+ * shard a contiguous slab of the whole array) on streams[i].  No communication. */
+int ctb_gemm_batched_sharded(ctb_group* g, void* const* streams, const void* const* A, const void* const* B,
+                             void* const* C, int64_t M, int64_t N, int64_t K, const int64_t* batch_per_dev, int64_t lda,
+                             int64_t ldb, int64_t ldc, int64_t strideA, int64_t strideB, int64_t strideC, int dtype,
+                             int tm, int tn, int tk);
+/* cutile_fmha's launch (examples/fmha.jl:146-168) over the devices of a group: device i runs batch_per_dev[i]
+ * batches (all heads) of Q[i], K[i], V[i] -> Out[i]; (D, S, H, B) arrays split along B are contiguous slabs. */
+int ctb_fmha_fwd_sharded(ctb_group* g, void* const* streams, const void* const* Q, const void* const* K,
+                         const void* const* V, void* const* Out, int64_t d_k, int64_t d_v, int64_t seq_q,
+                         int64_t seq_kv, int64_t heads, int64_t kv_heads, const int64_t* batch_per_dev, float qk_scale,
+                         int32_t input_pos, int tile_m, int tile_n, int query_group_size, int causal, int dtype);
+
+/* Expert-parallel cutile_moe.  ctb_ep holds one rank's exchange buffers for a fixed (T_local, H, topk): a single
+ * device allocation that the other ranks map -- ctb_ep_connect_local inside one process (after ctb_create_multi),
+ * or ctb_ep_export / ctb_ep_import across processes (a CUDA IPC handle of CTB_EP_HANDLE_BYTES bytes per rank,
+ * carried by the host; every rank imports every other rank's).  ctb_ep_table gives the ctb_ep_buffers table for
+ * the building-block calls above.
+ * ctb_moe_ffn_ep runs one rank's step: hidden (H, T_local), w1_local (H, 2I, E/N), w2_local (I, H, E/N),
+ * topk_weights / topk_ids (T_local, topk) with GLOBAL 1-based expert ids, out (H, T_local).
+ *   a2a_mode CTB_A2A_NCCL: rows are packed by destination rank and cross as grouped ncclSend/ncclRecv pairs, outputs
+ *     come back the same way.  The per-pair counts cross first and are read on the host: the call synchronises
+ *     `stream` once and cannot be captured in a graph.  Needs a communicator on the context.
+ *   a2a_mode CTB_A2A_PEER: the dispatch kernel stores each token row into the owning rank's buffer, the down
+ *     projection's epilogue stores each weighted output row into the sender's buffer (plain peer stores over
+ *     NVLink), two flag barriers with bounded waits in between.  Kernel launches only.
+ * Both give results bit-identical to ctb_moe_ffn on the gathered problem.  Every rank must make the call.
+ * ctb_moe_ffn_ep_group makes the calls of all ranks of a single-process group from one thread (NCCL requires its
+ * send/receive pairs of several devices driven by one thread to sit in one group call). */
+#define CTB_EP_HANDLE_BYTES 64
+typedef enum ctb_a2a_mode { CTB_A2A_NCCL = 0, CTB_A2A_PEER = 1 } ctb_a2a_mode;
+typedef struct ctb_ep ctb_ep;
+int ctb_ep_create(ctb_ctx* ctx, int world, int rank, int64_t T_local, int64_t H, int64_t topk, ctb_ep** out);
+void ctb_ep_destroy(ctb_ep* ep);
+int ctb_ep_export(ctb_ep* ep, void* handle);
+int ctb_ep_import(ctb_ep* ep, int peer_rank, const void* handle);
+int ctb_ep_connect_local(ctb_ep* const* eps, int n);
+const ctb_ep_buffers* ctb_ep_table(const ctb_ep* ep);
+int ctb_moe_ffn_ep(ctb_ep* ep, void* stream, const void* hidden, const void* w1_local, const void* w2_local,
+                   const void* topk_weights, const int32_t* topk_ids, void* out, int64_t T_local, int64_t H, int64_t I,
+                   int64_t E, int64_t topk, int tile_m, int tile_n, int tile_k, int a2a_mode);
+int ctb_moe_ffn_ep_group(ctb_group* g, ctb_ep* const* eps, void* const* streams, const void* const* hidden,
+                         const void* const* w1_local, const void* const* w2_local, const void* const* topk_weights,
+                         const int32_t* const* topk_ids, void* const* out, int64_t T_local, int64_t H, int64_t I,
+                         int64_t E, int64_t topk, int tile_m, int tile_n, int tile_k, int a2a_mode);
+
+/* Scratch of the context.  ctb_moe_ffn and the expert-parallel calls keep their intermediates (sorted slot ids,
+ * activations, per-slot outputs) in scratch owned by the context, grown on demand; growing frees and reallocates
+ * after a device synchronise, so a CUDA graph captured earlier must be captured again, and it is refused
+ * (CTB_UNSUPPORTED) while the stream is being captured.  Size it once up front instead:
+ * ctb_workspace_bytes(op, dims, ndims) with dims = {T, H, I, E, topk, tile_m} for CTB_OP_MOE_FFN and
+ * {T_local, H, I, E_local, topk, tile_m, world} for CTB_OP_MOE_EP (0 for an unknown op), then
+ * ctb_reserve_workspace.  One context serves one stream at a time. */
+typedef enum ctb_op { CTB_OP_MOE_FFN = 1, CTB_OP_MOE_EP = 2 } ctb_op;
+size_t ctb_workspace_bytes(int op, const int64_t* dims, int ndims);
+int ctb_reserve_workspace(ctb_ctx* ctx, void* stream, size_t bytes);
 
 /* ---- LayerNorm backward without any allocation --------------------------------- */
 /* No counterpart in the reference.  For callers that cannot obtain device memory

@@ -1,7 +1,6 @@
-"""Worker of the expert-parallel MoE tests (launched with torch.distributed.run, one rank per device).
-
-mode "plan" (CPU, gloo): checks the dispatch plan and the count/id exchange against a numpy ground truth.
-mode "gpu" (NCCL): checks cutile_moe_ep bit for bit against the single-GPU cutile_moe on the gathered problem."""
+"""Worker of the process-per-GPU expert-parallel MoE test (launched with torch.distributed.run, one rank per
+device): cutile_moe_ep through the C ABI, in both exchange modes, against the single-GPU cutile_moe on the gathered
+problem, bit for bit.  torch.distributed only carries the set-up byte strings (NCCL id, IPC handles)."""
 import json
 import os
 import sys
@@ -22,66 +21,42 @@ import torch
 import torch.distributed as dist
 
 
-def routing(T, E, topk, seed):
-    g = np.random.default_rng(seed)
-    ids = np.stack([g.permutation(E)[:topk] + 1 for _ in range(T)], axis=1).astype(np.int32)  # [topk, T]
-    raw = np.exp(g.random((topk, T), dtype=np.float32))
-    return ids, (raw / raw.sum(axis=0, keepdims=True)).astype(np.float16)
-
-
 def main():
-    mode = sys.argv[1]
-    dist.init_process_group("gloo" if mode == "plan" else "nccl")
+    dist.init_process_group("nccl")
     rank, world = dist.get_rank(), dist.get_world_size()
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
     import cutile_b200 as ctb
-    T, E, topk = 64, 8, 2
-    Tl = T // world
-    ids, w = routing(T, E, topk, seed=5)
-    my = slice(rank * Tl, (rank + 1) * Tl)
-    if mode == "plan":
-        order, send_counts = ctb.moe.ep_plan(torch.from_numpy(ids[:, my].copy()), E, world)
-        flat = ids[:, my].T.reshape(-1)
-        want_order = np.argsort(flat, kind="stable") + 1
-        assert np.array_equal(order.numpy(), want_order)
-        dest = (flat[want_order - 1] - 1) // (E // world)
-        assert np.array_equal(send_counts.numpy(), np.bincount(dest, minlength=world))
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts)
-        sent_e = torch.from_numpy(flat[want_order - 1].astype(np.int32))
-        got_e = torch.empty(int(recv_counts.sum()), dtype=torch.int32)
-        dist.all_to_all_single(got_e, sent_e, recv_counts.tolist(), send_counts.tolist())
-        lo, hi = rank * (E // world) + 1, (rank + 1) * (E // world)
-        assert ((got_e >= lo) & (got_e <= hi)).all()  # only this rank's experts arrive
-        allflat = ids.T.reshape(-1)
-        assert got_e.numel() == int(((allflat >= lo) & (allflat <= hi)).sum())  # and all of them
-        _emit({"rank": rank, "ok": True, "received": got_e.numel()})
-    else:
-        from oracle import inputs
-        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-        H, I = 256, 512
-        d = inputs.moe(tokens=T, hidden=H, experts=E, inter=I, topk=topk, seed=8)
-        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
-        El = E // world
-        out = ctb.moe.cutile_moe_ep(dev(d["X"][my]), dev(d["w1"][rank * El:(rank + 1) * El]),
-                                    dev(d["w2"][rank * El:(rank + 1) * El]), dev(w[:, my]), dev(ids[:, my]), E,
-                                    128, 128, 64)
-        full = ctb.moe.cutile_moe(dev(d["X"]), dev(d["w1"]), dev(d["w2"]), dev(w), dev(ids), 128, 128, 64)
-        torch.cuda.synchronize()
-        ctb.check_device_status(torch.cuda.current_device())
-        same = bool(torch.equal(out, full[my]))
-        # the same problem through the peer-memory path (stores into the other rank's buffers, no all-to-all);
-        # twice, to cover the reuse of the buffers from one step to the next
-        bufs = ctb.moe.EpPeerBuffers(Tl, H, topk, torch.device("cuda", torch.cuda.current_device()))
-        args = (dev(d["X"][my]), dev(d["w1"][rank * El:(rank + 1) * El]), dev(d["w2"][rank * El:(rank + 1) * El]),
-                dev(w[:, my]), dev(ids[:, my]), E, 128, 128, 64)
-        peer1 = ctb.moe.cutile_moe_ep_peer(bufs, *args)
-        peer2 = ctb.moe.cutile_moe_ep_peer(bufs, *args)
-        torch.cuda.synchronize()
-        ctb.check_device_status(torch.cuda.current_device())
-        same_peer = bool(torch.equal(peer1, full[my])) and bool(torch.equal(peer2, full[my]))
-        _emit({"rank": rank, "ok": same and same_peer, "nccl": same, "peer": same_peer})
-        assert same and same_peer
+    from oracle import inputs
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    results = []
+    # a small case (one slot block per expert) and the benchmark's 4096-token configuration
+    for T, H, E, I, topk, seed in ((64 * world, 256, 8 * world, 512, 2, 8), (4096, 1024, 32, 2048, 2, 4)):
+        if E % world or T % world:
+            continue
+        d = inputs.moe(tokens=T, hidden=H, experts=E, inter=I, topk=topk, seed=seed)
+        Tl, El = T // world, E // world
+        my = slice(rank * Tl, (rank + 1) * Tl)
+        X, Wr, w1, w2 = dev(d["X"]), dev(d["Wr"]), dev(d["w1"]), dev(d["w2"])
+        gates, ids = ctb.moe.moe_router(X, Wr, topk)
+        full = ctb.moe.cutile_moe(X, w1, w2, gates, ids, 128, 128, 64)
+        ep = ctb.multi.EpRank(Tl, H, topk, torch.device("cuda", local))
+        args = (X[my].contiguous(), w1[rank * El:(rank + 1) * El].contiguous(), w2[rank * El:(rank + 1) * El].contiguous(),
+                gates[:, my].contiguous(), ids[:, my].contiguous(), E, 128, 128, 64)
+        ok = {}
+        for mode in ("peer", "nccl"):
+            a = ep.cutile_moe_ep(*args, a2a_mode=mode)
+            b = ep.cutile_moe_ep(*args, a2a_mode=mode)  # twice: the buffers are reused from one step to the next
+            torch.cuda.synchronize()
+            ctb.check_device_status(local)
+            ok[mode] = bool(torch.equal(a, full[my])) and bool(torch.equal(b, full[my]))
+        ep.close()
+        results.append(dict(tokens=T, **ok))
+    good = all(r["peer"] and r["nccl"] for r in results)
+    _emit({"rank": rank, "ok": good, "cases": results})
+    dist.barrier()
     dist.destroy_process_group()
+    assert good
 
 
 if __name__ == "__main__":

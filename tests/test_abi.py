@@ -68,3 +68,31 @@ def test_expert_parallel_entry_points_validate_their_table():
     st = _lib.lib.ctb_moe_ep_experts(None, None, ctypes.byref(tab), None, None, 16, 64, 128, 4, 128, 128, 64)
     assert st == _lib.BAD_ARG
     assert ctypes.sizeof(_lib.EpBuffers) == 8 + 5 * 8 * _lib.EP_MAX_RANKS + 8  # layout of ctb_ep_buffers
+
+
+def test_multi_gpu_entry_points_fail_on_the_host_side():
+    """Bad device lists, missing tables and unknown ops are refused before any device or NCCL call."""
+    from cutile_b200 import _lib
+    import cutile_b200
+    g = ctypes.c_void_p()
+    assert _lib.lib.ctb_create_multi(ctypes.byref(g), None, 2) == _lib.BAD_ARG
+    two = (ctypes.c_int * 2)(3, 3)
+    assert _lib.lib.ctb_create_multi(ctypes.byref(g), two, 2) == _lib.BAD_ARG and "twice" in _lib.last_error()
+    nine = (ctypes.c_int * 9)(*range(9))
+    assert _lib.lib.ctb_create_multi(ctypes.byref(g), nine, 9) == _lib.BAD_ARG
+    assert _lib.lib.ctb_group_size(None) == 0 and not _lib.lib.ctb_group_ctx(None, 0)
+    assert _lib.lib.ctb_comm_init_rank(None, None, 0, 2) == _lib.BAD_ARG
+    assert _lib.lib.ctb_comm_unique_id(None) == _lib.BAD_ARG
+    assert _lib.lib.ctb_fmha_fwd_sharded(None, None, None, None, None, None, 64, 64, 128, 128, 2, 2, None, 0.125, 0, 128,
+                                         128, 1, 1, 1) == _lib.BAD_ARG
+    assert _lib.lib.ctb_moe_ffn_ep(None, None, None, None, None, None, None, None, 8, 64, 64, 8, 2, 128, 128, 64, 1) \
+        == _lib.BAD_ARG
+    assert _lib.lib.ctb_ep_connect_local(None, 2) == _lib.BAD_ARG
+    # scratch sizing is pure host arithmetic
+    wb = cutile_b200.multi.workspace_bytes
+    small, big = wb("moe_ffn", 256, 1024, 2048, 32, 2, 128), wb("moe_ffn", 4096, 1024, 2048, 32, 2, 128)
+    assert 0 < small < big and big >= 4096 * 2 * (2048 + 1024) * 2
+    assert wb("moe_ep", 512, 1024, 2048, 4, 2, 128, 8) >= 8 * 1024 * 2048 * 2
+    assert wb("nothing", 1, 2, 3) == 0 and wb("moe_ffn", 1, 2) == 0
+    with pytest.raises(cutile_b200.CtbError):
+        cutile_b200.multi.Group([0, 0])
