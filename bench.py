@@ -196,15 +196,14 @@ class Softmax(Workload):
         return (lambda: ref.softmax(x, dtype=np.float32)), 1.0, "full 4096x4096 rows, numpy float32"
 
     def check(self, host, st, ref, np):
-        rows = slice(0, 256)
-        return ref.max_abs_over_max(st["out"][rows].cpu().numpy(), ref.softmax(host["input"][rows]))
+        return ref.max_abs_over_max(st["out"].cpu().numpy(), ref.softmax(host["input"]))
 
 
 class LayerNormFwd(Workload):
     name = "layernorm_fwd"
     metric = "layernorm_fwd_gbps"
     unit = "GB/s"
-    kernel = "ln_fwd_kernel"
+    kernel = "ln_fwd_staged_kernel"
     M = N = 4096
 
     def describe(self):
@@ -236,9 +235,7 @@ class LayerNormFwd(Workload):
             "full 4096x4096, numpy float32"
 
     def check(self, host, st, ref, np):
-        r = slice(0, 256)
-        return ref.max_abs_over_max(st["Y"][r].cpu().numpy(),
-                                    ref.layernorm_fwd(host["X"][r], host["W"], host["B"], host["eps"])[0])
+        return ref.max_abs_over_max(st["Y"].cpu().numpy(), ref.layernorm_fwd(host["X"], host["W"], host["B"], host["eps"])[0])
 
 
 class LayerNormBwd(LayerNormFwd):
@@ -360,8 +357,8 @@ class Fmha(Workload):
     B, H, S, D = 8, 16, 1024, 64
 
     def describe(self):
-        return ("causal FMHA f16 batch 8 x heads 16 x seq 1024 x dim 64, N(0,1) seed 3, scale 1/8; flops = useful "
-                "causal work 4*B*H*D*S*(S+1)/2 (the reference's un-halved count 4*B*H*S*S*D is 2.0x this)")
+        return ("causal FMHA f16 b8 h16 s1024 d64, N(0,1) seed 3, scale 1/8; flops = useful causal work "
+                "4*B*H*D*S*(S+1)/2 (the reference counts 4*B*H*S*S*D, 2.0x this)")
 
     def work(self):
         return 4 * self.B * self.H * self.D * self.S * (self.S + 1) // 2
@@ -379,6 +376,10 @@ class Fmha(Workload):
         # the launch inside cutile_fmha; the output buffer is preallocated for the device-resident timing
         ctb.fmha.fmha_kernel(st["Q"], st["K"], st["V"], st["Out"], 0.125, 0, self.D, self.H, 128, 128, 1, True, True)
 
+    def call_surface(self, ctb, st):
+        # cutile_fmha allocates Out inside the timed call (examples/fmha.jl:160)
+        st["Out"] = ctb.fmha.cutile_fmha(st["Q"], st["K"], st["V"], qk_scale=0.125, causal=True)
+
     def e2e_io(self, st):
         return [("Q",), ("K",), ("V",)], [("Out",)]
 
@@ -389,6 +390,40 @@ class Fmha(Workload):
 
     def check(self, host, st, ref, np):
         sl = (slice(7, 8), slice(14, 16))
+        want = ref.fmha(host["Q"][sl], host["K"][sl], host["V"][sl], causal=True)
+        return ref.rel_fro(st["Out"][sl].cpu().numpy(), want)
+
+
+class SoftmaxOnline(Softmax):
+    """Rows too long for one tile: the chunked kernel with a running (max, sum) per thread."""
+    M, N = 1024, 32768
+
+    def __init__(self):
+        Softmax.__init__(self, 1)
+        self.name = "softmax_online"
+        self.kernel = "softmax_online_kernel"
+
+    def describe(self):
+        return f"row softmax f32 {self.M}x{self.N} N(0,4) seed 1, chunked online (rows longer than one tile)"
+
+    def step(self, ctb, st):
+        ctb.softmax.softmax_chunked_kernel(st["out"], st["x"], self.N, 1024)
+
+
+class FmhaB64(Fmha):
+    """The multi-GPU configuration (batch 64) on one GPU: the T1 of the strong-scaling series."""
+    name = "fmha_b64"
+    B = 64
+
+    def describe(self):
+        return "causal FMHA f16 b64 h16 s1024 d64 (the multi-GPU runs' problem), seed 3; useful causal flops"
+
+    def cpu_step(self, host, ref, np):
+        Q, K, V = host["Q"][:8], host["K"][:8], host["V"][:8]
+        return (lambda: ref.fmha(Q, K, V, causal=True, dtype=np.float32)), 0.125, "8 of 64 batches, numpy float32"
+
+    def check(self, host, st, ref, np):
+        sl = (slice(63, 64), slice(14, 16))
         want = ref.fmha(host["Q"][sl], host["K"][sl], host["V"][sl], causal=True)
         return ref.rel_fro(st["Out"][sl].cpu().numpy(), want)
 
@@ -425,6 +460,12 @@ class Moe(Workload):
         w, ids = ctb.moe.moe_router(st["X"], st["Wr"], self.topk)
         st["out"] = ctb.moe.cutile_moe(st["X"], st["w1"], st["w2"], w, ids, 128, 128, 64)
 
+    def call_surface(self, ctb, st):
+        # cutile_moe from routing ids to the result, allocating its output (examples/moe.jl:218-257)
+        if "w" not in st:
+            st["w"], st["ids"] = ctb.moe.moe_router(st["X"], st["Wr"], self.topk)
+        st["out"] = ctb.moe.cutile_moe(st["X"], st["w1"], st["w2"], st["w"], st["ids"], 128, 128, 64)
+
     def e2e_io(self, st):
         return [("X",)], [("out",)]  # the expert weights are model state and stay resident
 
@@ -451,16 +492,19 @@ class Moe4096(Moe):
 
 
 def registry():
-    w = [Fmha(), Moe(), Moe4096(), Gemm(), BatchedGemm(), LayerNormFwd(), LayerNormBwd(), Softmax(0), Softmax(1)]
+    w = [Fmha(), FmhaB64(), Moe(), Moe4096(), Gemm(), BatchedGemm(), LayerNormFwd(), LayerNormBwd(), Softmax(0), Softmax(1),
+         SoftmaxOnline()]
     return {x.name: x for x in w}
 
 
 # --------------------------------------------------------------------------- timing
-def device_time(torch, dist, fn_steps, steps, warmup, graph=True):
-    """`warmup` untimed steps, then exactly `steps` steps between two CUDA events on the launching stream; max over
-    ranks.  With graph=True the `steps` launches are captured once into a CUDA graph and the timed region replays
-    it, so the figure is device time and not the host's Python launch rate (the reference's protocol brackets single
-    launches with events for the same reason, examples/benchmarks.jl:104,159-171)."""
+def time_graph(torch, dist, fn_steps, steps, warmup, target_s=0.1, max_replays=400, graph=True):
+    """`warmup` untimed steps, then R timed regions of exactly `steps` steps each, every region between its own pair
+    of CUDA events on the launching stream, a barrier + synchronize before the first and after the last; the job's
+    time is the maximum over ranks.  With graph=True the `steps` launches are captured once into a CUDA graph and each
+    region replays it, so the figure is device time and not the host's Python launch rate (the reference's protocol
+    brackets single launches with events for the same reason, examples/benchmarks.jl:104,159-171).  R is chosen so that
+    the regions together last about `target_s`: long enough for the clock samples (every 2 ms) to fall inside."""
     for i in range(warmup):
         fn_steps(i)
     torch.cuda.synchronize()
@@ -474,26 +518,52 @@ def device_time(torch, dist, fn_steps, steps, warmup, graph=True):
                 for i in range(steps):
                     fn_steps(warmup + i)
         torch.cuda.current_stream().wait_stream(side)
-        g.replay()  # one untimed replay: the graph is uploaded before the timed region
-        torch.cuda.synchronize()
+
+    def region():
+        if g is not None:
+            g.replay()
+        else:
+            for i in range(steps):
+                fn_steps(warmup + i)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); region(); e1.record()       # one untimed region: the graph is uploaded, and it sizes R
+    torch.cuda.synchronize()
+    first = max(e0.elapsed_time(e1), 1e-3)
+    replays = int(max(3, min(max_replays, target_s * 1e3 / first)))
     if dist is not None:
+        t = torch.tensor([replays], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)  # every rank times the same number of regions
+        replays = int(t.item())
         dist.barrier()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(replays)]
     t0 = time.time()
-    e0.record()
-    if g is not None:
-        g.replay()
-    else:
-        for i in range(steps):
-            fn_steps(warmup + i)
-    e1.record()
+    for a, b in evs:
+        a.record(); region(); b.record()
     torch.cuda.synchronize()
     t1 = time.time()
     if dist is not None:
         dist.barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1), torch, dist, "cuda")
-    return ms, t0, t1
+    per = [a.elapsed_time(b) / steps for a, b in evs]
+    mean = max_over_ranks(sum(per) / len(per), torch, dist, "cuda")
+    best = max_over_ranks(min(per), torch, dist, "cuda")
+    return dict(ms=mean, min_ms=best, max_ms=max(per), replays=replays, t0=t0, t1=t1)
+
+
+def protocol_times(torch, fn, warm=5, iters=20):
+    """The reference's own measurement protocol (examples/benchmarks.jl:104,159-171): 5 warm-up calls, then 20 calls each
+    between its own pair of CUDA events; returns (min, mean) in ms.  Single eager calls: the host's launch cost and the
+    gaps between a call's kernels are part of the figure, as they are in the reference's."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return min(ts), sum(ts) / len(ts)
 
 
 def max_over_ranks(ms, torch, dist, device):
@@ -510,7 +580,87 @@ def aggregate_value(work_per_rank, world, ms_per_step, unit):
     return work_per_rank * world / (ms_per_step * 1e-3) / (1e9 if unit == "GB/s" else 1e12)
 
 
-def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu, sampler=None):
+def shard_range(total, world, rank):
+    """[lo, hi) of `total` independent units (batches, tokens, experts) on `rank`: contiguous, sizes differ by at most
+    one, earlier ranks take the larger shards."""
+    base, extra = divmod(total, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def profile_traffic(workload):
+    """DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of every kernel captured in
+    profiles/*_<workload>.txt (the ncu summaries of this repository), or None when there is no such file."""
+    import glob
+    import re
+    files = glob.glob(os.path.join(ROOT, "profiles", f"*_{workload}.txt"))
+    if not files:
+        return None
+    scale = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    per_kernel = {}
+    cur = None
+    for line in open(files[0]):
+        if line.startswith("== "):
+            name = line[3:].split("  grid")[0].strip()
+            cur = name if name not in per_kernel else None  # the first launch of each kernel
+            if cur:
+                per_kernel[cur] = 0.0
+        elif cur:
+            m = re.match(r"\s+dram__bytes_(read|write)\.sum \[(\w+)\] = ([\d.,]+)", line)
+            if m:
+                per_kernel[cur] += float(m.group(3).replace(",", "")) * scale.get(m.group(2), 1.0)
+    tot = sum(per_kernel.values())
+    return tot if tot > 0 else None
+
+
+def e2e_pipelined(torch, w, ctb, host, base, steps):
+    """The public call from pinned host buffers, as a three-stage pipeline over two sets of device buffers: the
+    host-to-device copies of step i+1 (copy stream), the kernels of step i (compute stream) and the device-to-host
+    copy of step i-1's result (second copy stream) overlap.  Every step moves its inputs in and its result out;
+    returns (ms per step, bytes in, bytes out)."""
+    ins, outs = w.e2e_io(base)
+    w.step(ctb, base)  # outputs that the step itself allocates exist from here on
+    torch.cuda.synchronize()
+    sets = [base, {k: (v.clone() if hasattr(v, "clone") else v) for k, v in base.items()}]
+    pin_in = {k[0]: torch.from_numpy(host[k[0]] if k[0] in host else base[k[0]].cpu().numpy()).pin_memory() for k in ins}
+    pin_out = [{k[0]: torch.empty(base[k[0]].shape, dtype=base[k[0]].dtype).pin_memory() for k in outs} for _ in range(2)]
+    cs, up, down = torch.cuda.current_stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    done_k = [None, None]   # kernel of the step that last used buffer set b
+    done_d = [None, None]   # its result has left the device
+
+    def run(n):
+        for i in range(n):
+            b = i & 1
+            st = sets[b]
+            with torch.cuda.stream(up):
+                if done_k[b] is not None:
+                    up.wait_event(done_k[b])      # the inputs of set b are free again
+                for k, h in pin_in.items():
+                    st[k].copy_(h, non_blocking=True)
+                ready = torch.cuda.Event(); ready.record(up)
+            cs.wait_event(ready)
+            if done_d[b] is not None:
+                cs.wait_event(done_d[b])          # the previous result of set b has been copied out
+            w.step(ctb, st)
+            done_k[b] = torch.cuda.Event(); done_k[b].record(cs)
+            with torch.cuda.stream(down):
+                down.wait_event(done_k[b])
+                for k, h in pin_out[b].items():
+                    h.copy_(st[k], non_blocking=True)
+                done_d[b] = torch.cuda.Event(); done_d[b].record(down)
+        cs.wait_stream(up)
+        cs.wait_stream(down)
+    run(3)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(cs); run(steps); b.record(cs)
+    torch.cuda.synchronize()
+    return (a.elapsed_time(b) / steps, sum(h.numel() * h.element_size() for h in pin_in.values()),
+            sum(h.numel() * h.element_size() for h in pin_out[0].values()))
+
+
+def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu, target_s=0.1):
+    """Times one workload (for the batch-sharded runs: this rank's share of it) on this rank's device."""
     import numpy as np
     from oracle import ref
     host = w.host_inputs()
@@ -518,71 +668,87 @@ def run_workload(w, torch, ctb, dist, steps, warmup, rank, world, do_e2e, do_cpu
     nbytes = sum(t.numel() * t.element_size() for t in base.values() if hasattr(t, "numel"))
     nsets = max(2, min(8, -(-2 * L2_BYTES // max(nbytes, 1)) + 1))
     sets = [base] + [{k: (v.clone() if hasattr(v, "clone") else v) for k, v in base.items()} for _ in range(nsets - 1)]
-    ms, t0, t1 = device_time(torch, dist, lambda i: w.step(ctb, sets[i % nsets]), steps, warmup)
+    tm = time_graph(torch, dist, lambda i: w.step(ctb, sets[i % nsets]), steps, warmup, target_s)
     ctb.check_device_status(torch.cuda.current_device())
-    per = ms / steps
-    scale = 1e9 if w.unit == "GB/s" else 1e12
-    value = aggregate_value(w.work(), world, per, w.unit)
-    res = dict(name=w.name, metric=w.metric, unit=w.unit, value=value, ms_per_step=per, work_per_step=w.work(),
-               workload=w.describe(), l2="rotating %d input/output sets (%.0f MB total, L2 is 126 MB)" %
-               (nsets, nsets * nbytes / 1e6), t0=t0, t1=t1, launches=w.launches_per_step * steps,
-               timing="K steps captured in one CUDA graph, replayed between two events")
+    res = dict(name=w.name, metric=w.metric, unit=w.unit, ms_per_step=tm["ms"], min_ms=tm["min_ms"], replays=tm["replays"],
+               work_per_step=w.work(), t0=tm["t0"], t1=tm["t1"], launches=w.launches_per_step * steps * tm["replays"],
+               l2="%d rotating input/output sets, %.0f MB" % (nsets, nsets * nbytes / 1e6))
     res["parity_err"] = w.check(host, sets[(warmup + steps - 1) % nsets], ref, np)
+    # the reference's protocol: single eager calls, kernel-only (outputs preallocated) and call surface (the wrapper
+    # that allocates its result, where the reference has one)
+    res["protocol"] = dict(zip(("min_ms", "mean_ms"), protocol_times(torch, lambda: w.step(ctb, base))))
+    if hasattr(w, "call_surface"):
+        res["protocol"].update(zip(("call_min_ms", "call_mean_ms"), protocol_times(torch, lambda: w.call_surface(ctb, base))))
     if do_e2e:
-        ins, outs = w.e2e_io(base)
-        w.step(ctb, base)  # outputs that the step itself allocates exist from here on
-        pin_in = {k[0]: torch.from_numpy(host[k[0]] if k[0] in host else base[k[0]].cpu().numpy()).pin_memory() for k in ins}
-        pin_out = {k[0]: torch.empty(base[k[0]].shape, dtype=base[k[0]].dtype).pin_memory() for k in outs}
-
-        def e2e_step(i):
-            for k, h in pin_in.items():
-                base[k].copy_(h, non_blocking=True)
-            w.step(ctb, base)
-            for k, h in pin_out.items():
-                h.copy_(base[k], non_blocking=True)
-        ems, _, _ = device_time(torch, dist, e2e_step, max(3, steps // 4), 3, graph=False)
-        eper = ems / max(3, steps // 4)
-        res["e2e"] = dict(value=w.work() * world / (eper * 1e-3) / scale, unit=w.unit, ms_per_step=eper,
-                          h2d_bytes_per_step=sum(h.numel() * h.element_size() for h in pin_in.values()),
-                          d2h_bytes_per_step=sum(h.numel() * h.element_size() for h in pin_out.values()))
+        ems, bi, bo = e2e_pipelined(torch, w, ctb, host, base, max(4, min(12, steps // 2)))
+        ems = max_over_ranks(ems, torch, dist, "cuda")
+        res["e2e"] = dict(ms_per_step=ems, h2d_bytes_per_step=bi, d2h_bytes_per_step=bo)
     if do_cpu and rank == 0:
         res["cpu_baseline"] = cpu_time(w, host)
     return res
 
 
-def run_moe_ep(torch, ctb, dist, steps, warmup, rank, world):
-    """Expert-parallel MoE at N > 1 (strong scaling): 4096 tokens in total, T/N tokens and 32/N experts per rank,
-    router on the local tokens, token rows and expert outputs cross NVLink as stores into peer memory issued by the
-    dispatch kernel and by the down projection's epilogue (no all-to-all, no host synchronisation).  Eager
-    launches, timed with CUDA events, max over ranks."""
+def run_moe_ep(torch, ctb, dist, steps, warmup, rank, world, local):
+    """Expert-parallel MoE at N > 1 (strong scaling): BASELINE's 4096 tokens in total, 4096/N tokens and 32/N experts
+    per rank, through the library's C entry point (ctb_moe_ffn_ep) in both exchange modes.  Checked against the
+    single-GPU cutile_moe on the gathered problem (bit for bit, every rank, outside the timed regions) and, for 256
+    tokens, against the float64 oracle."""
     import numpy as np
-    from oracle import inputs
+    from oracle import inputs, ref
     T, H, E, I, topk = 4096, 1024, 32, 2048, 2
     if E % world or T % world:
         return None
     Tl, El = T // world, E // world
-    g = np.random.default_rng(4)
-    X = torch.from_numpy(g.standard_normal((T, H), dtype=np.float32).astype(np.float16)[rank * Tl:(rank + 1) * Tl]).cuda()
-    Wr = torch.from_numpy((0.02 * g.standard_normal((E, H), dtype=np.float32)).astype(np.float16)).cuda()
-    gw = torch.Generator(device="cuda").manual_seed(100 + rank)  # this rank's expert shard, N(0, 0.02)
-    w1 = (0.02 * torch.randn(El, 2 * I, H, device="cuda", generator=gw)).half()
-    w2 = (0.02 * torch.randn(El, H, I, device="cuda", generator=gw)).half()
+    d = inputs.moe(tokens=T, hidden=H, experts=E, inter=I, topk=topk, seed=4)  # the same arrays on every rank
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    my, mine = slice(rank * Tl, (rank + 1) * Tl), slice(rank * El, (rank + 1) * El)
+    X, Wr = dev(d["X"][my]), dev(d["Wr"])
+    w1, w2 = dev(d["w1"][mine]), dev(d["w2"][mine])
+    ep = ctb.multi.EpRank(Tl, H, topk, torch.device("cuda", local))
+    ctb.multi.reserve_workspace(local, max(ctb.multi.workspace_bytes("moe_ep", Tl, H, I, El, topk, 128, world),
+                                           ctb.multi.workspace_bytes("moe_ffn", T, H, I, E, topk, 128)))
+    # ---- correctness at the measured configuration
+    Xf, w1f, w2f = dev(d["X"]), dev(d["w1"]), dev(d["w2"])
+    gf, idf = ctb.moe.moe_router(Xf, Wr, topk)
+    full = ctb.moe.cutile_moe(Xf, w1f, w2f, gf, idf, 128, 128, 64)
+    g, ids = ctb.moe.moe_router(X, Wr, topk)
+    same = {}
+    for mode in ("peer", "nccl"):
+        out = ep.cutile_moe_ep(X, w1, w2, g, ids, E, 128, 128, 64, a2a_mode=mode)
+        torch.cuda.synchronize()
+        t = torch.tensor([1 if torch.equal(out, full[my]) else 0], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        same[mode] = bool(t.item())
+    sample = np.arange(0, T, T // 256)
+    rid, rg, _ = ref.moe_router(d["X"][sample], d["Wr"], topk)
+    perr = ref.rel_fro(full.cpu().numpy()[sample], ref.moe_ffn(d["X"][sample], d["w1"], d["w2"], rg, rid)) if rank == 0 else None
+    del Xf, w1f, w2f, full
+    torch.cuda.empty_cache()
+    # ---- timing.  The expert shard is rotated through enough copies to exceed twice the L2 (the 1-GPU moe_4096
+    # row streams its weights from HBM as well).
+    shard_bytes = (w1.numel() + w2.numel()) * 2
+    nsets = max(2, -(-2 * L2_BYTES // shard_bytes) + 1)
+    wsets = [(w1, w2)] + [(w1.clone(), w2.clone()) for _ in range(nsets - 1)]
+    outs = torch.empty((Tl, H), dtype=torch.float16, device="cuda")
 
-    bufs = ctb.moe.EpPeerBuffers(Tl, H, topk, X.device)
-
-    def step(i):
-        w, ids = ctb.moe.moe_router(X, Wr, topk)
-        return ctb.moe.cutile_moe_ep_peer(bufs, X, w1, w2, w, ids, E, 128, 128, 64)
-    ms, _, _ = device_time(torch, dist, step, steps, warmup, graph=True)  # every launch is a kernel of this library
-    ctb.check_device_status(torch.cuda.current_device())
-    per = ms / steps
+    def step(mode):
+        def f(i):
+            a, b = wsets[i % nsets]
+            gg, ii = ctb.moe.moe_router(X, Wr, topk)
+            ep.cutile_moe_ep(X, a, b, gg, ii, E, 128, 128, 64, a2a_mode=mode, out=outs)
+        return f
     flops = 2 * T * topk * H * I * 3
-    return dict(metric="moe_ffn_tflops", value=flops / (per * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=per,
-                scaling="strong", workload=f"expert-parallel MoE f16, {T} tokens in total ({Tl} per rank), {El} of {E} "
-                "experts per rank, top-2; step = router + dispatch kernel storing token rows into the owners' peer "
-                "memory + barrier kernel + expert FFN whose epilogue stores the outputs into the senders' peer memory "
-                "+ barrier kernel + sum over top-k", timing="K steps captured in a CUDA graph per rank and replayed "
-                "between two CUDA events, max over ranks")
+    res = dict(metric="moe_ffn_tflops", u="TFLOP/s", bit_identical=same, err=perr, scaling="strong",
+               workload=f"{T} tokens, top-2, {El} of {E} experts and {Tl} tokens per rank, seed 4",
+               l2=f"{nsets} rotating copies of the expert shard ({nsets * shard_bytes / 1e6:.0f} MB per rank)")
+    tp = time_graph(torch, dist, step("peer"), steps, warmup, 0.05)  # kernel launches only: captured in a graph
+    ctb.check_device_status(local)
+    res.update(v=flops / (tp["ms"] * 1e-3) / 1e12, ms=tp["ms"], min_ms=tp["min_ms"], replays=tp["replays"])
+    tn = time_graph(torch, dist, step("nccl"), max(3, steps // 4), 2, 0.02, graph=False)  # reads counts on the host
+    ctb.check_device_status(local)
+    res["nccl"] = dict(v=flops / (tn["ms"] * 1e-3) / 1e12, ms=tn["ms"])
+    ep.close()
+    return res
 
 
 def cpu_time(w, host, repeats=3):
@@ -598,8 +764,35 @@ def cpu_time(w, host, repeats=3):
     scale = 1e9 if w.unit == "GB/s" else 1e12
     # numpy's element-wise code is single-threaded; only the OpenBLAS matmuls use every core
     threads = int(os.environ.get("OPENBLAS_NUM_THREADS", os.cpu_count() or 1)) if w.uses_blas else 1
-    return dict(value=w.work() * frac / best / scale, unit=w.unit, cores=threads, kind="port",
+    return dict(value=r4(w.work() * frac / best / scale), unit=w.unit, cores=threads, kind="port",
                 sample=sample + f"; best of {repeats}; {best * 1e3:.1f} ms", host_cpus=os.cpu_count())
+
+
+def comparators(torch, pk):
+    """Library kernels on the same box, for orientation only (never on the measured path): cuBLAS TF32 GEMM, whose rate
+    serves as the TF32 tensor peak of the GEMM rooflines, and torch's scaled_dot_product_attention on the FMHA shapes."""
+    out = {}
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        n = 8192
+        a, b = torch.randn(n, n, device="cuda"), torch.randn(n, n, device="cuda")
+        best = min(protocol_times(torch, lambda: torch.matmul(a, b), 3, 10)[0], 1e9)
+        out["cublas_tf32_8192_tflops"] = 2 * n ** 3 / (best * 1e-3) / 1e12
+        del a, b
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    import torch.nn.functional as F
+    for bsz in (8, 64):
+        g = torch.Generator(device="cuda").manual_seed(3)
+        sets = [[torch.randn(bsz, 16, 1024, 64, device="cuda", generator=g).half() for _ in range(3)]
+                for _ in range(4 if bsz == 8 else 2)]
+        tm = time_graph(torch, None, lambda i: F.scaled_dot_product_attention(*sets[i % len(sets)], is_causal=True, scale=0.125),
+                        10, 3, 0.05)
+        out[f"sdpa_b{bsz}_tflops"] = 4 * bsz * 16 * 64 * 1024 * 1025 // 2 / (tm["ms"] * 1e-3) / 1e12
+        del sets
+    torch.cuda.empty_cache()
+    return out
 
 
 _RESULT_FD = None
@@ -623,23 +816,29 @@ def emit(line):
     os.write(fd, data)
 
 
+def r4(x):
+    """Four significant digits: the line has to stay short enough to be kept whole by whoever records it."""
+    return None if x is None else float(f"{x:.4g}")
+
+
 def main():
     keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline", default=None)
     ap.add_argument("--only", default=None, help="comma-separated workload names (default: all at N=1)")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-compare", action="store_true", help="skip the library comparators (cuBLAS TF32, torch SDPA)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     reg = registry()
-    headline = a.headline or ("fmha_causal" if "fmha_causal" in reg else "softmax_tma")
+    headline = a.headline or "fmha_causal"
     hw = reg[headline]
     pk = peaks()
 
@@ -665,65 +864,146 @@ def main():
     torch.cuda.set_device(local)
     dist = None
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")  # plain peer stores and ring/tree NCCL: no multicast objects
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     sampler = ClockSampler(local)
     sampler.start()
-    time.sleep(0.3)
-    head = run_workload(hw, torch, ctb, dist, a.steps, a.warmup, rank, world, True, not a.no_cpu and world == 1)
+    time.sleep(0.2)
+    scale = lambda u: 1e9 if u == "GB/s" else 1e12
+
+    # ---- headline.  N = 1: BASELINE's single-GPU configuration (batch 8).  N > 1: its multi-GPU configuration, batch 64
+    # sharded by batch over the ranks with no data-path collective (strong scaling: the total work is fixed).
+    sharded = world > 1 and headline == "fmha_causal"
+    if sharded:
+        hw = reg["fmha_b64"]
+        lo, hi = shard_range(hw.B, world, rank)
+        head = run_workload(ShardedFmha(hw, lo, hi), torch, ctb, dist, a.steps, a.warmup, rank, world, True, False, 0.25)
+        head["work_total"] = hw.work()
+    else:
+        head = run_workload(hw, torch, ctb, dist, a.steps, a.warmup, rank, world, True, not a.no_cpu and world == 1, 0.25)
+        head["work_total"] = hw.work() * world
     clocks = sampler.summary(head["t0"], head["t1"])
-    others = {}
+    tf32_peak = None
+    comp = {}
+    if rank == 0 and world == 1 and not a.no_compare:
+        comp = comparators(torch, pk)
+        tf32_peak = comp.get("cublas_tf32_8192_tflops")
+
+    def peak_of(w):
+        if w.bound == "hbm":
+            return pk["hbm"], "GB/s"
+        if getattr(w, "peak_scale", 1.0) != 1.0:  # TF32: the cuBLAS TF32 rate measured in this run, else half the bf16 figure
+            return (tf32_peak or pk["tensor"] * w.peak_scale), "TFLOP/s"
+        return pk["tensor"], "TFLOP/s"
+
+    def roof(r, w, work=None):
+        peak, unit = peak_of(w)
+        rw = work if work is not None else (w.roof_work() if hasattr(w, "roof_work") else r["work_per_step"])
+        ach = rw / (r["ms_per_step"] * 1e-3) / scale(unit)
+        return dict(bound=w.bound, achieved=r4(ach), peak=r4(peak), unit=unit, frac=r4(ach / peak),
+                    traffic=profile_traffic(w.name), kernel=w.kernel, peak_source=pk["source"])
+
+    kernels = {}
     if world == 1:
         names = [n for n in reg if n != headline]
         if a.only is not None:
             names = [n for n in a.only.split(",") if n in reg and n != headline]  # "--only none": headline alone
         for n in names:
-            r = run_workload(reg[n], torch, ctb, None, a.steps, a.warmup, rank, 1, True, not a.no_cpu)
-            r["clocks"] = sampler.summary(r["t0"], r["t1"])
-            others[n] = r
-    if world > 1:
+            w = reg[n]
+            r = run_workload(w, torch, ctb, None, a.steps, a.warmup, rank, 1, True, not a.no_cpu, 0.1)
+            ck = sampler.summary(r["t0"], r["t1"])
+            rf = roof(r, w)
+            # v value [GB/s for hbm-bound, TFLOP/s for tensor-bound], ms mean per step, min best replay, frac of the binding
+            # roofline (b), traf DRAM bytes per step from the ncu summary, e2e ms per step from pinned host memory,
+            # p1/pc min ms of the reference's protocol (kernel only / allocating wrapper), cpu baseline in the value's unit,
+            # err parity figure, mhz median SM clock inside the timed region
+            e = dict(v=r4(w.work() / (r["ms_per_step"] * 1e-3) / scale(w.unit)), ms=r4(r["ms_per_step"]), min=r4(r["min_ms"]),
+                     frac=rf["frac"], b=rf["bound"][0], traf=None if rf["traffic"] is None else int(rf["traffic"]),
+                     e2e=r4(r["e2e"]["ms_per_step"]), p1=r4(r["protocol"]["min_ms"]), pc=r4(r["protocol"].get("call_min_ms")),
+                     cpu=r4((r.get("cpu_baseline") or {}).get("value")), err=r4(r["parity_err"]), mhz=ck.get("sm_mhz"))
+            kernels[n] = {k: v for k, v in e.items() if v is not None}
+    else:
+        # batched GEMM sharded by batch (strong scaling, no collective)
+        bw = reg["bgemm_tf32"]
+        lo, hi = shard_range(bw.batch, world, rank)
+        r = run_workload(ShardedBgemm(bw, lo, hi), torch, ctb, dist, a.steps, a.warmup, rank, world, False, False, 0.05)
+        if True:
+            kernels["bgemm_tf32_sharded"] = dict(v=r4(bw.work() / (r["ms_per_step"] * 1e-3) / 1e12), u="TFLOP/s", ms=r4(r["ms_per_step"]),
+                                                 min_ms=r4(r["min_ms"]), scaling="strong",
+                                                 workload=f"batch 8 of A[1024x2048]*B[2048x512] TF32 split by batch over {world} ranks, "
+                                                          "no collective")
         try:
-            ep = run_moe_ep(torch, ctb, dist, max(5, min(a.steps, 30)), 3, rank, world)
+            ep = run_moe_ep(torch, ctb, dist, max(5, min(a.steps, 20)), 3, rank, world, local)
         except Exception as e:  # the headline line is still reported; the entry says why it is missing
             sys.stderr.write(f"moe_ep_4096 failed on rank {rank}: {e!r}\n")
             ep = dict(metric="moe_ffn_tflops", unavailable=repr(e)[:300])
         if ep is not None:
-            others["moe_ep_4096"] = ep
+            for k in ("v", "ms", "min_ms", "err"):
+                if k in ep:
+                    ep[k] = r4(ep[k])
+            kernels["moe_ep_4096"] = ep
     sampler.stop()
 
-    # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of each workload's dominant kernel,
-    # from the ncu captures summarised in profiles/<kernel>_<workload>.txt (for the MoE workloads: gate/up + down
-    # launches of moe_gemm_kernel).  Writes are below the algorithmic output bytes wherever the L2 still holds the
-    # output when the kernel ends.
-    ncu_traffic = {"fmha_causal": 51.35e6, "softmax_tma": 84.48e6, "softmax_chunked": 83.28e6, "layernorm_fwd": 85.46e6,
-                   "layernorm_bwd": 170.13e6, "gemm_tf32": 383.89e6, "bgemm_tf32": 104.26e6, "moe_256": 414.27e6,
-                   "moe_4096": 483.97e6}
-
-    def roof(r, w):
-        peak = pk["hbm"] if w.bound == "hbm" else pk["tensor"] * getattr(w, "peak_scale", 1.0)
-        rw = w.roof_work() if hasattr(w, "roof_work") else r["work_per_step"]
-        ach = rw / (r["ms_per_step"] * 1e-3) / (1e9 if w.bound == "hbm" else 1e12)
-        return dict(bound=w.bound, achieved=ach, peak=peak, unit="GB/s" if w.bound == "hbm" else "TFLOP/s",
-                    frac=ach / peak, traffic=ncu_traffic.get(w.name), kernel=w.kernel,
-                    peak_source=pk["source"])
-
     if rank == 0:
-        line = dict(metric=hw.metric, value=head["value"], unit=hw.unit, n_gpus=world, steps=a.steps, warmup=a.warmup,
-                    ms_per_step=head["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None,
-                    dtype=hw.dtype, data="synthetic",
-                    config={"workload": hw.describe(), "l2": head["l2"], "per_gpu": "same workload on every rank",
-                            "timing": head["timing"]},
-                    clocks=clocks, e2e=head.get("e2e"), gpu_launches=head["launches"], roofline=roof(head, hw),
-                    cpu_baseline=head.get("cpu_baseline"), parity_err=head["parity_err"])
-        if others:
-            line["kernels"] = {n: (r if n not in reg else
-                                   dict(metric=r["metric"], value=r["value"], unit=r["unit"],
-                                        ms_per_step=r["ms_per_step"], roofline=roof(r, reg[n]), e2e=r.get("e2e"),
-                                        cpu_baseline=r.get("cpu_baseline"), parity_err=r["parity_err"],
-                                        workload=r["workload"], clocks=r["clocks"])) for n, r in others.items()}
+        per = head["ms_per_step"]
+        value = head["work_total"] / (per * 1e-3) / scale(hw.unit)
+        e2e = head.get("e2e")
+        if e2e:
+            e2e = dict(value=r4(head["work_total"] / (e2e["ms_per_step"] * 1e-3) / scale(hw.unit)), unit=hw.unit,
+                       ms_per_step=r4(e2e["ms_per_step"]), h2d_bytes_per_step=e2e["h2d_bytes_per_step"],
+                       d2h_bytes_per_step=e2e["d2h_bytes_per_step"], how="pinned host buffers; H2D, kernels, D2H on 3 streams")
+        cfg = {"workload": hw.describe(), "l2": head["l2"], "replays": head["replays"],
+               "timing": "K steps per CUDA graph, R replays each between two CUDA events, mean over replays, max over ranks",
+               "per_gpu": (f"batch {hw.B // world} of 64 per rank, sharded by batch, no collective" if sharded
+                           else "the whole workload on one GPU")}
+        line = dict(metric=hw.metric, value=r4(value), unit=hw.unit, n_gpus=world, steps=a.steps, warmup=a.warmup,
+                    ms_per_step=r4(per), min_ms_per_step=r4(head["min_ms"]), higher_is_better=True,
+                    scaling="strong" if sharded else "weak", vs_baseline=None, dtype=hw.dtype, data="synthetic", config=cfg,
+                    clocks=clocks, e2e=e2e, gpu_launches=head["launches"],
+                    roofline=roof(head, hw, work=head["work_per_step"]), cpu_baseline=head.get("cpu_baseline"),
+                    parity_err=r4(head["parity_err"]),
+                    protocol=dict({k: r4(v) for k, v in head["protocol"].items()},
+                                  how="benchmarks.jl: 5 warm-up, 20 single calls, min/mean ms; call_* = allocating wrapper"))
+        if comp:  # library kernels on the same box, for orientation (cuBLAS TF32 is the TF32 peak of the GEMM rows)
+            line["comparators"] = {k: r4(v) for k, v in comp.items()}
+        if kernels:
+            line["kernels"] = kernels
         emit(line)
     if dist is not None:
+        dist.barrier()
         dist.destroy_process_group()
+
+
+class ShardedFmha(FmhaB64):
+    """Batches [lo, hi) of the batch-64 FMHA problem: one rank's share when the batch * head items are split by batch
+    (the (D, S, H, B) arrays are batch-last, so a share is a contiguous slab)."""
+
+    def __init__(self, whole, lo, hi):
+        self.lo, self.hi, self.B = lo, hi, hi - lo
+
+    def host_inputs(self):
+        d = FmhaB64().host_inputs()
+        return {k: (v[self.lo:self.hi] if k in ("Q", "K", "V") else v) for k, v in d.items()}
+
+    def check(self, host, st, ref, np):
+        sl = (slice(self.B - 1, self.B), slice(14, 16))
+        want = ref.fmha(host["Q"][sl], host["K"][sl], host["V"][sl], causal=True)
+        return ref.rel_fro(st["Out"][sl].cpu().numpy(), want)
+
+
+class ShardedBgemm(BatchedGemm):
+    """Batches [lo, hi) of the batch-8 GEMM problem (batch-last arrays: a contiguous slab per rank)."""
+
+    def __init__(self, whole, lo, hi):
+        self.lo, self.hi, self.batch = lo, hi, hi - lo
+
+    def host_inputs(self):
+        d = BatchedGemm().host_inputs()
+        return {k: (v[self.lo:self.hi] if k in ("A", "B") else v) for k, v in d.items()}
+
+    def check(self, host, st, ref, np):
+        return ref.rel_fro(st["C"][0].cpu().numpy(), ref.gemm(host["A"][0], host["B"][0]))
 
 
 if __name__ == "__main__":
