@@ -428,6 +428,76 @@ class FmhaB64(Fmha):
         return ref.rel_fro(st["Out"][sl].cpu().numpy(), want)
 
 
+class VecAdd(Workload):
+    name = "vadd"
+    metric = "vadd_gbps"
+    unit = "GB/s"
+    kernel = "vadd_kernel"
+    n = 2 ** 27
+
+    def describe(self):
+        return "c = a + b, f32, 2^27 elements ~ U(0,1) seed 5 (examples/vadd.jl benchmark shape)"
+
+    def work(self):
+        return 3 * self.n * 4
+
+    def host_inputs(self):
+        from oracle import inputs
+        return inputs.vadd((self.n,), seed=5)
+
+    def to_device(self, host, torch):
+        a, b = torch.from_numpy(host["a"]).cuda(), torch.from_numpy(host["b"]).cuda()
+        return dict(a=a, b=b, c=torch.empty_like(a))
+
+    def step(self, ctb, st):
+        ctb.vadd.vec_add_kernel_1d(st["a"], st["b"], st["c"], 1024)
+
+    def e2e_io(self, st):
+        return [("a",), ("b",)], [("c",)]
+
+    def cpu_step(self, host, ref, np):
+        a, b = host["a"], host["b"]
+        return (lambda: ref.vadd(a, b)), 1.0, "full 2^27 elements, numpy float32"
+
+    def check(self, host, st, ref, np):
+        return float(np.max(np.abs(st["c"].cpu().numpy() - ref.vadd(host["a"], host["b"]))))  # exact: 0
+
+
+class Transpose(Workload):
+    name = "transpose"
+    metric = "transpose_gbps"
+    unit = "GB/s"
+    kernel = "transpose_kernel"
+    m = n = 8192
+
+    def describe(self):
+        return "y = transpose(x), f32 8192x8192 ~ U(0,1) seed 6 (examples/transpose.jl benchmark shape)"
+
+    def work(self):
+        return 2 * self.m * self.n * 4
+
+    def host_inputs(self):
+        from oracle import inputs
+        return inputs.transpose(self.m, self.n, seed=6)
+
+    def to_device(self, host, torch):
+        x = torch.from_numpy(host["x"]).cuda()
+        return dict(x=x, y=torch.empty(self.m, self.n, device="cuda"))
+
+    def step(self, ctb, st):
+        ctb.transpose.transpose_kernel(st["x"], st["y"], 64, 64)
+
+    def e2e_io(self, st):
+        return [("x",)], [("y",)]
+
+    def cpu_step(self, host, ref, np):
+        x = host["x"]
+        return (lambda: ref.transpose(x)), 1.0, "full 8192x8192, numpy float32"
+
+    def check(self, host, st, ref, np):
+        return float(np.max(np.abs(st["y"].cpu().numpy() - ref.transpose(host["x"]))))  # exact: 0
+
+
 class Moe(Workload):
     name = "moe_256"
     metric = "moe_ffn_tflops"
@@ -493,7 +563,7 @@ class Moe4096(Moe):
 
 def registry():
     w = [Fmha(), FmhaB64(), Moe(), Moe4096(), Gemm(), BatchedGemm(), LayerNormFwd(), LayerNormBwd(), Softmax(0), Softmax(1),
-         SoftmaxOnline()]
+         SoftmaxOnline(), VecAdd(), Transpose()]
     return {x.name: x for x in w}
 
 

@@ -187,6 +187,21 @@ int ctb_version_info(char* buf, size_t n) {
   return CTB_OK;
 }
 
+int ctb_validate_hints(int num_ctas, int occupancy, int opt_level, int num_worker_warps) {
+  // the reference's validate_hint (src/language/types.jl:864-882); CTB_HINT_UNSET = the keyword was not given
+  if (num_ctas != CTB_HINT_UNSET) {
+    if (num_ctas < 1 || num_ctas > 16) return fail(CTB_BAD_ARG, "num_ctas must be between 1 and 16, got %d", num_ctas);
+    if (!is_pow2(num_ctas)) return fail(CTB_BAD_ARG, "num_ctas must be a power of 2, got %d", num_ctas);
+  }
+  if (occupancy != CTB_HINT_UNSET && (occupancy < 1 || occupancy > 32))
+    return fail(CTB_BAD_ARG, "occupancy must be between 1 and 32, got %d", occupancy);
+  if (opt_level != CTB_HINT_UNSET && (opt_level < 0 || opt_level > 3))
+    return fail(CTB_BAD_ARG, "opt_level must be between 0 and 3, got %d", opt_level);
+  if (num_worker_warps != CTB_HINT_UNSET && num_worker_warps != 4 && num_worker_warps != 8)
+    return fail(CTB_BAD_ARG, "num_worker_warps must be either 4 or 8, got %d", num_worker_warps);
+  return CTB_OK;
+}
+
 int ctb_check_device_status(ctb_ctx* ctx, void* stream) {
   CTB_CHECK_CTX(ctx);
   cudaStream_t s = static_cast<cudaStream_t>(stream);

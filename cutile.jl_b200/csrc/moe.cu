@@ -913,7 +913,8 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
                 int K, int wrows, int N, int E, const __half* topk_w, const int* sorted_ids, const int* expert_ids,
                 const int* nblocks_dev, int nblocks_host, int max_blocks, int replicas, int mul_weight, int tile_m,
                 int total, void* C, long long ldc, int w_tokens = 0, int w_topk = 1, void* const* c_peer = nullptr,
-                int c_split = 0) {
+                int c_split = 0, int expect_blocks = -1) {
+  if (expect_blocks < 0) expect_blocks = max_blocks;
   CUtensorMap tw;
   uint64_t dims[3] = {(uint64_t)K, (uint64_t)wrows, (uint64_t)E};
   uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)K * wrows * 2};
@@ -934,8 +935,11 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
     p.c_peer[q] = c_peer ? (__half*)c_peer[q] : nullptr;
     if (c_split && c_peer && c_peer[q] && (uintptr_t)c_peer[q] % 16) p.c_vec = 0;
   }
-  // two 128-row weight tiles per item share one gathered token tile (MMA N = 256)
-  const int nw = (epi == EPI_SWIGLU || N >= 2 * kRows) ? 2 : 1;
+  // Two 128-row weight tiles per item share one gathered token tile (MMA N = 256), unless the (block, tile pair) items
+  // would leave more than half of the SMs without work: then single tiles, twice as many items.  `expect_blocks` is
+  // the caller's estimate of the blocks that will actually hold slots (max_blocks is only the capacity).
+  const int pairs = (N + 2 * kRows - 1) / (2 * kRows);
+  const int nw = (epi == EPI_SWIGLU) ? 2 : (N >= 2 * kRows && (long long)expect_blocks * pairs * 2 > ctx->sm_count) ? 2 : 1;
   p.n_tiles = epi == EPI_SWIGLU ? (N + kRows - 1) / kRows : (N + nw * kRows - 1) / (nw * kRows);
   // the token tile is the MMA's A operand with M = 128 rows whatever tile_m is: the instruction reads all of them
   p.stage_bytes = nw * kWTile + kRows * 128;
@@ -1028,6 +1032,8 @@ int moe_experts_rows(ctb_ctx* ctx, cudaStream_t st, const void* rows, int64_t ld
   int* s_exp = (int*)(w + o_exp);
   int* s_nb = (int*)(w + o_nb);
   __half* act = (__half*)(w + o_act);
+  // with rows from `world` ranks in the buffer (c_split rows each), about one rank's worth is for this rank's experts
+  const int expect_blocks = c_split > 0 ? (int)(c_split / tile_m + E_local) : blocks_cap;
   r = launch_align(ctx, st, ids, 32, (int)R, 1, (int)E_local, tile_m, s_tok, s_exp, s_nb, blocks_cap, /*skip_empty=*/1);
   if (r) return r;
   r = launch_gemm(ctx, st, EPI_SWIGLU, (const __half*)rows, ld_rows, (int)R, (const __half*)w1_local, (int)H,
@@ -1036,7 +1042,7 @@ int moe_experts_rows(ctb_ctx* ctx, cudaStream_t st, const void* rows, int64_t ld
   if (r) return r;
   return launch_gemm(ctx, st, EPI_F16, act, I, (int)R, (const __half*)w2_local, (int)I, (int)H, (int)H, (int)E_local,
                      (const __half*)gates, s_tok, s_exp, s_nb, -1, blocks_cap, 1, 1, tile_m, (int)R, C, ldc, 0, 1, c_peer,
-                     (int)c_split);
+                     (int)c_split, expect_blocks);
 }
 
 }  // namespace ctb_internal

@@ -52,7 +52,10 @@ SIGNATURES = {
     "ctb_status_string": [_i],
     "ctb_version_info": [C.c_char_p, C.c_size_t],
     "ctb_check_device_status": [_p, _p],
+    "ctb_validate_hints": [_i, _i, _i, _i],
     "ctb_softmax": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
+    "ctb_vadd": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i],
+    "ctb_transpose": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
     "ctb_layernorm_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i],
     "ctb_layernorm_bwd_dx_partial_dwdb": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64,
                                           _i, _i],

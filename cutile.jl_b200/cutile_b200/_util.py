@@ -14,13 +14,45 @@ def next_power_of_2(n):
     return p
 
 
-def handles(t):
-    """(context, raw stream handle) for the device that holds tensor `t`."""
+_HINT_KEYS = ("num_ctas", "occupancy", "opt_level", "num_worker_warps")
+
+
+def check_hints(hints):
+    """The launch keywords of `@cuda backend=cuTile ...` / `ct.launch` (src/launch.jl:855-869): `num_ctas`,
+    `occupancy`, `opt_level`, `num_worker_warps` are validated with the reference's ranges (validate_hint,
+    src/language/types.jl:864-882) and are advisory (the kernels pick their own configuration); `sm_arch`, `name`
+    and `dependent` are accepted; `stream` is honoured by handles().  Anything else is an error, as in the reference."""
+    vals = []
+    for k in _HINT_KEYS:
+        v = hints.get(k)
+        if v is None:
+            vals.append(-1)
+        elif isinstance(v, bool) or not isinstance(v, int):
+            raise _lib.CtbError(_lib.BAD_ARG, f"{k} must be an integer, got {type(v).__name__}")
+        else:
+            vals.append(v)
+    for k in hints:
+        if k not in _HINT_KEYS and k not in ("sm_arch", "name", "dependent", "stream"):
+            raise _lib.CtbError(_lib.BAD_ARG, f"unknown hint key: {k}")
+    if any(v != -1 for v in vals):
+        _lib.check(_lib.lib.ctb_validate_hints(*vals))
+
+
+def handles(t, hints=None):
+    """(context, raw stream handle) for the device that holds tensor `t`; `hints` are the launch keywords of the
+    call (checked; `stream`, a torch stream or a raw handle, replaces the current stream)."""
     if not isinstance(t, torch.Tensor) or not t.is_cuda:
         # the reference rejects host arrays the same way (src/language/types.jl:371-376)
         raise _lib.CtbError(_lib.BAD_ARG, "expected a CUDA tensor (device array); host arrays are not accepted")
     dev = t.device.index if t.device.index is not None else torch.cuda.current_device()
-    return _lib.context(dev), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    stream = None
+    if hints:
+        check_hints(hints)
+        stream = hints.get("stream")
+    if stream is None:
+        stream = torch.cuda.current_stream(dev)
+    raw = stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+    return _lib.context(dev), C.c_void_p(raw)
 
 
 def ptr(t):

@@ -14,9 +14,9 @@ def _dims(t, what):
     return t.shape[0], t.shape[1], t.shape[2], t.stride(1), t.stride(0)
 
 
-def batch_matmul_kernel(A, B, C, tm, tn, tk):
+def batch_matmul_kernel(A, B, C, tm, tn, tk, **hints):
     """batch_matmul_kernel(A, B, C, tm, tn, tk), examples/batchmatmul.jl:15-56."""
-    ctx, stream = handles(A)
+    ctx, stream = handles(A, hints)
     nb, K, M, lda, sA = _dims(A, "A")
     nb2, N, Kb, ldb, sB = _dims(B, "B")
     nb3, Nc, Mc, ldc, sC = _dims(C, "C")

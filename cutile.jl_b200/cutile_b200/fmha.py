@@ -12,9 +12,9 @@ from . import _lib
 from ._util import handles, ptr, dtype_code
 
 
-def fmha_kernel(Q, K, V, Out, qk_scale, input_pos, TILE_D, H, TILE_M, TILE_N, QUERY_GROUP_SIZE, CAUSAL, EVEN_K):
+def fmha_kernel(Q, K, V, Out, qk_scale, input_pos, TILE_D, H, TILE_M, TILE_N, QUERY_GROUP_SIZE, CAUSAL, EVEN_K, **hints):
     """fmha_kernel(...), examples/fmha.jl:20-139 (the launch inside cutile_fmha)."""
-    ctx, stream = handles(Q)
+    ctx, stream = handles(Q, hints)
     for t, name in ((Q, "Q"), (K, "K"), (V, "V"), (Out, "Out")):
         if t.dim() != 4 or not t.is_contiguous():
             raise _lib.CtbError(_lib.BAD_ARG, f"fmha: {name} must be a dense 4-D tensor")
@@ -31,7 +31,8 @@ def fmha_kernel(Q, K, V, Out, qk_scale, input_pos, TILE_D, H, TILE_M, TILE_N, QU
     return Out
 
 
-def cutile_fmha(Q, K, V, *, qk_scale=None, input_pos=0, tile_m=128, tile_n=128, query_group_size=1, causal=False):
+def cutile_fmha(Q, K, V, *, qk_scale=None, input_pos=0, tile_m=128, tile_n=128, query_group_size=1, causal=False,
+                **hints):
     """cutile_fmha(Q, K, V; qk_scale, input_pos, tile_m, tile_n, query_group_size, causal),
     examples/fmha.jl:146-168: allocates and returns Out."""
     B, H, Sq, D = Q.shape
@@ -40,4 +41,4 @@ def cutile_fmha(Q, K, V, *, qk_scale=None, input_pos=0, tile_m=128, tile_n=128, 
         qk_scale = 1.0 / math.sqrt(D)
     Out = torch.empty((B, H, Sq, Dv), dtype=Q.dtype, device=Q.device)
     return fmha_kernel(Q, K, V, Out, qk_scale, input_pos, D, H, tile_m, tile_n, query_group_size, causal,
-                       Skv % tile_n == 0)
+                       Skv % tile_n == 0, **hints)

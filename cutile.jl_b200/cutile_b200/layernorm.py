@@ -8,9 +8,9 @@ from . import _lib
 from ._util import handles, ptr, rows
 
 
-def layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N):
+def layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N, **hints):
     """layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N), examples/layernorm.jl:27-68."""
-    ctx, stream = handles(X)
+    ctx, stream = handles(X, hints)
     ldx, M, N = rows(X, "X")
     ldy, My, Ny = rows(Y, "Y")
     if (My, Ny) != (M, N) or W.numel() != N or B.numel() != N or Mean.numel() != M or Rstd.numel() != M:
@@ -19,11 +19,11 @@ def layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N):
                                           ldx, ldy, float(eps), int(TILE_N)))
 
 
-def layer_norm_bwd_dx_partial_dwdb(DX, DY, DW, DB, X, W, Mean, Rstd, Locks, GROUP_SIZE_M, TILE_N):
+def layer_norm_bwd_dx_partial_dwdb(DX, DY, DW, DB, X, W, Mean, Rstd, Locks, GROUP_SIZE_M, TILE_N, **hints):
     """layer_norm_bwd_dx_partial_dwdb(...), examples/layernorm.jl:118-171.
     `Locks` is accepted for signature compatibility and never touched; DW/DB
     need no zero-fill."""
-    ctx, stream = handles(X)
+    ctx, stream = handles(X, hints)
     ldx, M, N = rows(X, "X")
     lddy, _, _ = rows(DY, "DY")
     lddx, _, _ = rows(DX, "DX")
@@ -36,9 +36,9 @@ def layer_norm_bwd_dx_partial_dwdb(DX, DY, DW, DB, X, W, Mean, Rstd, Locks, GROU
         ptr(Locks), N, M, ldx, lddy, lddx, int(GROUP_SIZE_M), int(TILE_N)))
 
 
-def layer_norm_bwd_dwdb(DW, DB, FINAL_DW, FINAL_DB, TILE_M, TILE_N):
+def layer_norm_bwd_dwdb(DW, DB, FINAL_DW, FINAL_DB, TILE_M, TILE_N, **hints):
     """layer_norm_bwd_dwdb(DW, DB, FINAL_DW, FINAL_DB, TILE_M, TILE_N), examples/layernorm.jl:186-205."""
-    ctx, stream = handles(DW)
+    ctx, stream = handles(DW, hints)
     G, N = DW.shape
     _lib.check(_lib.lib.ctb_layernorm_bwd_dwdb(ctx, stream, ptr(DW), ptr(DB), ptr(FINAL_DW), ptr(FINAL_DB), N, G,
                                                int(TILE_M), int(TILE_N)))

@@ -7,9 +7,9 @@ from . import _lib
 from ._util import handles, ptr, rows, dtype_code
 
 
-def matmul_kernel(A, B, C, tm, tn, tk):
+def matmul_kernel(A, B, C, tm, tn, tk, **hints):
     """matmul_kernel(A, B, C, tm, tn, tk), examples/matmul.jl:28-60."""
-    ctx, stream = handles(A)
+    ctx, stream = handles(A, hints)
     lda, K, M = rows(A, "A")
     ldb, N, Kb = rows(B, "B")
     ldc, Nc, Mc = rows(C, "C")

@@ -57,10 +57,10 @@ def moe_align_tile_size(topk_ids, tile_m, num_experts):
 
 
 def fused_moe_kernel(A, B, C, topk_weights, sorted_token_ids, sorted_expert_ids, num_token_replicas,
-                     mul_routed_weight, TILE_M, TILE_N, TILE_K):
+                     mul_routed_weight, TILE_M, TILE_N, TILE_K, **hints):
     """fused_moe_kernel(...), examples/moe.jl:45-105.  A [tokens, K]; B [E, N, K]; C [total, N];
     topk_weights flat [total] (slot fastest), as invoke_fused_moe_kernel passes it (:193)."""
-    ctx, stream = handles(A)
+    ctx, stream = handles(A, hints)
     a_cols, K = A.shape
     E, N, Kb = B.shape
     c_cols, Nc = C.shape
@@ -77,10 +77,10 @@ def fused_moe_kernel(A, B, C, topk_weights, sorted_token_ids, sorted_expert_ids,
     return C
 
 
-def silu_and_mul_kernel(A, B, C, TILE_N):
+def silu_and_mul_kernel(A, B, C, TILE_N, **hints):
     """silu_and_mul_kernel(A, B, C, TILE_N), examples/moe.jl:110-128.  A, B may be row
     views (halves of the gate/up buffer, :210-211): torch [cols, n] with any row stride."""
-    ctx, stream = handles(A)
+    ctx, stream = handles(A, hints)
     cols, n = C.shape
     for t in (A, B, C):
         if t.shape != (cols, n) or (n > 1 and t.stride(1) != 1):

@@ -62,6 +62,16 @@ int ctb_version_info(char* buf, size_t n);
  * expiry or a bad index since the last call. */
 int ctb_check_device_status(ctb_ctx* ctx, void* stream);
 
+/* Launch hints of the reference's launch layer (`@cuda backend=cuTile num_ctas=... occupancy=... opt_level=...
+ * num_worker_warps=...`, src/launch.jl:855-869), validated with the reference's ranges (validate_hint,
+ * src/language/types.jl:864-882): num_ctas a power of two in [1, 16], occupancy in [1, 32], opt_level in [0, 3],
+ * num_worker_warps 4 or 8; CTB_HINT_UNSET for a keyword that was not given.  The hints are advisory here: the
+ * hand-written kernels choose cluster size, occupancy and warp roles themselves, so the host bindings check the
+ * values (CTB_BAD_ARG with the reference's message for a bad one) and pass nothing on.  `stream` is honoured: it is
+ * the stream argument of every entry point.  `dependent` (programmatic dependent launch) is accepted and ignored. */
+#define CTB_HINT_UNSET (-1)
+int ctb_validate_hints(int num_ctas, int occupancy, int opt_level, int num_worker_warps);
+
 /* ---- Row softmax -------------------------------------------------------- */
 /* softmax_tma_kernel(output, input, TILE_SIZE)      examples/softmax.jl:18-42
  * softmax_chunked_kernel(output, input, n_elems, TILE_SIZE)   :48-100
@@ -74,6 +84,20 @@ int ctb_check_device_status(ctb_ctx* ctx, void* stream);
  * dtype: CTB_F32 or CTB_F16 (computes in f32, like the reference). */
 int ctb_softmax(ctb_ctx* ctx, void* stream, void* output, const void* input, int64_t N, int64_t M, int64_t ld_out,
                 int64_t ld_in, int variant, int tile_size, int dtype);
+
+/* ---- Element-wise addition and transpose ----------------------------------- */
+/* vec_add_kernel_1d(a, b, c, tile)                    examples/vadd.jl:10-17
+ * vec_add_kernel_2d(a, b, c, tile_x, tile_y)          examples/vadd.jl:20-28
+ * vec_add_kernel_1d_gather(a, b, c, tile)             examples/vadd.jl:31-45
+ * c = a + b over `rows` rows of n contiguous elements (1-D: rows = 1); row strides lda/ldb/ldc in elements.  The
+ * gather/scatter variant addresses the same contiguous elements and runs the same kernel.  dtype CTB_F32 or CTB_F16
+ * (the sum is formed in the element type, like the reference's tile addition). */
+int ctb_vadd(ctb_ctx* ctx, void* stream, const void* a, const void* b, void* c, int64_t n, int64_t rows, int64_t lda,
+             int64_t ldb, int64_t ldc, int tile_x, int tile_y, int use_gather, int dtype);
+/* transpose_kernel(x, y, tm, tn)                      examples/transpose.jl:11-19
+ * y(n, m) = transpose of x(m, n), column-major with leading dimensions ldx/ldy; CTB_F32 or CTB_F16. */
+int ctb_transpose(ctb_ctx* ctx, void* stream, const void* x, void* y, int64_t m, int64_t n, int64_t ldx, int64_t ldy, int tm,
+                  int tn, int dtype);
 
 /* ---- LayerNorm ---------------------------------------------------------- */
 /* layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N)   examples/layernorm.jl:27-68

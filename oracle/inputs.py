@@ -76,3 +76,17 @@ def moe(tokens=256, hidden=1024, experts=32, inter=2048, topk=2, seed=4):
         w2[e] = (0.02 * g.standard_normal((hidden, inter), dtype=np.float32)).astype(np.float16)
     return dict(X=X, Wr=Wr, w1=w1, w2=w2, tokens=tokens, hidden=hidden,
                 experts=experts, inter=inter, topk=topk)
+
+
+def vadd(shape=(2 ** 27,), seed=5, dtype=np.float32):
+    """a, b ~ U(0,1) (``examples/vadd.jl:52-64``: cuRAND.rand); benchmark shape 2^27 elements."""
+    g = np.random.default_rng(seed)
+    a = g.random(shape, dtype=np.float32).astype(dtype)
+    b = g.random(shape, dtype=np.float32).astype(dtype)
+    return dict(a=a, b=b, shape=tuple(shape))
+
+
+def transpose(m=8192, n=8192, seed=6, dtype=np.float32):
+    """x(M, N) ~ U(0,1) (``examples/transpose.jl:25-36``), numpy x[N, M]; benchmark shape 8192 x 8192."""
+    g = np.random.default_rng(seed)
+    return dict(x=g.random((n, m), dtype=np.float32).astype(dtype), m=m, n=n)

@@ -208,6 +208,16 @@ def moe_ffn(X, w1, w2, topk_weights, topk_ids, dtype=np.float64):
 
 
 # ------------------------------------------------------------------- error norms
+def vadd(a, b):
+    """c = a + b in the element type (``examples/vadd.jl:127-129``: ``Array(result.c) ≈ Array(a) + Array(b)``)."""
+    return a + b
+
+
+def transpose(x):
+    """y = transpose(x) (``examples/transpose.jl:58-60``).  numpy x[N, M] holds Julia x(M, N); the result holds y(N, M)."""
+    return np.ascontiguousarray(x.T)
+
+
 def rel_fro(out, ref):
     """||out-ref||_F / ||ref||_F, the norm-wise measure Julia's ``isapprox`` uses
     on arrays (``examples/matmul.jl:100``)."""

@@ -96,3 +96,20 @@ def test_multi_gpu_entry_points_fail_on_the_host_side():
     assert wb("nothing", 1, 2, 3) == 0 and wb("moe_ffn", 1, 2) == 0
     with pytest.raises(cutile_b200.CtbError):
         cutile_b200.multi.Group([0, 0])
+
+
+def test_launch_hints_follow_the_reference_rules():
+    """num_ctas / occupancy / opt_level / num_worker_warps are validated like validate_hint
+    (src/language/types.jl:864-882); unknown keywords are refused; sm_arch, name, dependent and stream are accepted."""
+    import cutile_b200
+    from cutile_b200 import _lib
+    from cutile_b200._util import check_hints
+    check_hints(dict(num_ctas=2, occupancy=2, opt_level=3, num_worker_warps=8, sm_arch="10.0", dependent=False, name="k"))
+    assert _lib.lib.ctb_validate_hints(-1, -1, -1, -1) == _lib.OK
+    for bad, word in ((dict(num_ctas=3), "power of 2"), (dict(num_ctas=32), "between 1 and 16"),
+                      (dict(occupancy=0), "between 1 and 32"), (dict(opt_level=4), "between 0 and 3"),
+                      (dict(num_worker_warps=6), "either 4 or 8"), (dict(whatever=1), "unknown hint key"),
+                      (dict(occupancy=2.5), "must be an integer")):
+        with pytest.raises(cutile_b200.CtbError) as e:
+            check_hints(bad)
+        assert e.value.status == _lib.BAD_ARG and word in str(e.value)

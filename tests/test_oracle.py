@@ -111,3 +111,11 @@ def test_moe_router_and_ffn_small():
             u = d["w1"][e, I:].astype(np.float64) @ x
             acc += float(gates[s, t]) * (d["w2"][e].astype(np.float64) @ (g / (1 + np.exp(-g)) * u))
         assert np.allclose(out[t], acc)
+
+
+def test_vadd_and_transpose_restatements():
+    d = inputs.vadd((1000,), seed=1)
+    assert np.array_equal(ref.vadd(d["a"], d["b"]), d["a"] + d["b"]) and ref.vadd(d["a"], d["b"]).dtype == np.float32
+    t = inputs.transpose(5, 3)
+    y = ref.transpose(t["x"])
+    assert y.shape == (5, 3) and y[4, 2] == t["x"][2, 4] and y.flags.c_contiguous
