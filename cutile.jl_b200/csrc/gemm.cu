@@ -20,6 +20,12 @@
 //              store C with coalesced 128-byte rows while the MMA warp already
 //              works on the next tile in the other accumulator.
 // Out-of-range parts of edge tiles are zero-filled by TMA and masked on store.
+//
+// Large problems run gemm_pair_kernel instead: the two CTAs of a 2-CTA cluster share one 256 x 256 tile
+// (tcgen05 cta_group::2, the counterpart of the reference's num_ctas = 2 hint on this architecture,
+// examples/matmul.jl:30).  Each CTA loads its own 128 rows of A and its own 128 columns of B per k-block, so an SM
+// takes in 32 KB of operands per 128 x 256 x (128 bytes of K) of MMA work instead of 48 KB: operand delivery, not the
+// tensor pipe, is what bounds the single-CTA kernel.  No load in this file is a cluster multicast.
 #include "ctx.h"
 #include "ptx.cuh"
 
@@ -221,6 +227,211 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+// ---- CTA-pair kernel ---------------------------------------------------------------------------------------------
+// Cluster of 2 CTAs = one 256 (M) x 256 (N) tile per step.  CTA rank r holds A rows [128 r, 128 r + 128) and
+// B columns [128 r, 128 r + 128) of the tile in its shared memory and the accumulator rows [128 r, 128 r + 128) x 256
+// columns in its TMEM.  Barriers: full[] lives in rank 0 and counts the bytes of both CTAs' loads; empty[] and
+// acc_full[] exist in both CTAs and are arrived by rank 0's multicast commits; acc_empty[] lives in rank 0 and is
+// arrived by the epilogue warps of both CTAs.
+constexpr int kPairStages = 6;
+constexpr int kPairTileM = 256;
+
+template <typename T>
+struct PairCfg {
+  using G = Cfg<T>;
+  static constexpr int B_ROWS = kTileN / 2;          // columns of the tile held by one CTA
+  static constexpr int B_BYTES = B_ROWS * 128;
+  static constexpr int STAGE_BYTES = G::A_BYTES + B_BYTES;  // per CTA
+};
+
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    gemm_pair_kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                     T* __restrict__ C, const Params p, int* status) {
+  using G = Cfg<T>;
+  using P = PairCfg<T>;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ __align__(8) uint64_t full[kPairStages], empty[kPairStages], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  if (threadIdx.x == 0) {
+    abort_s = 0;
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);  // four epilogue warps in each of the two CTAs
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmapA);
+    tma_prefetch_desc(&tmapB);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&tmem_base_s, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();  // the peer's barriers exist before anything is signalled on them
+  cluster_wait();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* abort = &abort_s;
+  const int nk = (p.K + G::BK - 1) / G::BK;
+
+  if (warp == 0) {
+    // ---- TMA producer (both CTAs): own halves of A and B, bytes counted on rank 0's full barrier
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int t = pair; t < p.num_tiles; t += num_pairs) {
+      int b, tm, tn;
+      tile_coords(p, t, b, tm, tn);
+      const int m0 = tm * kPairTileM + (int)rank * kTileM, n0 = tn * kTileN + (int)rank * P::B_ROWS;
+      bool ok = true;
+      for (int kb = 0; kb < nk; ++kb) {
+        ok = CTB_WARP_WAIT(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+        if (!ok) break;
+        unsigned char* sa = smem + (size_t)stage * P::STAGE_BYTES;
+        if (elect_one()) {
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * P::STAGE_BYTES);
+          const uint32_t bar = map_to_cta(&full[stage], 0);
+#pragma unroll
+          for (int j = 0; j < G::A_BOXES; ++j)
+            tma_load_3d_pair(sa + j * G::A_BOX_BYTES, &tmapA, m0 + j * G::CHUNK_M, kb * G::BK, b, bar);
+          tma_load_3d_pair(sa + G::A_BYTES, &tmapB, kb * G::BK, n0, b, bar);
+        }
+        __syncwarp();
+        if (++stage == kPairStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) break;
+    }
+  } else if (warp == 1) {
+    if (rank == 0) {
+      // ---- MMA issuer (rank 0 only): one instruction drives the tensor cores of both SMs
+      constexpr uint32_t idesc = make_idesc(G::FMT, kPairTileM, kTileN, /*A MN-major*/ 1, /*B K-major*/ 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int t = pair; t < p.num_tiles; t += num_pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!CTB_WARP_WAIT(&acc_empty[acc], acc_phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
+        tc_fence_after();
+        const uint32_t d = tmem_base + acc * kAccCols;
+        bool ok = true;
+        for (int kb = 0; kb < nk; ++kb) {
+          ok = CTB_WARP_WAIT(&full[stage], phase, status, DEV_TIMEOUT_TMA, abort);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + (size_t)stage * P::STAGE_BYTES);
+          const uint32_t sb = sa + G::A_BYTES;
+          if (elect_one()) {
+#pragma unroll
+            for (int k = 0; k < G::BK / G::UK; ++k) {
+              const uint64_t ad = make_sdesc(sa + k * G::UK * 128, G::A_BOX_BYTES, G::A_SBO, G::A_LAYOUT);
+              const uint64_t bd = make_sdesc_sw128(sb + k * 32, 0, 1024);
+              if constexpr (sizeof(T) == 4)
+                mma_tf32_ss_pair(d, ad, bd, idesc, (kb | k) != 0);
+              else
+                mma_f16_ss_pair(d, ad, bd, idesc, (kb | k) != 0);
+            }
+            tc_commit_pair(&empty[stage], 3);
+          }
+          __syncwarp();
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (elect_one()) tc_commit_pair(&acc_full[acc], 3);
+        __syncwarp();
+      }
+    }
+  } else {
+    const int sub = warp & 3;  // TMEM lanes [32*sub, 32*sub+32) belong to this warp
+    int it = 0;
+    for (int t = pair; t < p.num_tiles; t += num_pairs, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      int b, tm, tn;
+      tile_coords(p, t, b, tm, tn);
+      bool ok = CTB_WARP_WAIT(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
+      if (!ok) break;
+      tc_fence_after();
+      const int m = tm * kPairTileM + (int)rank * kTileM + sub * 32 + lane;
+      T* crow = C + (long long)b * p.strideC + m;
+      const uint32_t taddr = tmem_base + acc * kAccCols + ((uint32_t)(sub * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kTileN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tc_wait_ld();
+        const int n0 = tn * kTileN + c * 32;
+        if (m < p.M) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (n0 + j < p.N) {
+              if constexpr (sizeof(T) == 4)
+                crow[(long long)(n0 + j) * p.ldc] = __uint_as_float(r[j]);
+              else
+                crow[(long long)(n0 + j) * p.ldc] = __float2half_rn(__uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(&acc_empty[acc], 0));
+    }
+  }
+  // Neither CTA may leave (or free its TMEM) while the other can still read its shared memory, write its TMEM or
+  // signal its barriers: every thread of both CTAs meets here, also after an abort.
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+// How many 2-CTA clusters of gemm_pair_kernel the device runs at once (asked once per element type).
+template <typename T>
+int pair_clusters(ctb_ctx* ctx, size_t smem) {
+  static int cached[16] = {0};  // per device; 0 = not asked yet, -1 = unavailable
+  int& c = cached[ctx->device & 15];
+  if (c == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * ctx->sm_count);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<T>, &cfg);
+    c = (e == cudaSuccess && n > 0) ? n : -1;
+    if (e != cudaSuccess) (void)cudaGetLastError();
+  }
+  return c;
+}
+
 template <typename T>
 int launch(ctb_ctx* ctx, cudaStream_t st, const T* A, const T* B, T* C, int M, int N, int K, int batch, long long lda,
            long long ldb, long long ldc, long long sA, long long sB, long long sC) {
@@ -247,6 +458,33 @@ int launch(ctb_ctx* ctx, cudaStream_t st, const T* A, const T* B, T* C, int M, i
   Params p;
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   p.ldc = ldc; p.strideC = sC;
+  {
+    // CTA pairs when there are enough 256 x 256 tiles to occupy at least half of the SM pairs
+    const long long pairs = (long long)((M + kPairTileM - 1) / kPairTileM) * ((N + kTileN - 1) / kTileN) * batch;
+    if (M >= kPairTileM && N >= kTileN && pairs * 4 >= ctx->sm_count && pairs <= INT32_MAX) {
+      using P = PairCfg<T>;
+      CUtensorMap tb2;
+      uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)batch};
+      uint64_t str[2] = {(uint64_t)ldb * G::ES, (uint64_t)(batch > 1 ? sB : ldb * (long long)N) * G::ES};
+      uint32_t box[3] = {(uint32_t)G::BK, (uint32_t)P::B_ROWS, 1};
+      int r = make_tmap(&tb2, dt, 3, B, dims, str, box);
+      if (r) return r;
+      p.tiles_m = (M + kPairTileM - 1) / kPairTileM;
+      p.tiles_n = (N + kTileN - 1) / kTileN;
+      p.num_tiles = (int)pairs;
+      const size_t smem = (size_t)kPairStages * P::STAGE_BYTES + 1024;
+      auto k = gemm_pair_kernel<T>;
+      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return cuda_fail(e, "ctb_gemm: shared memory opt-in");
+      const int clusters = pair_clusters<T>(ctx, smem);
+      if (clusters > 0) {
+        const int grid = 2 * (int)std::min<long long>(pairs, clusters);
+        k<<<grid, kThreads, smem, st>>>(ta, tb2, C, p, ctx->dev_status);
+        CTB_CHECK_LAUNCH("ctb_gemm launch");
+        return CTB_OK;
+      }
+    }
+  }
   p.tiles_m = (M + kTileM - 1) / kTileM;
   p.tiles_n = (N + kTileN - 1) / kTileN;
   const long long nt = (long long)p.tiles_m * p.tiles_n * batch;

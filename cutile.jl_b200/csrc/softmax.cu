@@ -10,9 +10,10 @@
 //   rows that fit the registers of a CTA and are 16-byte aligned take the
 //   variant-0 kernel (one HBM read, one write; a chunk-by-chunk running
 //   (max, sum) over bulk-copied chunks was measured 1.5x slower because it
-//   evaluates two exponentials per element).  Longer or unaligned rows: a
-//   running (max, sum) per thread over chunks with 128-bit loads, the row kept
-//   in registers when it fits (one HBM read), else re-read once.
+//   evaluates two exponentials per element).  Longer rows that fit shared
+//   memory (up to 200 KB) are kept there whole, in chunks that are searched for
+//   the maximum as they land (still one HBM read, one write).  Anything else:
+//   a running (max, sum) per thread over chunks with 128-bit loads, re-read once.
 //
 // Both compute in f32 (examples/softmax.jl:32-35,92).  exp(x - max) is evaluated
 // as ex2.approx((x - max)*log2(e)) (relative error about 2^-22 plus the rounding
@@ -180,7 +181,108 @@ __global__ void __launch_bounds__(kThreads) softmax_staged_kernel(T* __restrict_
   if (tid == 0) bulk_wait<0>();  // stores complete before the CTA (and its smem) goes away
 }
 
-// ------------------------------------------------------------------ variant 1
+// ------------------------------------------------------------------ variant 1, rows that fit shared memory
+// Rows too long for the registers of a CTA but not for its shared memory (up to about 200 KB): one CTA per SM keeps
+// the whole row on chip, so HBM is still read once and written once.  The row arrives as kRowChunks bulk copies, each
+// with its own mbarrier; the threads look for the maximum of a chunk as soon as it has landed, under the copies of
+// the chunks behind it.  Then one pass of exponentials (stored back) and sum, one pass that scales, and one bulk
+// store per chunk; a chunk's part of the buffer is refilled with the next row's chunk as soon as its store has read it.
+constexpr int kRowThreads = 512;
+constexpr int kRowChunks = 8;
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads) softmax_row_smem_kernel(T* __restrict__ out, const T* __restrict__ in, int N,
+                                                                       int M, long long ld_out, long long ld_in, int* status) {
+  using P = typename Pack<T>::type;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full[kRowChunks];
+  __shared__ float red[kRowThreads / 32];
+  const int tid = threadIdx.x;
+  const int npack = N / 4;
+  // chunk boundaries in packs, multiples of 4 packs (16 bytes for f16, 64 for f32)
+  const int per = ((npack + kRowChunks - 1) / kRowChunks + 3) & ~3;
+  if (tid == 0) {
+    for (int c = 0; c < kRowChunks; ++c) mbar_init(&full[c], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  P* buf = reinterpret_cast<P*>(smem);
+  auto block_reduce = [&](float v, bool is_max) {
+    v = is_max ? warp_max(v) : warp_sum(v);
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    float r = red[0];
+    for (int i = 1; i < kRowThreads / 32; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];  // fixed order
+    __syncthreads();
+    return r;
+  };
+  // thread 0 issues the bulk copies of chunk c of `row` (the buffer region of the chunk must be free)
+  auto load_chunk = [&](int row, int c) {
+    const int p0 = c * per, p1 = min(npack, p0 + per);
+    if (p1 <= p0) return;
+    const uint32_t bytes = (uint32_t)(p1 - p0) * 4 * sizeof(T);
+    mbar_expect_tx(&full[c], bytes);
+    bulk_g2s(buf + p0, in + (long long)row * ld_in + (long long)p0 * 4, bytes, &full[c]);
+  };
+  if (tid == 0 && (int)blockIdx.x < M)
+    for (int c = 0; c < kRowChunks; ++c) load_chunk(blockIdx.x, c);
+  bool alive = true;
+  int it = 0;
+  for (int row = blockIdx.x; row < M && alive; row += gridDim.x, ++it) {
+    float mx = -FLT_MAX;
+    for (int c = 0; c < kRowChunks; ++c) {
+      const int p0 = c * per, p1 = min(npack, p0 + per);
+      if (p1 <= p0) break;
+      if (!mbar_wait(&full[c], it & 1, status, DEV_TIMEOUT_TMA)) alive = false;
+      for (int p = p0 + tid; p < p1; p += kRowThreads) {
+        float f[4];
+        Pack<T>::unpack(buf[p], f);
+        mx = fmaxf(mx, fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])));
+      }
+    }
+    alive = __syncthreads_and(alive);
+    if (!alive) break;
+    mx = block_reduce(mx, true);
+    float s4[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int p = tid; p < npack; p += kRowThreads) {
+      float f[4];
+      Pack<T>::unpack(buf[p], f);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        f[k] = exp_sub(f[k], mx);
+        s4[k] += f[k];
+      }
+      if (sizeof(T) == 4) buf[p] = Pack<T>::pack(f);  // f32 rows keep the exponentials; f16 rows recompute them below
+    }
+    const float inv = 1.0f / block_reduce((s4[0] + s4[1]) + (s4[2] + s4[3]), false);
+    // Scale and store chunk by chunk; as soon as the store of a chunk has read its part of the buffer, the same
+    // part takes the next row's chunk, so that the next row streams in under the rest of this one.
+    const int next = row + gridDim.x;
+    for (int c = 0; c < kRowChunks; ++c) {
+      const int p0 = c * per, p1 = min(npack, p0 + per);
+      if (p1 <= p0) break;
+      for (int p = p0 + tid; p < p1; p += kRowThreads) {
+        float f[4];
+        Pack<T>::unpack(buf[p], f);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) f[k] = (sizeof(T) == 4 ? f[k] : exp_sub(f[k], mx)) * inv;
+        buf[p] = Pack<T>::pack(f);
+      }
+      fence_proxy_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        bulk_s2g(out + (long long)row * ld_out + (long long)p0 * 4, buf + p0, (uint32_t)(p1 - p0) * 4 * sizeof(T));
+        bulk_commit();
+        if (next < M) {
+          bulk_wait_read<0>();
+          load_chunk(next, c);
+        }
+      }
+    }
+  }
+  if (tid == 0) bulk_wait<0>();
+}
+
+// ------------------------------------------------------------------ variant 1, any row
 // VEC = elements per load (4 => Pack<T>, 1 => scalar).  CACHE = register-resident
 // packs per thread; rows with more are re-read from global for the final pass.
 template <typename T, int VEC, int CACHE>
@@ -278,6 +380,14 @@ int launch(ctb_ctx* ctx, cudaStream_t st, T* out, const T* in, int N, int M, lon
     if (per_sm < 1) per_sm = 1;
     const int grid = min(M, ctx->sm_count * per_sm);
     k<<<grid, kThreads, smem, st>>>(out, in, N, M, ldo, ldi, stage_bytes, ctx->dev_status);
+  } else if (bulk_ok && row_bytes <= 200 * 1024) {
+    const size_t smem = (row_bytes + 127) & ~size_t(127);
+    auto k = softmax_row_smem_kernel<T>;
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cuda_fail(e, "ctb_softmax: shared memory opt-in");
+    const int per_sm = std::max(1, (int)((size_t)220 * 1024 / (smem + 2048)));
+    const int grid = min(M, ctx->sm_count * std::min(per_sm, 4));
+    k<<<grid, kRowThreads, smem, st>>>(out, in, N, M, ldo, ldi, ctx->dev_status);
   } else {
     int per_sm = 8;
     const int grid = min(M, ctx->sm_count * per_sm);

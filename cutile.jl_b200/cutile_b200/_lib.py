@@ -56,6 +56,7 @@ SIGNATURES = {
     "ctb_softmax": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
     "ctb_vadd": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i],
     "ctb_transpose": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
+    "ctb_fft": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _i, _i],
     "ctb_layernorm_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i],
     "ctb_layernorm_bwd_dx_partial_dwdb": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64,
                                           _i, _i],

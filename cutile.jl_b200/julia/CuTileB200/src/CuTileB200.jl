@@ -238,6 +238,20 @@ function transpose_kernel(x::CuArray{T,2}, y::CuArray{T,2}, tm::Int, tn::Int; op
         context(), launch_opts(; opts...), dptr(x), dptr(y), m, n, stride(x, 2), stride(y, 2), tm, tn, dtype(T)))
 end
 
+# ---- examples/fft.jl ---------------------------------------------------------
+"fft_kernel of examples/fft.jl:22-126; the tables are the caller's (make_twiddles there)."
+function fft_kernel(x_packed_in::CuArray{Float32,3}, y_packed_out::CuArray{Float32,3}, W0::CuArray{Float32,3},
+                    W1::CuArray{Float32,3}, W2::CuArray{Float32,3}, T0::CuArray{Float32,3}, T1::CuArray{Float32,3},
+                    N::Int, F0::Int, F1::Int, F2::Int, BS::Int, D::Int; opts...)
+    size(x_packed_in) == size(y_packed_out) || throw(ArgumentError("fft_kernel: x and y differ in shape"))
+    batch = length(x_packed_in) ÷ 2N
+    check(ccall((:ctb_fft, LIB), Cint,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid},
+         Int64, Cint, Cint, Cint, Int64, Cint, Cint),
+        context(), launch_opts(; opts...), dptr(x_packed_in), dptr(y_packed_out), dptr(W0), dptr(W1), dptr(W2), dptr(T0),
+        dptr(T1), N, F0, F1, F2, batch, BS, D))
+end
+
 # ---- building blocks of the expert-parallel MoE ----
 "dst(:, i) = src(:, cld(ids[i], num_token_replicas)); ids out of range give zero rows."
 function moe_gather_rows(dst::CuArray{Float16,2}, src::CuArray{Float16,2}, ids::CuArray{Int32,1}, num_token_replicas::Int)

@@ -99,6 +99,16 @@ int ctb_vadd(ctb_ctx* ctx, void* stream, const void* a, const void* b, void* c, 
 int ctb_transpose(ctb_ctx* ctx, void* stream, const void* x, void* y, int64_t m, int64_t n, int64_t ldx, int64_t ldy, int tm,
                   int tn, int dtype);
 
+/* ---- FFT -------------------------------------------------------------------- */
+/* fft_kernel(x_packed_in, y_packed_out, W0, W1, W2, T0, T1, N, F0, F1, F2, BS, D)   examples/fft.jl:22-126
+ * Batched complex FFT of length N = F0 * F1 * F2 along the first dimension as three DFT-matrix stages.  x and y are
+ * f32 (D, 2N / D, batch): per batch item N interleaved (re, im) pairs, whatever D.  W0/W1/W2 are the (2, F, F) DFT
+ * matrices and T0 (2, F1 * F2, F0), T1 (2, F2, F1) the twiddle factors of make_twiddles (examples/fft.jl:128-176); the
+ * kernel uses the values it is given.  Factors are powers of two up to 32, N <= 8192; BS (batch items per block of the
+ * reference launch, batch % BS == 0) and D (2N % D == 0) are validated and otherwise advisory.  f32 FMA arithmetic. */
+int ctb_fft(ctb_ctx* ctx, void* stream, const void* x, void* y, const void* W0, const void* W1, const void* W2, const void* T0,
+            const void* T1, int64_t N, int F0, int F1, int F2, int64_t batch, int BS, int D);
+
 /* ---- LayerNorm ---------------------------------------------------------- */
 /* layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N)   examples/layernorm.jl:27-68
  * X, Y (N, M) f32; W, B (N); Mean, Rstd (M). */

@@ -90,3 +90,13 @@ def transpose(m=8192, n=8192, seed=6, dtype=np.float32):
     """x(M, N) ~ U(0,1) (``examples/transpose.jl:25-36``), numpy x[N, M]; benchmark shape 8192 x 8192."""
     g = np.random.default_rng(seed)
     return dict(x=g.random((n, m), dtype=np.float32).astype(dtype), m=m, n=n)
+
+
+def fft(batch=256, factors=(16, 16, 16), seed=7):
+    """input ~ complex standard normal (``examples/fft.jl:182-190``: cuRAND.randn(ComplexF32, N, batch)), numpy
+    complex64 [batch, N]; benchmark shape batch 256, factors (16, 16, 16)."""
+    g = np.random.default_rng(seed)
+    n = int(np.prod(factors))
+    re = g.standard_normal((batch, n), dtype=np.float32)
+    im = g.standard_normal((batch, n), dtype=np.float32)
+    return dict(input=(re + 1j * im).astype(np.complex64) * np.float32(np.sqrt(0.5)), factors=tuple(factors), batch=batch, n=n)

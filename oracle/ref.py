@@ -218,6 +218,73 @@ def transpose(x):
     return np.ascontiguousarray(x.T)
 
 
+def fft_dft_matrix(size, dtype=np.float32):
+    """``dft_matrix`` (``examples/fft.jl:128-138``): W[i, j] = exp(-2 pi i ij / size), rounded to ComplexF32 and split
+    into Float32 planes.  Julia (2, size, size) is numpy [size, size, 2]."""
+    w = np.zeros((size, size), dtype=np.complex64)
+    for i in range(size):
+        for j in range(size):
+            w[i, j] = np.exp(-2j * np.pi * i * j / size)
+    return np.stack([w.real, w.imag], axis=-1).astype(dtype)
+
+
+def fft_make_twiddles(factors, dtype=np.float32):
+    """``make_twiddles`` (``examples/fft.jl:141-176``).  T0 Julia (2, F1F2, F0) is numpy [F0, F1F2, 2] with
+    [i, j] = exp(-2 pi i ij / N); T1 Julia (2, F2, F1) is numpy [F1, F2, 2] with [j, k] = exp(-2 pi i jk / F1F2)."""
+    F0, F1, F2 = factors
+    N, F1F2 = F0 * F1 * F2, F1 * F2
+    T0 = np.zeros((F0, F1F2, 2), dtype=dtype)
+    for i in range(F0):
+        for j in range(F1F2):
+            v = np.exp(-2j * np.pi * i * j / N)
+            T0[i, j, 0], T0[i, j, 1] = v.real, v.imag
+    T1 = np.zeros((F1, F2, 2), dtype=dtype)
+    for j in range(F1):
+        for k in range(F2):
+            v = np.exp(-2j * np.pi * j * k / F1F2)
+            T1[j, k, 0], T1[j, k, 1] = v.real, v.imag
+    return fft_dft_matrix(F0, dtype), fft_dft_matrix(F1, dtype), fft_dft_matrix(F2, dtype), T0, T1
+
+
+def _jl(a, shape):
+    """Julia ``reshape`` (column-major)."""
+    return np.reshape(a, shape, order="F")
+
+
+def fft_three_stage(x, W0, W1, W2, T0, T1, factors, dtype=np.float64):
+    """``fft_kernel`` (``examples/fft.jl:22-126``) stage by stage with Julia's column-major reshapes and permutes:
+    F0-point DFT, twiddle T0, permute, F1-point DFT, twiddle T1, permute, F2-point DFT, final permute.
+    x: complex numpy [batch, N] (Julia (N, batch)); tables as numpy arrays in the layouts of ``fft_make_twiddles``.
+    Returns complex [batch, N]."""
+    F0, F1, F2 = factors
+    N, F1F2, F0F2, F0F1 = F0 * F1 * F2, F1 * F2, F0 * F2, F0 * F1
+    ct = np.complex128 if dtype == np.float64 else np.complex64
+    BS = x.shape[0]
+    cplx = lambda t: (t[..., 0].astype(dtype) + 1j * t[..., 1].astype(dtype)).astype(ct)
+    # numpy [j, i] of a (2, F, F) table is Julia W(i, j)
+    w0, w1, w2 = cplx(W0).T, cplx(W1).T, cplx(W2).T            # now indexed [i, j] like Julia
+    t0 = _jl(cplx(T0).T, (N,))                                   # Julia T0(j, i) flattened column-major
+    t1 = _jl(cplx(T1).T, (F1F2,))                                # Julia T1(k, j) flattened
+    X = x.astype(ct).T                                           # Julia (N, BS)
+    X = _jl(X, (F1F2, F0, BS))
+    X = np.einsum("jnb,nk->jkb", X, w0)                          # X * W0 per batch (:80-83)
+    X = _jl(X, (N, BS)) * t0[:, None]                            # (:86-87)
+    X = np.transpose(_jl(X, (F2, F1, F0, BS)), (2, 0, 1, 3))     # permutedims (3, 1, 2, 4) (:90-91)
+    X = _jl(X, (F0F2, F1, BS))
+    X = np.einsum("rnb,nk->rkb", X, w1)                          # (:95-98)
+    X = _jl(X, (F0, F1F2, BS)) * t1[None, :, None]               # (:101-102)
+    X = np.transpose(_jl(X, (F0, F2, F1, BS)), (2, 0, 1, 3))     # (:105-106)
+    X = _jl(X, (F0F1, F2, BS))
+    X = np.einsum("qnb,nk->qkb", X, w2)                          # (:110-113)
+    X = np.transpose(_jl(X, (F1, F0, F2, BS)), (1, 0, 2, 3))     # permutedims (2, 1, 3, 4) (:116-117)
+    return np.ascontiguousarray(_jl(X, (N, BS)).T)
+
+
+def fft(x):
+    """The example's check (``examples/fft.jl:243-247``): ``FFTW.fft(input, 1)``, the DFT along the N dimension."""
+    return np.fft.fft(np.asarray(x, dtype=np.complex128), axis=-1)
+
+
 def rel_fro(out, ref):
     """||out-ref||_F / ||ref||_F, the norm-wise measure Julia's ``isapprox`` uses
     on arrays (``examples/matmul.jl:100``)."""

@@ -4,6 +4,7 @@ import json
 import os
 
 import numpy as np
+import pytest
 
 from oracle import inputs, ref
 
@@ -119,3 +120,25 @@ def test_vadd_and_transpose_restatements():
     t = inputs.transpose(5, 3)
     y = ref.transpose(t["x"])
     assert y.shape == (5, 3) and y[4, 2] == t["x"][2, 4] and y.flags.c_contiguous
+
+
+@pytest.mark.parametrize("batch,factors", [(2, (2, 2, 2)), (4, (8, 8, 8)), (3, (4, 8, 16)), (2, (16, 16, 16)), (2, (1, 4, 2)),
+                                           (2, (32, 2, 8))])
+def test_fft_three_stage_restatement_is_the_dft(batch, factors):
+    """The stage-by-stage restatement of the example's kernel, fed the example's own f32 tables, reproduces the DFT that
+    the example verifies against (FFTW there, numpy's pocketfft here) and closed-form answers."""
+    d = inputs.fft(batch, factors)
+    tabs = ref.fft_make_twiddles(factors)
+    y = ref.fft_three_stage(d["input"], *tabs, factors)
+    want = ref.fft(d["input"])
+    assert ref.rel_fro(np.stack([y.real, y.imag]), np.stack([want.real, want.imag])) <= 2e-7
+    n = d["n"]
+    imp = np.zeros((1, n), dtype=np.complex64)
+    imp[0, n // 2 + (n > 1)] = 1
+    p = n // 2 + (n > 1)
+    yi = ref.fft_three_stage(imp, *tabs, factors)[0]
+    assert np.abs(yi - np.exp(-2j * np.pi * p * np.arange(n) / n)).max() <= 1e-6
+    # tables: symmetric DFT matrices with unit-modulus entries, first row/column of every table equal to 1
+    for t in tabs:
+        assert np.allclose(np.hypot(t[..., 0], t[..., 1]), 1.0, atol=1e-6)
+        assert np.array_equal(t[0, :, 0], np.ones(t.shape[1], np.float32)) and not t[0, :, 1].any()
