@@ -283,7 +283,7 @@ class Gemm(Workload):
     bound = "tensor"
     peak_scale = 0.5  # TF32 MMAs run at half the bf16 rate the measured peak was taken at
     dtype = "tf32"
-    kernel = "gemm_kernel<float>"
+    kernel = "gemm_pair_kernel<float>"
     uses_blas = True
     M = N = K = 4096
 
@@ -395,16 +395,16 @@ class Fmha(Workload):
 
 
 class SoftmaxOnline(Softmax):
-    """Rows too long for one tile: the chunked kernel with a running (max, sum) per thread."""
+    """Rows too long for one tile of registers (128 KB each): the chunked variant keeps the whole row in shared memory."""
     M, N = 1024, 32768
 
     def __init__(self):
         Softmax.__init__(self, 1)
         self.name = "softmax_online"
-        self.kernel = "softmax_online_kernel"
+        self.kernel = "softmax_row_smem_kernel"
 
     def describe(self):
-        return f"row softmax f32 {self.M}x{self.N} N(0,4) seed 1, chunked online (rows longer than one tile)"
+        return f"row softmax f32 {self.M}x{self.N} N(0,4) seed 1, chunked variant, row resident in shared memory (rows longer than one register tile)"
 
     def step(self, ctb, st):
         ctb.softmax.softmax_chunked_kernel(st["out"], st["x"], self.N, 1024)
@@ -498,6 +498,47 @@ class Transpose(Workload):
         return float(np.max(np.abs(st["y"].cpu().numpy() - ref.transpose(host["x"]))))  # exact: 0
 
 
+class Fft(Workload):
+    name = "fft"
+    metric = "fft_gbps"
+    unit = "GB/s"
+    kernel = "fft_kernel"
+    batch, factors = 256, (16, 16, 16)
+
+    def describe(self):
+        return ("batched complex FFT, 256 x 4096 points as (16, 16, 16) DFT-matrix stages, c64 ~ N(0,1) seed 7 "
+                "(examples/fft.jl benchmark shape; the example reports the time, ms_per_step here)")
+
+    def work(self):
+        return 2 * self.batch * 4096 * 8
+
+    def host_inputs(self):
+        from oracle import inputs
+        return inputs.fft(self.batch, self.factors, seed=7)
+
+    def to_device(self, host, torch):
+        import cutile_b200 as ctb
+        x = torch.from_numpy(host["input"]).cuda()
+        return dict(x=x, y=torch.empty_like(x), plan=ctb.fft.FftPlan(self.factors, "cuda"))
+
+    def step(self, ctb, st):
+        st["plan"](st["x"], st["y"])
+
+    def e2e_io(self, st):
+        return [("x",)], [("y",)]
+
+    def cpu_step(self, host, ref, np):
+        x = host["input"][:64]
+        tabs = ref.fft_make_twiddles(self.factors)
+        return (lambda: ref.fft_three_stage(x, *tabs, self.factors, dtype=np.float32)), 64 / self.batch, \
+            "64 of 256 batch items, numpy complex64 three-stage restatement"
+
+    def check(self, host, st, ref, np):
+        y = st["y"].cpu().numpy()
+        want = ref.fft(host["input"])
+        return ref.rel_fro(np.stack([y.real, y.imag]), np.stack([want.real, want.imag]))
+
+
 class Moe(Workload):
     name = "moe_256"
     metric = "moe_ffn_tflops"
@@ -563,7 +604,7 @@ class Moe4096(Moe):
 
 def registry():
     w = [Fmha(), FmhaB64(), Moe(), Moe4096(), Gemm(), BatchedGemm(), LayerNormFwd(), LayerNormBwd(), Softmax(0), Softmax(1),
-         SoftmaxOnline(), VecAdd(), Transpose()]
+         SoftmaxOnline(), VecAdd(), Transpose(), Fft()]
     return {x.name: x for x in w}
 
 
@@ -975,6 +1016,7 @@ def main():
                     traffic=profile_traffic(w.name), kernel=w.kernel, peak_source=pk["source"])
 
     kernels = {}
+    kernel_mhz = []  # median SM clock inside each workload's timed region
     if world == 1:
         names = [n for n in reg if n != headline]
         if a.only is not None:
@@ -984,15 +1026,18 @@ def main():
             r = run_workload(w, torch, ctb, None, a.steps, a.warmup, rank, 1, True, not a.no_cpu, 0.1)
             ck = sampler.summary(r["t0"], r["t1"])
             rf = roof(r, w)
-            # v value [GB/s for hbm-bound, TFLOP/s for tensor-bound], ms mean per step, min best replay, frac of the binding
-            # roofline (b), traf DRAM bytes per step from the ncu summary, e2e ms per step from pinned host memory,
-            # p1/pc min ms of the reference's protocol (kernel only / allocating wrapper), cpu baseline in the value's unit,
-            # err parity figure, mhz median SM clock inside the timed region
-            e = dict(v=r4(w.work() / (r["ms_per_step"] * 1e-3) / scale(w.unit)), ms=r4(r["ms_per_step"]), min=r4(r["min_ms"]),
-                     frac=rf["frac"], b=rf["bound"][0], traf=None if rf["traffic"] is None else int(rf["traffic"]),
-                     e2e=r4(r["e2e"]["ms_per_step"]), p1=r4(r["protocol"]["min_ms"]), pc=r4(r["protocol"].get("call_min_ms")),
-                     cpu=r4((r.get("cpu_baseline") or {}).get("value")), err=r4(r["parity_err"]), mhz=ck.get("sm_mhz"))
-            kernels[n] = {k: v for k, v in e.items() if v is not None}
+            # one row per workload, columns named in kernels["cols"]: v value [GB/s for hbm-bound, TFLOP/s for
+            # tensor-bound], ms mean per step, frac of the binding roofline b (h = HBM, t = tensor), traf DRAM MB per step
+            # from the ncu summary, e2e ms per step from pinned host memory, p1 min ms of the reference's protocol
+            # (5 warm-up, 20 single calls), cpu baseline in the value's unit, err parity figure
+            traf = None if rf["traffic"] is None else round(rf["traffic"] / 1e6, 1)
+            kernels[n] = [r4(w.work() / (r["ms_per_step"] * 1e-3) / scale(w.unit)), r4(r["ms_per_step"]), rf["frac"],
+                          rf["bound"][0], traf, r4(r["e2e"]["ms_per_step"]), r4(r["protocol"]["min_ms"]),
+                          r4((r.get("cpu_baseline") or {}).get("value")), r4(r["parity_err"])]
+            if ck.get("sm_mhz"):
+                kernel_mhz.append(ck["sm_mhz"])
+        if kernels:
+            kernels = dict(cols="v ms frac b traf_MB e2e_ms p1_ms cpu err", **kernels)
     else:
         # batched GEMM sharded by batch (strong scaling, no collective)
         bw = reg["bgemm_tf32"]
@@ -1022,9 +1067,9 @@ def main():
         if e2e:
             e2e = dict(value=r4(head["work_total"] / (e2e["ms_per_step"] * 1e-3) / scale(hw.unit)), unit=hw.unit,
                        ms_per_step=r4(e2e["ms_per_step"]), h2d_bytes_per_step=e2e["h2d_bytes_per_step"],
-                       d2h_bytes_per_step=e2e["d2h_bytes_per_step"], how="pinned host buffers; H2D, kernels, D2H on 3 streams")
+                       d2h_bytes_per_step=e2e["d2h_bytes_per_step"], how="pinned host; H2D | kernels | D2H on 3 streams")
         cfg = {"workload": hw.describe(), "l2": head["l2"], "replays": head["replays"],
-               "timing": "K steps per CUDA graph, R replays each between two CUDA events, mean over replays, max over ranks",
+               "timing": "K-step CUDA graph, R replays each between CUDA events, mean, max over ranks",
                "per_gpu": (f"batch {hw.B // world} of 64 per rank, sharded by batch, no collective" if sharded
                            else "the whole workload on one GPU")}
         line = dict(metric=hw.metric, value=r4(value), unit=hw.unit, n_gpus=world, steps=a.steps, warmup=a.warmup,
@@ -1034,9 +1079,11 @@ def main():
                     roofline=roof(head, hw, work=head["work_per_step"]), cpu_baseline=head.get("cpu_baseline"),
                     parity_err=r4(head["parity_err"]),
                     protocol=dict({k: r4(v) for k, v in head["protocol"].items()},
-                                  how="benchmarks.jl: 5 warm-up, 20 single calls, min/mean ms; call_* = allocating wrapper"))
+                                  how="5 warm-up, 20 single calls; call_* = allocating wrapper"))
         if comp:  # library kernels on the same box, for orientation (cuBLAS TF32 is the TF32 peak of the GEMM rows)
             line["comparators"] = {k: r4(v) for k, v in comp.items()}
+        if kernel_mhz:
+            line["clocks"]["kernels_sm_mhz_min"] = min(kernel_mhz)
         if kernels:
             line["kernels"] = kernels
         emit(line)

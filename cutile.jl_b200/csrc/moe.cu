@@ -464,12 +464,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   // full[s]: one arrival with the TMA byte count from the weight producer + one arrival per gather thread
   __shared__ __align__(8) uint64_t full[kMaxStages], empty[kMaxStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_base_s;
-  __shared__ int abort_s;
+  __shared__ int abort_s, tok_rows_s;
   __shared__ int meta_e[kMetaItems], meta_ext[kMetaItems];  // expert (0-based, -1 = skip) and slot extent per item
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     abort_s = 0;
-    for (int s = 0; s < p.stages; ++s) {
+    tok_rows_s = 16;
+    for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&full[s], 1 + kGatherThreads);  // gather threads arrive when their cp.async copies have landed
       mbar_init(&empty[s], 1);
     }
@@ -520,6 +521,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     nt = pair - bm * p.n_tiles;
   };
 
+  // Ring geometry of this CTA.  A stage holds the weight tile(s) and as many token rows as the fullest block among
+  // this CTA's items needs (a multiple of 16): with few tokens per expert the stages shrink and more of them, i.e.
+  // more weight bytes in flight, fit the same shared memory.  The MMA still reads 128 token rows; the rows past the
+  // stage's token part are whatever follows in shared memory (the next stage or the output staging, always inside
+  // the allocation) and only feed accumulator rows that nobody reads.
+  for (int n = warp; n < my_items; n += kGemmThreads / 32) {
+    int bm, nt_, w0_, nw_;
+    decode(blockIdx.x + n * gridDim.x, bm, nt_, w0_, nw_);
+    const int e = p.expert_ids[bm] - 1;
+    const int ext = (e < 0 || e >= p.E) ? 0 : block_extent(p.sorted_ids + (long long)bm * p.tile_m, p.tile_m, p.total, lane);
+    if (lane == 0 && ext > 0) atomicMax(&tok_rows_s, min(kMaxTileM, (ext + 15) & ~15));
+  }
+  __syncthreads();
+  const int ring_bytes = p.stages * p.stage_bytes;  // the host's budget, sized for full 128-row token tiles
+  const int stage_bytes = wbytes + tok_rows_s * 128;
+  const int stages = min(kMaxStages, ring_bytes / stage_bytes);
+
   // pipeline state of each role persists across rounds
   int stage = 0, nacc = 0;
   uint32_t phase = 0;
@@ -551,7 +569,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int kb = 0; kb < nk; ++kb) {
           ok = CTB_WARP_WAIT(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
           if (!ok) break;
-          unsigned char* dst = smem + (size_t)stage * p.stage_bytes;
+          unsigned char* dst = smem + (size_t)stage * stage_bytes;
           if (elect_one()) {
             mbar_expect_tx(&full[stage], nw * kWTile);
             if (EPI == EPI_SWIGLU) {
@@ -564,7 +582,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             }
           }
           __syncwarp();
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          if (++stage == stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
       }
@@ -589,7 +607,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (!ok) break;
           fence_proxy_async_smem();  // the gathered rows were written through the generic proxy
           tc_fence_after();
-          const uint32_t sw = smem_u32(smem + (size_t)stage * p.stage_bytes);
+          const uint32_t sw = smem_u32(smem + (size_t)stage * stage_bytes);
           const uint32_t st = sw + wbytes;
           if (elect_one()) {
 #pragma unroll
@@ -599,7 +617,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             tc_commit(&empty[stage]);
           }
           __syncwarp();
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          if (++stage == stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         if (elect_one()) tc_commit(&acc_full[acc]);
@@ -662,7 +680,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         for (int kb = 0; kb < nk; ++kb) {
           ok = CTB_WARP_WAIT1(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
           if (!ok) break;
-          const uint32_t base = smem_u32(smem + (size_t)stage * p.stage_bytes + wbytes) + chunk_off;
+          const uint32_t base = smem_u32(smem + (size_t)stage * stage_bytes + wbytes) + chunk_off;
           const bool in_k = kb * kBK + cch * 8 < p.K;  // K is a multiple of 8: a chunk is inside or outside as a whole
 #pragma unroll
           for (int q = 0; q < kQ; ++q) {
@@ -672,7 +690,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             }
           }
           cp_async_arrive_noinc(&full[stage]);  // fires when this thread's copies have landed
-          if (++stage == p.stages) { stage = 0; phase ^= 1; }
+          if (++stage == stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         n = n_next;
@@ -687,7 +705,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       constexpr int kOutCols = EPI == EPI_SWIGLU ? kRows : NW * kRows;  // output rows per item
       constexpr int kMyCols = kOutCols / 2;                            // ... of which this warp writes half
       // this thread's row of its warp's staging tile (rows 16 bytes apart from a multiple of 128: no bank conflicts)
-      unsigned char* stg = smem + (size_t)p.stages * p.stage_bytes +
+      unsigned char* stg = smem + (size_t)ring_bytes +
                            ((size_t)(warp - (2 + kGatherWarps)) * 32 + lane) * kStagePitch;
       for (int n = 0; n < rn; ++n) {
         if (meta_e[n] < 0) continue;

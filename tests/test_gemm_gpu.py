@@ -25,7 +25,9 @@ def dense(cuda, d, tiles=(64, 64, 64)):
 @pytest.mark.parametrize("M,N,K,tiles", [(256, 256, 256, (32, 32, 32)), (512, 512, 512, (64, 64, 64)),
                                          (256, 512, 128, (32, 32, 32)), (1024, 1024, 1024, (64, 64, 64)),
                                          (200, 300, 100, (64, 64, 64)), (4, 4, 4, (64, 64, 64)),
-                                         (132, 260, 36, (64, 64, 64)), (4096, 4096, 4096, (64, 64, 64))])
+                                         (132, 260, 36, (64, 64, 64)), (4096, 4096, 4096, (64, 64, 64)),
+                                         (2048, 2048, 256, (64, 64, 64)), (2304, 2600, 100, (64, 64, 64)),
+                                         (3000, 1800, 72, (64, 64, 64)), (260, 9000, 40, (64, 64, 64))])
 def test_gemm_tf32(cuda, M, N, K, tiles):
     d = inputs.gemm(M, N, K, seed=2)
     C = dense(cuda, d, tiles)
@@ -50,7 +52,8 @@ def batched(cuda, d, tiles=(128, 128, 64)):
     (256, 128, 256, 4, np.float32, (32, 32, 32)), (512, 256, 512, 4, np.float32, (64, 64, 64)),
     (512, 256, 1024, 4, np.float16, (128, 256, 64)), (1024, 2048, 512, 8, np.float32, (128, 128, 64)),
     (1024, 512, 2048, 8, np.float32, (128, 128, 64)), (100, 72, 36, 3, np.float32, (128, 128, 64)),
-    (136, 40, 264, 2, np.float16, (128, 128, 64))])
+    (136, 40, 264, 2, np.float16, (128, 128, 64)),
+    (1000, 72, 1300, 5, np.float32, (128, 128, 64)), (1032, 136, 1544, 4, np.float16, (128, 128, 64))])
 def test_batched_gemm(cuda, M, K, N, batch, dtype, tiles):
     d = inputs.batched_gemm(M, K, N, batch, seed=2, dtype=dtype)
     C = batched(cuda, d, tiles)

@@ -16,7 +16,14 @@ dist.init_process_group("gloo")
 rank, world = dist.get_rank(), dist.get_world_size()
 ms = bench.max_over_ranks(10.0 + 5.0 * rank, torch, dist, "cpu")   # rank 1 is the slow one
 val = bench.aggregate_value(1e12, world, ms, "TFLOP/s")            # 1 TFLOP per rank per step
-os.write(1, (json.dumps({"rank": rank, "ms": ms, "value": val}) + "\n").encode())  # one write: ranks share the pipe
+# batch shards of the multi-GPU FMHA (64) and batched GEMM (8) problems, and a ragged count: gathered over the ranks
+shards = {}
+for total in (64, 8, 7):
+    mine = torch.tensor(list(bench.shard_range(total, world, rank)))
+    got = [torch.zeros(2, dtype=mine.dtype) for _ in range(world)]
+    dist.all_gather(got, mine)
+    shards[str(total)] = [g.tolist() for g in got]
+os.write(1, (json.dumps({"rank": rank, "ms": ms, "value": val, "shards": shards}) + "\n").encode())  # one write: ranks share the pipe
 dist.destroy_process_group()
 """ % ROOT
 
@@ -53,6 +60,8 @@ def test_time_is_max_over_ranks_and_value_aggregates(tmp_path):
     for x in rows:
         assert x["ms"] == 15.0                      # the slowest rank's time on every rank
         assert abs(x["value"] - 2 / 15e-3) < 1e-9   # 2 TFLOP of work in 15 ms
+        # the ranks' shards tile [0, total) without gaps or overlap, sizes differ by at most one
+        assert x["shards"] == {"64": [[0, 32], [32, 64]], "8": [[0, 4], [4, 8]], "7": [[0, 4], [4, 7]]}
 
 
 def test_reference_arm_prints_once_under_torchrun():
