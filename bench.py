@@ -1076,7 +1076,7 @@ def main():
                     ms_per_step=r4(per), min_ms_per_step=r4(head["min_ms"]), higher_is_better=True,
                     scaling="strong" if sharded else "weak", vs_baseline=None, dtype=hw.dtype, data="synthetic", config=cfg,
                     clocks=clocks, e2e=e2e, gpu_launches=head["launches"],
-                    roofline=roof(head, hw, work=head["work_per_step"]), cpu_baseline=head.get("cpu_baseline"),
+                    roofline=roof(head, hw, work=head["work_per_step"] if sharded else None), cpu_baseline=head.get("cpu_baseline"),
                     parity_err=r4(head["parity_err"]),
                     protocol=dict({k: r4(v) for k, v in head["protocol"].items()},
                                   how="5 warm-up, 20 single calls; call_* = allocating wrapper"))

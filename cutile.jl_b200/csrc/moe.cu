@@ -238,9 +238,20 @@ template <typename IdT>
 __global__ void __launch_bounds__(kAlignThreads)
     moe_align_kernel(const IdT* __restrict__ topk_ids, int T, int topk, int E, int tile_m,
                      int* __restrict__ sorted_token_ids, int* __restrict__ sorted_expert_ids,
-                     int* __restrict__ num_blocks, int capacity_blocks, int skip_empty, int* status) {
+                     int* __restrict__ num_blocks, int capacity_blocks, int skip_empty, int* status,
+                     const unsigned char* __restrict__ warm, long long warm_bytes) {
   cg::cluster_group cluster = cg::this_cluster();
   const int C = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+  if ((int)blockIdx.x >= C) {
+    // The clusters after the first do not sort: they ask the L2 to fetch the head of the expert weights that the next
+    // kernel streams (HBM is idle while the ids are sorted), one 128-byte line per request, and leave.
+    const long long nlines = warm_bytes >> 7;
+    const long long first = (long long)((int)blockIdx.x - C) * kAlignThreads + threadIdx.x;
+    const long long step = (long long)((int)gridDim.x - C) * kAlignThreads;
+    for (long long c = first; c < nlines; c += step)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(warm + (c << 7)) : "memory");
+    return;
+  }
   extern __shared__ int sm[];
   int* wcount = sm;                       // [kAlignWarps][E]: per-warp counts, then running offsets
   int* estart = sm + kAlignWarps * E;     // [E]: first padded position of expert e
@@ -452,6 +463,7 @@ constexpr int kPassCols = 32;                      // output columns an epilogue
 constexpr int kStagePitch = kPassCols * 2 + 16;    // bytes between staging rows
 constexpr int kEpiStageBytes = kEpiWarps * 32 * kStagePitch;
 constexpr int kMetaItems = 64;  // work items whose block metadata a CTA caches per round
+constexpr int kIssue = 1;      // k-blocks the weight producer requests at a time (2 measured no faster)
 
 // EPI: epilogue.  NW: 128-row weight tiles per work item (2 for SwiGLU = gate tile + up tile; 2 for the plain
 // epilogues when the expert has at least 256 output rows, so that a gathered token tile is used by 256 rows).
@@ -566,23 +578,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         int bm_, nt, w0, nw;
         decode(blockIdx.x + (r0 + n) * gridDim.x, bm_, nt, w0, nw);
         bool ok = true;
-        for (int kb = 0; kb < nk; ++kb) {
-          ok = CTB_WARP_WAIT(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+        // kIssue k-blocks are requested at a time (with 2, the two 128-byte pieces of a weight row reach the memory
+        // controller together)
+        for (int kb = 0; kb < nk; kb += kIssue) {
+          const int nb = min(kIssue, nk - kb);
+          int s2 = stage;
+          uint32_t ph2 = phase;
+          for (int b = 0; b < nb && ok; ++b) {
+            ok = CTB_WARP_WAIT(&empty[s2], ph2 ^ 1, status, DEV_TIMEOUT_SLOT, abort);
+            if (++s2 == stages) { s2 = 0; ph2 ^= 1; }
+          }
           if (!ok) break;
-          unsigned char* dst = smem + (size_t)stage * stage_bytes;
           if (elect_one()) {
-            mbar_expect_tx(&full[stage], nw * kWTile);
-            if (EPI == EPI_SWIGLU) {
-              tma_load_3d(dst, &tmW, kb * kBK, nt * kRows, e, &full[stage]);
-              tma_load_3d(dst + kWTile, &tmW, kb * kBK, p.N + nt * kRows, e, &full[stage]);
-            } else {
+            int s3 = stage;
+            for (int b = 0; b < nb; ++b) {
+              unsigned char* dst = smem + (size_t)s3 * stage_bytes;
+              mbar_expect_tx(&full[s3], nw * kWTile);
+              if (EPI == EPI_SWIGLU) {
+                tma_load_3d(dst, &tmW, (kb + b) * kBK, nt * kRows, e, &full[s3]);
+                tma_load_3d(dst + kWTile, &tmW, (kb + b) * kBK, p.N + nt * kRows, e, &full[s3]);
+              } else {
 #pragma unroll
-              for (int w = 0; w < NW; ++w)
-                if (w < nw) tma_load_3d(dst + w * kWTile, &tmW, kb * kBK, nt * kRowsItem + (w0 + w) * kRows, e, &full[stage]);
+                for (int w = 0; w < NW; ++w)
+                  if (w < nw)
+                    tma_load_3d(dst + w * kWTile, &tmW, (kb + b) * kBK, nt * kRowsItem + (w0 + w) * kRows, e, &full[s3]);
+              }
+              if (++s3 == stages) s3 = 0;
             }
           }
           __syncwarp();
-          if (++stage == stages) { stage = 0; phase ^= 1; }
+          stage = s2;
+          phase = ph2;
         }
         if (!ok) break;
       }
@@ -978,13 +1004,30 @@ int launch_gemm(ctb_ctx* ctx, cudaStream_t st, int epi, const __half* A, long lo
   return CTB_OK;
 }
 
+// Bytes of the gate/up weights worth fetching into the L2 ahead of the expert GEMM: with few slots that GEMM streams
+// the weights once and is bound by HBM, which sits idle during the sort; the blocks are ordered by expert, so the GEMM
+// starts at the head of the tensor.  48 MB is what a sort of that size gives the memory time to deliver and a safe
+// share of the L2.  With many slots the GEMM is bound by the tensor cores and nothing is fetched.
+long long warm_bytes(long long slots, long long weight_bytes) {
+  return slots <= 2048 ? std::min<long long>(weight_bytes, 48ll << 20) : 0;
+}
+
+// `warm`, `warm_bytes`: memory (16-byte aligned) that extra CTAs of the launch ask the L2 to fetch while the ids are
+// sorted; null for none.
 int launch_align(ctb_ctx* ctx, cudaStream_t st, const void* topk_ids, int ids_bits, int T, int topk, int E, int tile_m,
-                 int* sorted_token_ids, int* sorted_expert_ids, int* num_blocks, int capacity, int skip_empty = 0) {
+                 int* sorted_token_ids, int* sorted_expert_ids, int* num_blocks, int capacity, int skip_empty = 0,
+                 const void* warm = nullptr, long long warm_bytes = 0) {
   const size_t smem = (size_t)(kAlignWarps * E + 5 * E + 1) * sizeof(int);
   const long long total = (long long)T * topk;
   const int C = total >= 4096 ? 8 : total >= 2048 ? 4 : 1;  // CTAs in the cluster: about 1024 ids each at least
+  if (!warm || warm_bytes <= 0 || (uintptr_t)warm % 16) {
+    warm = nullptr;
+    warm_bytes = 0;
+  }
+  const int extra = warm ? std::max(1, (ctx->sm_count - C) / C) : 0;  // whole clusters that only warm the L2
+  const unsigned char* warm_p = static_cast<const unsigned char*>(warm);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(C);
+  cfg.gridDim = dim3(C * (1 + extra));
   cfg.blockDim = dim3(kAlignThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
@@ -999,10 +1042,11 @@ int launch_align(ctb_ctx* ctx, cudaStream_t st, const void* topk_ids, int ids_bi
   cudaError_t e;
   if (ids_bits == 32)
     e = cudaLaunchKernelEx(&cfg, moe_align_kernel<int>, (const int*)topk_ids, T, topk, E, tile_m, sorted_token_ids,
-                           sorted_expert_ids, num_blocks, capacity, skip_empty, ctx->dev_status);
+                           sorted_expert_ids, num_blocks, capacity, skip_empty, ctx->dev_status, warm_p, warm_bytes);
   else
     e = cudaLaunchKernelEx(&cfg, moe_align_kernel<long long>, (const long long*)topk_ids, T, topk, E, tile_m,
-                           sorted_token_ids, sorted_expert_ids, num_blocks, capacity, skip_empty, ctx->dev_status);
+                           sorted_token_ids, sorted_expert_ids, num_blocks, capacity, skip_empty, ctx->dev_status, warm_p,
+                           warm_bytes);
   if (e != cudaSuccess) return cuda_fail(e, "moe align launch");
   return CTB_OK;
 }
@@ -1052,7 +1096,8 @@ int moe_experts_rows(ctb_ctx* ctx, cudaStream_t st, const void* rows, int64_t ld
   __half* act = (__half*)(w + o_act);
   // with rows from `world` ranks in the buffer (c_split rows each), about one rank's worth is for this rank's experts
   const int expect_blocks = c_split > 0 ? (int)(c_split / tile_m + E_local) : blocks_cap;
-  r = launch_align(ctx, st, ids, 32, (int)R, 1, (int)E_local, tile_m, s_tok, s_exp, s_nb, blocks_cap, /*skip_empty=*/1);
+  r = launch_align(ctx, st, ids, 32, (int)R, 1, (int)E_local, tile_m, s_tok, s_exp, s_nb, blocks_cap, /*skip_empty=*/1,
+                   w1_local, warm_bytes(R, 2 * I * H * E_local * 2));
   if (r) return r;
   r = launch_gemm(ctx, st, EPI_SWIGLU, (const __half*)rows, ld_rows, (int)R, (const __half*)w1_local, (int)H,
                   (int)(2 * I), (int)I, (int)E_local, nullptr, s_tok, s_exp, s_nb, -1, blocks_cap, 1, 0, tile_m, (int)R,
@@ -1200,7 +1245,8 @@ int ctb_moe_ffn(ctb_ctx* ctx, void* stream, const void* hidden, const void* w1, 
   int* s_nb = (int*)(w + o_nb);
   __half* act = (__half*)(w + o_act);
   __half* slots = (__half*)(w + o_slots);
-  r = launch_align(ctx, st, topk_ids, ids_bits, (int)T, (int)topk, (int)E, tile_m, s_tok, s_exp, s_nb, cap);
+  r = launch_align(ctx, st, topk_ids, ids_bits, (int)T, (int)topk, (int)E, tile_m, s_tok, s_exp, s_nb, cap, 0, w1,
+                   warm_bytes(T * topk, 2 * I * H * E * 2));
   if (r) return r;
   // gate/up projection with the SwiGLU epilogue: act(:, id) = silu(Wg x) * (Wu x)
   r = launch_gemm(ctx, st, EPI_SWIGLU, (const __half*)hidden, H, (int)T, (const __half*)w1, (int)H, (int)(2 * I),
