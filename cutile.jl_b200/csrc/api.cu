@@ -134,6 +134,7 @@ int ctb_create(ctb_ctx** out, int device) {
   c->workspace_bytes = 0;
   c->sched_pool = nullptr;
   c->sched_next = 0;
+  c->flag_wait_ns = 2000000000ull;
   c->comm = nullptr;
   e = cudaMalloc(&c->dev_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(c->dev_status, 0, sizeof(int));
@@ -199,6 +200,14 @@ int ctb_validate_hints(int num_ctas, int occupancy, int opt_level, int num_worke
     return fail(CTB_BAD_ARG, "opt_level must be between 0 and 3, got %d", opt_level);
   if (num_worker_warps != CTB_HINT_UNSET && num_worker_warps != 4 && num_worker_warps != 8)
     return fail(CTB_BAD_ARG, "num_worker_warps must be either 4 or 8, got %d", num_worker_warps);
+  return CTB_OK;
+}
+
+int ctb_set_flag_wait_limit(ctb_ctx* ctx, uint64_t nanoseconds) {
+  CTB_CHECK_CTX(ctx);
+  if (nanoseconds < 1000ull || nanoseconds > 10000000000ull)
+    return fail(CTB_BAD_ARG, "ctb_set_flag_wait_limit: the limit must lie between 1 microsecond and 10 seconds");
+  ctx->flag_wait_ns = nanoseconds;
   return CTB_OK;
 }
 

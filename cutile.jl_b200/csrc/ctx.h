@@ -22,6 +22,7 @@ struct ctb_ctx {
   int* sched_pool;
   unsigned sched_next;
   void* comm;             // ctb_internal::Comm* once an NCCL communicator is attached (multi.cu)
+  unsigned long long flag_wait_ns;  // how long a kernel waits for another rank's flag before it gives up
 };
 
 namespace ctb_internal {

@@ -63,6 +63,11 @@ struct Params {
   int M, N, K, batch;
   long long ldc, strideC;
   int tiles_m, tiles_n, num_tiles;
+  // Split-K (single-CTA kernel, few tiles): a work unit is (tile, split); split s takes the k-blocks
+  // [s * nk / splits, (s + 1) * nk / splits) and leaves its f32 accumulator tile in partial[unit] (column by column,
+  // 128 rows each); gemm_splitk_reduce_kernel adds the splits in ascending order.
+  int splits;
+  float* partial;
 };
 
 __device__ __forceinline__ void tile_coords(const Params& p, int t, int& b, int& tm, int& tn) {
@@ -113,16 +118,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t tmem_base = tmem_base_s;
   volatile int* abort = &abort_s;
   const int nk = (p.K + G::BK - 1) / G::BK;
+  const int units = p.num_tiles * p.splits;
 
   if (warp == 0) {
     // ---- TMA producer: the whole warp walks the loop, one elected lane issues
     int stage = 0;
     uint32_t phase = 0;
-    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
       int b, tm, tn;
-      tile_coords(p, t, b, tm, tn);
+      tile_coords(p, u / p.splits, b, tm, tn);
+      const int sp = u % p.splits, kb_lo = sp * nk / p.splits, kb_hi = (sp + 1) * nk / p.splits;
       bool ok = true;
-      for (int kb = 0; kb < nk; ++kb) {
+      for (int kb = kb_lo; kb < kb_hi; ++kb) {
         ok = CTB_WARP_WAIT(&empty[stage], phase ^ 1, status, DEV_TIMEOUT_SLOT, abort);
         if (!ok) break;
         unsigned char* sa = smem + (size_t)stage * G::STAGE_BYTES;
@@ -147,14 +154,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     int stage = 0;
     uint32_t phase = 0;
     int it = 0;
-    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++it) {
+    for (int u = blockIdx.x; u < units; u += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!CTB_WARP_WAIT(&acc_empty[acc], acc_phase ^ 1, status, DEV_TIMEOUT_SLOT, abort)) break;
       tc_fence_after();
       const uint32_t d = tmem_base + acc * kAccCols;
+      const int sp = u % p.splits, kb_lo = sp * nk / p.splits, kb_hi = (sp + 1) * nk / p.splits;
       bool ok = true;
-      for (int kb = 0; kb < nk; ++kb) {
+      for (int kb = kb_lo; kb < kb_hi; ++kb) {
         ok = CTB_WARP_WAIT(&full[stage], phase, status, DEV_TIMEOUT_TMA, abort);
         if (!ok) break;
         tc_fence_after();
@@ -166,9 +174,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint64_t ad = make_sdesc(sa + k * G::UK * 128, G::A_BOX_BYTES, G::A_SBO, G::A_LAYOUT);
             const uint64_t bd = make_sdesc_sw128(sb + k * 32, 0, 1024);
             if constexpr (sizeof(T) == 4)
-              mma_tf32_ss(d, ad, bd, idesc, (kb | k) != 0);
+              mma_tf32_ss(d, ad, bd, idesc, ((kb - kb_lo) | k) != 0);
             else
-              mma_f16_ss(d, ad, bd, idesc, (kb | k) != 0);
+              mma_f16_ss(d, ad, bd, idesc, ((kb - kb_lo) | k) != 0);
           }
           tc_commit(&empty[stage]);
         }
@@ -185,16 +193,17 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else {
     const int sub = warp & 3;  // TMEM lanes [32*sub, 32*sub+32) belong to this warp
     int it = 0;
-    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++it) {
+    for (int u = blockIdx.x; u < units; u += gridDim.x, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       int b, tm, tn;
-      tile_coords(p, t, b, tm, tn);
+      tile_coords(p, u / p.splits, b, tm, tn);
       bool ok = CTB_WARP_WAIT(&acc_full[acc], acc_phase, status, DEV_TIMEOUT_MMA, abort);
       if (!ok) break;
       tc_fence_after();
       const int m = tm * kTileM + sub * 32 + lane;
       T* crow = C + (long long)b * p.strideC + m;
+      float* prow = p.partial + (long long)u * (kTileM * kTileN) + sub * 32 + lane;
       const uint32_t taddr = tmem_base + acc * kAccCols + ((uint32_t)(sub * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < kTileN / 32; ++c) {
@@ -202,7 +211,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         tmem_ld32(taddr + c * 32, r);
         tc_wait_ld();
         const int n0 = tn * kTileN + c * 32;
-        if (m < p.M) {
+        if (p.splits > 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) prow[(c * 32 + j) * kTileM] = __uint_as_float(r[j]);
+        } else if (m < p.M) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (n0 + j < p.N) {
@@ -224,6 +236,49 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Adds the splits of every tile in ascending order and writes C.  A thread takes four consecutive rows of a column
+// (16-byte loads; a warp covers 128 rows = one column of the tile) and requests eight splits at a time.
+template <typename T>
+__global__ void __launch_bounds__(256)
+    gemm_splitk_reduce_kernel(const float* __restrict__ partial, T* __restrict__ C, const Params p) {
+  constexpr int kTileElems = kTileM * kTileN;
+  const long long total = (long long)p.num_tiles * (kTileElems / 4);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / (kTileElems / 4)), e = (int)(i - (long long)t * (kTileElems / 4)) * 4;
+    const int col = e / kTileM, row = e - col * kTileM;
+    int b, tm, tn;
+    tile_coords(p, t, b, tm, tn);
+    const int m = tm * kTileM + row, n = tn * kTileN + col;
+    if (m >= p.M || n >= p.N) continue;
+    const float4* src = reinterpret_cast<const float4*>(partial + (long long)t * p.splits * kTileElems + e);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        v[q] = s0 + q < p.splits ? __ldcs(src + (long long)(s0 + q) * (kTileElems / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {  // ascending split order
+        acc.x += v[q].x;
+        acc.y += v[q].y;
+        acc.z += v[q].z;
+        acc.w += v[q].w;
+      }
+    }
+    T* dst = C + (long long)b * p.strideC + (long long)n * p.ldc + m;
+    const float o[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if (m + q < p.M) {
+        if constexpr (sizeof(T) == 4)
+          dst[q] = o[q];
+        else
+          dst[q] = __float2half_rn(o[q]);
+      }
+    }
   }
 }
 
@@ -472,6 +527,8 @@ int launch(ctb_ctx* ctx, cudaStream_t st, const T* A, const T* B, T* C, int M, i
       p.tiles_m = (M + kPairTileM - 1) / kPairTileM;
       p.tiles_n = (N + kTileN - 1) / kTileN;
       p.num_tiles = (int)pairs;
+      p.splits = 1;
+      p.partial = nullptr;
       const size_t smem = (size_t)kPairStages * P::STAGE_BYTES + 1024;
       auto k = gemm_pair_kernel<T>;
       cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -490,13 +547,30 @@ int launch(ctb_ctx* ctx, cudaStream_t st, const T* A, const T* B, T* C, int M, i
   const long long nt = (long long)p.tiles_m * p.tiles_n * batch;
   if (nt > INT32_MAX) return fail(CTB_UNSUPPORTED, "ctb_gemm: too many tiles");
   p.num_tiles = (int)nt;
+  // Few tiles and a long K (one rank's share of a batch-sharded problem): split K over the idle SMs, at least four
+  // k-blocks per split.
+  const int nk = (K + G::BK - 1) / G::BK;
+  p.splits = (int)std::max<long long>(1, std::min<long long>(std::min<long long>(ctx->sm_count / nt, nk / 4), 16));
+  p.partial = nullptr;
+  if (p.splits > 1) {
+    void* ws = nullptr;
+    int r = workspace(ctx, (size_t)nt * p.splits * kTileM * kTileN * sizeof(float), &ws, st);
+    if (r) return r;
+    p.partial = static_cast<float*>(ws);
+  }
   const size_t smem = (size_t)kStages * G::STAGE_BYTES + 1024;
   auto k = gemm_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e, "ctb_gemm: shared memory opt-in");
-  const int grid = (int)std::min<long long>(nt, ctx->sm_count);
+  const int grid = (int)std::min<long long>(nt * p.splits, ctx->sm_count);
   k<<<grid, kThreads, smem, st>>>(ta, tb, C, p, ctx->dev_status);
   CTB_CHECK_LAUNCH("ctb_gemm launch");
+  if (p.splits > 1) {
+    const long long work = nt * kTileM * kTileN / 4;
+    const int rgrid = (int)std::min<long long>((work + 255) / 256, (long long)ctx->sm_count * 8);
+    gemm_splitk_reduce_kernel<T><<<rgrid, 256, 0, st>>>(p.partial, C, p);
+    CTB_CHECK_LAUNCH("ctb_gemm split-K reduction launch");
+  }
   return CTB_OK;
 }
 

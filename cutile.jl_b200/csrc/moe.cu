@@ -928,7 +928,8 @@ __global__ void __launch_bounds__(256)
 struct EpFlags {
   uint32_t* flags[CTB_EP_MAX_RANKS];
 };
-__global__ void moe_ep_barrier_kernel(const EpFlags f, uint32_t* epoch, int world, int rank, int* status) {
+__global__ void moe_ep_barrier_kernel(const EpFlags f, uint32_t* epoch, int world, int rank, int* status,
+                                      unsigned long long limit_ns) {
   const int lane = threadIdx.x;
   uint32_t e = 0;
   if (lane == 0) {
@@ -944,7 +945,7 @@ __global__ void moe_ep_barrier_kernel(const EpFlags f, uint32_t* epoch, int worl
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
       if ((int32_t)(v - e) >= 0) break;
-      if ((it & 255u) == 255u && globaltimer_ns() - t0 > kWaitLimitNs) {
+      if ((it & 255u) == 255u && globaltimer_ns() - t0 > limit_ns) {
         atomicMax(status, DEV_TIMEOUT_SLOT);
         break;
       }
@@ -1316,7 +1317,7 @@ int ctb_moe_ep_barrier(ctb_ctx* ctx, void* stream, const ctb_ep_buffers* bufs) {
     if (q < bufs->world && !f.flags[q]) return fail(CTB_BAD_ARG, "ctb_moe_ep_barrier: null flag array of rank %d", q);
   }
   moe_ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(f, bufs->epoch, bufs->world, bufs->rank,
-                                                                        ctx->dev_status);
+                                                                        ctx->dev_status, ctx->flag_wait_ns);
   CTB_CHECK_LAUNCH("ctb_moe_ep_barrier launch");
   return CTB_OK;
 }

@@ -52,6 +52,7 @@ SIGNATURES = {
     "ctb_status_string": [_i],
     "ctb_version_info": [C.c_char_p, C.c_size_t],
     "ctb_check_device_status": [_p, _p],
+    "ctb_set_flag_wait_limit": [_p, C.c_uint64],
     "ctb_validate_hints": [_i, _i, _i, _i],
     "ctb_softmax": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
     "ctb_vadd": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i],
@@ -152,3 +153,8 @@ def context(device):
 
 def check_device_status(device, stream=0):
     check(lib.ctb_check_device_status(context(device), _p(stream)))
+
+
+def set_flag_wait_limit(device, nanoseconds):
+    """How long kernels of the device's context wait for another rank's flag before they give up (2 s by default)."""
+    check(lib.ctb_set_flag_wait_limit(context(device), int(nanoseconds)))

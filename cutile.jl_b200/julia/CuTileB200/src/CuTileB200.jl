@@ -75,6 +75,13 @@ function timed(f; nruns::Int=1, warmup::Int=0)
     return Float64[1000 * (CUDA.@elapsed f()) for _ in 1:nruns]
 end
 
+"Synchronises the current stream and throws if a kernel recorded a bounded-wait expiry or a bad index."
+check_device_status() = check(ccall((:ctb_check_device_status, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}), context(), stream()))
+
+"How long kernels wait for another rank's flag before they give up (nanoseconds; 2 s by default)."
+set_flag_wait_limit(ns::Integer) =
+    check(ccall((:ctb_set_flag_wait_limit, LIB), Cint, (Ptr{Cvoid}, UInt64), context(), UInt64(ns)))
+
 function versioninfo()
     buf = Vector{UInt8}(undef, 256)
     check(ccall((:ctb_version_info, LIB), Cint, (Ptr{UInt8}, Csize_t), buf, 256))

@@ -61,6 +61,11 @@ int ctb_version_info(char* buf, size_t n);
  * CTB_OK, or CTB_TIMEOUT / CTB_BAD_ARG if a kernel recorded a bounded-wait
  * expiry or a bad index since the last call. */
 int ctb_check_device_status(ctb_ctx* ctx, void* stream);
+/* How long the kernels of this context wait for a flag that another rank writes (the barrier of the peer-memory
+ * expert-parallel step) before they record a timeout in the status word and return; 1 microsecond to 10 seconds,
+ * 2 seconds by default.  A host that learns of a lost rank by other means lowers it so that the surviving ranks'
+ * next step ends quickly with CTB_TIMEOUT from ctb_check_device_status instead of waiting out the default. */
+int ctb_set_flag_wait_limit(ctb_ctx* ctx, uint64_t nanoseconds);
 
 /* Launch hints of the reference's launch layer (`@cuda backend=cuTile num_ctas=... occupancy=... opt_level=...
  * num_worker_warps=...`, src/launch.jl:855-869), validated with the reference's ranges (validate_hint,
