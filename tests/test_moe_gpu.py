@@ -73,7 +73,10 @@ def dev(d, *names):
 
 
 # examples/moe.jl:402-410 main() cases (random routing as in its prepare())
-@pytest.mark.parametrize("T,H,E,I,topk", [(48, 512, 64, 1024, 8), (128, 512, 32, 1024, 4), (64, 1024, 64, 2048, 8)])
+# the reference's main() cases, then cases with some hundred slots per expert: several full blocks per expert, ragged
+# last blocks, an intermediate size that is not a multiple of the tile
+@pytest.mark.parametrize("T,H,E,I,topk", [(48, 512, 64, 1024, 8), (128, 512, 32, 1024, 4), (64, 1024, 64, 2048, 8),
+                                          (1024, 256, 4, 384, 2), (600, 512, 2, 256, 1), (1500, 320, 5, 136, 1)])
 def test_cutile_moe_reference_cases(cuda, T, H, E, I, topk):
     import torch
     d = inputs.moe(tokens=T, hidden=H, experts=E, inter=I, topk=topk, seed=4)
