@@ -135,6 +135,7 @@ int ctb_create(ctb_ctx** out, int device) {
   c->sched_pool = nullptr;
   c->sched_next = 0;
   c->flag_wait_ns = 2000000000ull;
+  c->tf32_rne = 0;
   c->comm = nullptr;
   e = cudaMalloc(&c->dev_status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(c->dev_status, 0, sizeof(int));
@@ -208,6 +209,13 @@ int ctb_set_flag_wait_limit(ctb_ctx* ctx, uint64_t nanoseconds) {
   if (nanoseconds < 1000ull || nanoseconds > 10000000000ull)
     return fail(CTB_BAD_ARG, "ctb_set_flag_wait_limit: the limit must lie between 1 microsecond and 10 seconds");
   ctx->flag_wait_ns = nanoseconds;
+  return CTB_OK;
+}
+
+int ctb_set_tf32_rounding(ctb_ctx* ctx, int nearest_even) {
+  CTB_CHECK_CTX(ctx);
+  if (nearest_even != 0 && nearest_even != 1) return fail(CTB_BAD_ARG, "ctb_set_tf32_rounding: mode must be 0 or 1");
+  ctx->tf32_rne = nearest_even;
   return CTB_OK;
 }
 

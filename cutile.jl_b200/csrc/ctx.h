@@ -23,6 +23,7 @@ struct ctb_ctx {
   unsigned sched_next;
   void* comm;             // ctb_internal::Comm* once an NCCL communicator is attached (multi.cu)
   unsigned long long flag_wait_ns;  // how long a kernel waits for another rank's flag before it gives up
+  int tf32_rne;           // 1: f32 GEMM operands are rounded to TF32 (nearest even) by a pass of their own first
 };
 
 namespace ctb_internal {

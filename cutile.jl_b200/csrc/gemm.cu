@@ -487,11 +487,54 @@ int pair_clusters(ctb_ctx* ctx, size_t smem) {
   return c;
 }
 
+// out[i] = in[i] rounded to TF32 precision, nearest even (NaNs stay NaNs): u + 0xFFF + bit 13, low 13 bits cleared.
+__global__ void __launch_bounds__(256) tf32_round_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, long long n4,
+                                                         const uint32_t* __restrict__ in_tail, uint32_t* __restrict__ out_tail,
+                                                         int tail) {
+  auto rne = [](uint32_t u) {
+    const bool nan = ((u >> 23) & 0xFFu) == 0xFFu && (u & 0x7FFFFFu) != 0;
+    const uint32_t r = (u + 0xFFFu + ((u >> 13) & 1u)) & 0xFFFFE000u;
+    return nan ? ((u & 0xFFFFE000u) | 0x2000u) : r;
+  };
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    uint4 v = __ldcs(in + i);
+    v.x = rne(v.x); v.y = rne(v.y); v.z = rne(v.z); v.w = rne(v.w);
+    out[i] = v;
+  }
+  if (blockIdx.x == 0 && (int)threadIdx.x < tail) out_tail[threadIdx.x] = rne(in_tail[threadIdx.x]);
+}
+
 template <typename T>
 int launch(ctb_ctx* ctx, cudaStream_t st, const T* A, const T* B, T* C, int M, int N, int K, int batch, long long lda,
            long long ldb, long long ldc, long long sA, long long sB, long long sC) {
   using G = Cfg<T>;
   const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  size_t ws_used = 0;  // bytes of the context scratch taken by rounded operand copies (the split-K partials follow)
+  if (sizeof(T) == 4 && ctx->tf32_rne) {
+    // rounded copies with the layout of the originals (same leading dimensions and batch strides)
+    // elements from the first to the last one that the arrays are known to hold
+    const long long ea = (long long)(batch - 1) * sA + lda * (long long)(K - 1) + M;
+    const long long eb = (long long)(batch - 1) * sB + ldb * (long long)(N - 1) + K;
+    auto up = [](size_t v) { return (v + 255) & ~size_t(255); };
+    const size_t oa = 0, ob = up((size_t)ea * 4);
+    ws_used = ob + up((size_t)eb * 4);
+    const size_t partial_max = (size_t)ctx->sm_count * kTileM * kTileN * sizeof(float);  // split-K: at most one tile per SM
+    void* ws = nullptr;
+    int r = workspace(ctx, ws_used + partial_max, &ws, st);
+    if (r) return r;
+    float* A2 = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + oa);
+    float* B2 = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + ob);
+    const int rgrid = ctx->sm_count * 8;
+    tf32_round_kernel<<<rgrid, 256, 0, st>>>(reinterpret_cast<const uint4*>(A), reinterpret_cast<uint4*>(A2), ea / 4,
+                                            reinterpret_cast<const uint32_t*>(A) + (ea & ~3ll),
+                                            reinterpret_cast<uint32_t*>(A2) + (ea & ~3ll), (int)(ea & 3));
+    tf32_round_kernel<<<rgrid, 256, 0, st>>>(reinterpret_cast<const uint4*>(B), reinterpret_cast<uint4*>(B2), eb / 4,
+                                            reinterpret_cast<const uint32_t*>(B) + (eb & ~3ll),
+                                            reinterpret_cast<uint32_t*>(B2) + (eb & ~3ll), (int)(eb & 3));
+    CTB_CHECK_LAUNCH("ctb_gemm operand rounding launch");
+    A = reinterpret_cast<const T*>(A2);
+    B = reinterpret_cast<const T*>(B2);
+  }
   CUtensorMap ta, tb;
   {
     // A memory: [batch][K][M], M contiguous
@@ -554,9 +597,9 @@ int launch(ctb_ctx* ctx, cudaStream_t st, const T* A, const T* B, T* C, int M, i
   p.partial = nullptr;
   if (p.splits > 1) {
     void* ws = nullptr;
-    int r = workspace(ctx, (size_t)nt * p.splits * kTileM * kTileN * sizeof(float), &ws, st);
+    int r = workspace(ctx, ws_used + (size_t)nt * p.splits * kTileM * kTileN * sizeof(float), &ws, st);
     if (r) return r;
-    p.partial = static_cast<float*>(ws);
+    p.partial = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + ws_used);
   }
   const size_t smem = (size_t)kStages * G::STAGE_BYTES + 1024;
   auto k = gemm_kernel<T>;

@@ -53,6 +53,7 @@ SIGNATURES = {
     "ctb_version_info": [C.c_char_p, C.c_size_t],
     "ctb_check_device_status": [_p, _p],
     "ctb_set_flag_wait_limit": [_p, C.c_uint64],
+    "ctb_set_tf32_rounding": [_p, _i],
     "ctb_validate_hints": [_i, _i, _i, _i],
     "ctb_softmax": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
     "ctb_vadd": [_p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _i],
@@ -153,6 +154,12 @@ def context(device):
 
 def check_device_status(device, stream=0):
     check(lib.ctb_check_device_status(context(device), _p(stream)))
+
+
+def set_tf32_rounding(device, nearest_even):
+    """f32 GEMM operands: False = truncated by the tensor core (default), True = rounded to nearest even first, like
+    the reference's f32 -> tf32 conversion."""
+    check(lib.ctb_set_tf32_rounding(context(device), 1 if nearest_even else 0))
 
 
 def set_flag_wait_limit(device, nanoseconds):

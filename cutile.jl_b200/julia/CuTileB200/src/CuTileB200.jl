@@ -78,6 +78,10 @@ end
 "Synchronises the current stream and throws if a kernel recorded a bounded-wait expiry or a bad index."
 check_device_status() = check(ccall((:ctb_check_device_status, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}), context(), stream()))
 
+"f32 GEMM operands: `false` = truncated to TF32 by the tensor core (default), `true` = rounded to nearest even first."
+set_tf32_rounding(nearest_even::Bool) =
+    check(ccall((:ctb_set_tf32_rounding, LIB), Cint, (Ptr{Cvoid}, Cint), context(), nearest_even ? 1 : 0))
+
 "How long kernels wait for another rank's flag before they give up (nanoseconds; 2 s by default)."
 set_flag_wait_limit(ns::Integer) =
     check(ccall((:ctb_set_flag_wait_limit, LIB), Cint, (Ptr{Cvoid}, UInt64), context(), UInt64(ns)))

@@ -66,6 +66,12 @@ int ctb_check_device_status(ctb_ctx* ctx, void* stream);
  * 2 seconds by default.  A host that learns of a lost rank by other means lowers it so that the surviving ranks'
  * next step ends quickly with CTB_TIMEOUT from ctb_check_device_status instead of waiting out the default. */
 int ctb_set_flag_wait_limit(ctb_ctx* ctx, uint64_t nanoseconds);
+/* How ctb_gemm / ctb_gemm_batched turn f32 operands into TF32.  0 (default): the tensor core reads the f32 bits and
+ * ignores the low 13 mantissa bits (truncation; no extra pass).  1: round to nearest even like the reference's
+ * f32 -> tf32 conversion (src/compiler/intrinsics/conversions.jl:188-197, bit patterns of test/types.jl:203-245): a
+ * pass of its own writes rounded copies of A and B into the context's scratch first (about one fifth more time at
+ * 4096^3), after which the products are those of the reference's operands. */
+int ctb_set_tf32_rounding(ctb_ctx* ctx, int nearest_even);
 
 /* Launch hints of the reference's launch layer (`@cuda backend=cuTile num_ctas=... occupancy=... opt_level=...
  * num_worker_warps=...`, src/launch.jl:855-869), validated with the reference's ranges (validate_hint,

@@ -99,3 +99,30 @@ def test_gemm_strided_and_rejections(cuda):
     with pytest.raises(cuda.CtbError) as e:
         cuda.matmul.matmul_kernel(A, torch.zeros(80, 32, device="cuda"), C, 64, 64, 64)
     assert e.value.status == lib.BAD_ARG
+
+
+@pytest.mark.parametrize("M,N,K,batch", [(256, 256, 256, 1), (200, 300, 100, 1), (1024, 512, 2048, 2), (4096, 4096, 4096, 1)])
+def test_gemm_tf32_round_to_nearest_even_option(cuda, M, N, K, batch):
+    """With ctb_set_tf32_rounding(1) the operands are rounded like the reference's f32 -> tf32 conversion (nearest even,
+    pinned by the bit patterns of tests/golden/tf32_bits.json): against an oracle fed operands rounded that way only
+    f32 accumulation error remains, and the error against the exact product is below the truncating default's."""
+    import torch
+    lib = cuda._lib
+    if batch == 1:
+        d = inputs.gemm(M, N, K, seed=5)
+        run = lambda: dense(cuda, d)
+        exact, rounded = ref.gemm(d["A"], d["B"]), ref.gemm(ref.tf32_round(d["A"]), ref.tf32_round(d["B"]))
+    else:
+        d = inputs.batched_gemm(M, K, N, batch, seed=5)
+        run = lambda: batched(cuda, d)
+        exact = ref.batched_gemm(d["A"], d["B"])
+        rounded = ref.batched_gemm(ref.tf32_round(d["A"]), ref.tf32_round(d["B"]))
+    trunc_err = ref.rel_fro(run(), exact)
+    lib.set_tf32_rounding(0, True)
+    try:
+        C = run()
+    finally:
+        lib.set_tf32_rounding(0, False)
+    assert ref.rel_fro(C, rounded) <= 2e-5
+    assert ref.rel_fro(C, exact) < trunc_err
+    assert lib.lib.ctb_set_tf32_rounding(lib.context(0), 2) == lib.BAD_ARG
