@@ -35,6 +35,7 @@
 // 128 x 128 score tile costs each of the four schedulers about 1130 clocks when two warps
 // share the unit, 1275 for a warp on its own), against 512 clocks of tensor-core time per
 // tile.  A polynomial exp2 on the FMA pipe costs more per element than the unit does.
+#include <cuda_bf16.h>
 #include <math.h>
 
 #include "ctx.h"
@@ -148,6 +149,18 @@ __device__ __forceinline__ void chunk_max(uint32_t (&v)[32], int c, bool masked,
   }
 }
 
+// two f32 -> one 32-bit pair of 16-bit floats in the operands' format (round to nearest even)
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    return pack_f16x2(lo, hi);
+  }
+}
+
+template <bool BF16>
 __global__ void __launch_bounds__(kThreadsD, 1)
     fmha_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const Params p,
@@ -271,8 +284,9 @@ __global__ void __launch_bounds__(kThreadsD, 1)
       }
     } else {
       // ---- MMA issuer of stream s (whole warp in lock step, one elected lane issues)
-      constexpr uint32_t idesc_qk = make_idesc(FMT_F16, kTM, kTN, 0, 0);
-      constexpr uint32_t idesc_pv = make_idesc(FMT_F16, kTM, kD, 0, /*V is MN-major*/ 1);
+      constexpr uint32_t kFmt = BF16 ? FMT_BF16 : FMT_F16;
+      constexpr uint32_t idesc_qk = make_idesc(kFmt, kTM, kTN, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc(kFmt, kTM, kD, 0, /*V is MN-major*/ 1);
       const uint32_t tS = tmem + s * kStreamCols + kOffS, tP = tmem + s * kStreamCols + kOffP,
                      tO = tmem + s * kStreamCols + kOffO;
       bool ok = true;
@@ -417,8 +431,8 @@ __global__ void __launch_bounds__(kThreadsD, 1)
             const float p2 = ex2_approx_ftz(x1.x), p3 = ex2_approx_ftz(x1.y);
             a0 = fadd2(a0, p0, p1);
             a1 = fadd2(a1, p2, p3);
-            pk[(k >> 1) + 0] = pack_f16x2(p0, p1);
-            pk[(k >> 1) + 1] = pack_f16x2(p2, p3);
+            pk[(k >> 1) + 0] = pack16<BF16>(p0, p1);
+            pk[(k >> 1) + 1] = pack16<BF16>(p2, p3);
           }
           tmem_st16(trow + kOffP + c * 16, pk);
         }
@@ -486,10 +500,10 @@ __global__ void __launch_bounds__(kThreadsD, 1)
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             uint4 v;
-            v.x = pack_f16x2(__uint_as_float(r[k * 8 + 0]) * inv, __uint_as_float(r[k * 8 + 1]) * inv);
-            v.y = pack_f16x2(__uint_as_float(r[k * 8 + 2]) * inv, __uint_as_float(r[k * 8 + 3]) * inv);
-            v.z = pack_f16x2(__uint_as_float(r[k * 8 + 4]) * inv, __uint_as_float(r[k * 8 + 5]) * inv);
-            v.w = pack_f16x2(__uint_as_float(r[k * 8 + 6]) * inv, __uint_as_float(r[k * 8 + 7]) * inv);
+            v.x = pack16<BF16>(__uint_as_float(r[k * 8 + 0]) * inv, __uint_as_float(r[k * 8 + 1]) * inv);
+            v.y = pack16<BF16>(__uint_as_float(r[k * 8 + 2]) * inv, __uint_as_float(r[k * 8 + 3]) * inv);
+            v.z = pack16<BF16>(__uint_as_float(r[k * 8 + 4]) * inv, __uint_as_float(r[k * 8 + 5]) * inv);
+            v.w = pack16<BF16>(__uint_as_float(r[k * 8 + 6]) * inv, __uint_as_float(r[k * 8 + 7]) * inv);
             // 16-byte chunk c*4+k of row `lane`, at its place in the 128-byte swizzle
             *reinterpret_cast<uint4*>(stage + lane * 128 + (((c * 4 + k) ^ (lane & 7)) << 4)) = v;
           }
@@ -543,7 +557,8 @@ extern "C" int ctb_fmha_fwd(ctb_ctx* ctx, void* stream, const void* Q, const voi
                 (long long)kv_heads, query_group_size);
   if (!is_pow2(tile_m) || !is_pow2(tile_n))
     return fail(CTB_UNSUPPORTED_TILE, "ctb_fmha_fwd: tile_m/tile_n must be powers of two");
-  if (dtype != CTB_F16) return fail(CTB_UNSUPPORTED, "ctb_fmha_fwd: only f16 is implemented");
+  if (dtype != CTB_F16 && dtype != CTB_BF16) return fail(CTB_UNSUPPORTED, "ctb_fmha_fwd: f16 and bf16 are implemented");
+  const CUtensorMapDataType tdt = dtype == CTB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   if (d_k != kD || d_v != kD) return fail(CTB_UNSUPPORTED, "ctb_fmha_fwd: only head dimension 64 is implemented");
   if (input_pos < 0) return fail(CTB_BAD_ARG, "ctb_fmha_fwd: negative input_pos");
   if (seq_q > (1 << 24) || seq_kv > (1 << 24) || heads * batch > 65535 * 64)
@@ -557,15 +572,15 @@ extern "C" int ctb_fmha_fwd(ctb_ctx* ctx, void* stream, const void* Q, const voi
   {
     uint64_t dims[3] = {kD, (uint64_t)seq_q, (uint64_t)(heads * batch)};
     uint64_t str[2] = {kD * 2, (uint64_t)seq_q * kD * 2};
-    int r = make_tmap(&tq, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, Q, dims, str, box);
+    int r = make_tmap(&tq, tdt, 3, Q, dims, str, box);
     if (r) return r;
   }
   {
     uint64_t dims[3] = {kD, (uint64_t)seq_kv, (uint64_t)(kv_heads * batch)};
     uint64_t str[2] = {kD * 2, (uint64_t)seq_kv * kD * 2};
-    int r = make_tmap(&tk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, K, dims, str, box);
+    int r = make_tmap(&tk, tdt, 3, K, dims, str, box);
     if (r) return r;
-    r = make_tmap(&tv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, V, dims, str, box);
+    r = make_tmap(&tv, tdt, 3, V, dims, str, box);
     if (r) return r;
   }
   Params p;
@@ -583,14 +598,15 @@ extern "C" int ctb_fmha_fwd(ctb_ctx* ctx, void* stream, const void* Q, const voi
     const uint32_t obox[3] = {kD, 32, 1};
     uint64_t dims[3] = {kD, (uint64_t)seq_q, (uint64_t)(heads * batch)};
     uint64_t str[2] = {kD * 2, (uint64_t)seq_q * kD * 2};
-    int r = make_tmap(&to, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, Out, dims, str, obox);
+    int r = make_tmap(&to, tdt, 3, Out, dims, str, obox);
     if (r) return r;
   }
   const size_t smem = (size_t)2 * kStreamBytes + kOutStageBytes + 1024;
   const int grid = std::min((p.items + 1) / 2, ctx->sm_count);  // one persistent CTA per SM, two streams each
-  cudaError_t e = cudaFuncSetAttribute(fmha_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  auto kern = dtype == CTB_BF16 ? fmha_kernel<true> : fmha_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return cuda_fail(e, "ctb_fmha_fwd: shared memory opt-in");
-  fmha_kernel<<<grid, kThreadsD, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, to, p, ctx->dev_status);
+  kern<<<grid, kThreadsD, smem, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, to, p, ctx->dev_status);
   CTB_CHECK_LAUNCH("ctb_fmha_fwd launch");
   return CTB_OK;
 }

@@ -60,6 +60,7 @@ end
 dptr(a) = reinterpret(Ptr{Cvoid}, pointer(a))
 dtype(::Type{Float32}) = CTB_F32
 dtype(::Type{Float16}) = CTB_F16
+dtype(::Type{Core.BFloat16}) = Cint(2)  # CTB_BF16 (flash attention)
 
 """
     timed(f; nruns=1, warmup=0) -> Vector{Float64}

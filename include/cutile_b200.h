@@ -161,9 +161,10 @@ int ctb_gemm_batched(ctb_ctx* ctx, void* stream, const void* A, const void* B, v
  *             QUERY_GROUP_SIZE, CAUSAL, EVEN_K)      examples/fmha.jl:20-139
  * as launched by cutile_fmha(Q, K, V; ...)           examples/fmha.jl:146-168
  * Q, Out (D, seq_q, heads, batch); K, V (D, seq_kv, kv_heads, batch), dense,
- * f16.  heads = kv_heads * query_group_size.  Query i sits at position
+ * f16 or bf16.  heads = kv_heads * query_group_size.  Query i sits at position
  * i + input_pos for the causal rule.  EVEN_K is derived from seq_kv here.
- * Implemented: dtype CTB_F16, d_k = d_v = 64. */
+ * Implemented: dtype CTB_F16 and CTB_BF16 (operands, probabilities and output in that type; f32 scores, softmax
+ * state and accumulation), d_k = d_v = 64. */
 int ctb_fmha_fwd(ctb_ctx* ctx, void* stream, const void* Q, const void* K, const void* V, void* Out, int64_t d_k,
                  int64_t d_v, int64_t seq_q, int64_t seq_kv, int64_t heads, int64_t kv_heads, int64_t batch,
                  float qk_scale, int32_t input_pos, int tile_m, int tile_n, int query_group_size, int causal,

@@ -86,3 +86,21 @@ def test_fmha_rejections(cuda):
     with pytest.raises(cuda.CtbError) as e:
         cuda.fmha.cutile_fmha(q32, q32, q32)
     assert e.value.status == lib.UNSUPPORTED
+
+
+@pytest.mark.parametrize("batch,heads,seq_q,seq_kv,causal,input_pos,kv_heads", [
+    (2, 8, 128, 128, True, 0, 8), (8, 16, 1024, 1024, True, 0, 16), (2, 4, 200, 333, True, 133, 2), (1, 2, 256, 512, False, 0, 2)])
+def test_fmha_bf16(cuda, batch, heads, seq_q, seq_kv, causal, input_pos, kv_heads):
+    """bfloat16 operands (examples/fmha.jl takes the element type as a parameter, :236): the same kernel with bf16 MMAs,
+    probabilities and output rounded to bf16.  The oracle is fed the bf16-rounded inputs; tolerance 1e-2 (8 mantissa
+    bits in P and in the output)."""
+    import torch
+    d = inputs.fmha(batch, heads, seq_q, seq_kv, 64, kv_heads=kv_heads, seed=17)
+    Q, K, V = (torch.from_numpy(d[k].astype(np.float32)).cuda().to(torch.bfloat16) for k in ("Q", "K", "V"))
+    out = cuda.fmha.cutile_fmha(Q, K, V, causal=causal, input_pos=input_pos, query_group_size=heads // kv_heads)
+    torch.cuda.synchronize()
+    assert out.dtype == torch.bfloat16
+    back = lambda t: t.float().cpu().numpy()
+    want = ref.fmha(back(Q), back(K), back(V), causal=causal, input_pos=input_pos)
+    assert ref.rel_fro(back(out), want) <= 1e-2
+    cuda.check_device_status(0)
