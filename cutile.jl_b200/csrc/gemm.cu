@@ -26,6 +26,10 @@
 // examples/matmul.jl:30).  Each CTA loads its own 128 rows of A and its own 128 columns of B per k-block, so an SM
 // takes in 32 KB of operands per 128 x 256 x (128 bytes of K) of MMA work instead of 48 KB: operand delivery, not the
 // tensor pipe, is what bounds the single-CTA kernel.  No load in this file is a cluster multicast.
+#include <cuda_bf16.h>
+
+#include <type_traits>
+
 #include "ctx.h"
 #include "ptx.cuh"
 
@@ -41,6 +45,14 @@ constexpr int kThreads = 192;
 constexpr int kAccCols = kTileN;  // f32 accumulator columns per tile
 constexpr uint32_t kTmemCols = 512;
 
+// f32 accumulator -> result element (round to nearest even for the 16-bit types)
+template <typename T>
+__device__ __forceinline__ T from_f32(float v) {
+  if constexpr (std::is_same<T, float>::value) return v;
+  else if constexpr (std::is_same<T, __nv_bfloat16>::value) return __float2bfloat16_rn(v);
+  else return __float2half_rn(v);
+}
+
 template <typename T>
 struct Cfg {
   static constexpr int ES = sizeof(T);
@@ -52,7 +64,7 @@ struct Cfg {
   static constexpr int A_BYTES = A_BOXES * A_BOX_BYTES;
   static constexpr int B_BYTES = kTileN * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr uint32_t FMT = sizeof(T) == 4 ? FMT_TF32 : FMT_F16;
+  static constexpr uint32_t FMT = sizeof(T) == 4 ? FMT_TF32 : std::is_same<T, __nv_bfloat16>::value ? FMT_BF16 : FMT_F16;
   // An MN-major tf32 operand must use the 128-byte swizzle with 32-byte atoms
   // (4 K-rows per swizzle period); 16-bit types use the ordinary 128-byte swizzle.
   static constexpr uint32_t A_LAYOUT = sizeof(T) == 4 ? SDESC_SW128_ATOM32 : SDESC_SW128;
@@ -221,7 +233,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               if constexpr (sizeof(T) == 4)
                 crow[(long long)(n0 + j) * p.ldc] = __uint_as_float(r[j]);
               else
-                crow[(long long)(n0 + j) * p.ldc] = __float2half_rn(__uint_as_float(r[j]));
+                crow[(long long)(n0 + j) * p.ldc] = from_f32<T>(__uint_as_float(r[j]));
             }
           }
         }
@@ -276,7 +288,7 @@ __global__ void __launch_bounds__(256)
         if constexpr (sizeof(T) == 4)
           dst[q] = o[q];
         else
-          dst[q] = __float2half_rn(o[q]);
+          dst[q] = from_f32<T>(o[q]);
       }
     }
   }
@@ -440,7 +452,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
               if constexpr (sizeof(T) == 4)
                 crow[(long long)(n0 + j) * p.ldc] = __uint_as_float(r[j]);
               else
-                crow[(long long)(n0 + j) * p.ldc] = __float2half_rn(__uint_as_float(r[j]));
+                crow[(long long)(n0 + j) * p.ldc] = from_f32<T>(__uint_as_float(r[j]));
             }
           }
         }
@@ -508,7 +520,9 @@ template <typename T>
 int launch(ctb_ctx* ctx, cudaStream_t st, const T* A, const T* B, T* C, int M, int N, int K, int batch, long long lda,
            long long ldb, long long ldc, long long sA, long long sB, long long sC) {
   using G = Cfg<T>;
-  const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = sizeof(T) == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : std::is_same<T, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   size_t ws_used = 0;  // bytes of the context scratch taken by rounded operand copies (the split-K partials follow)
   if (sizeof(T) == 4 && ctx->tf32_rne) {
     // rounded copies with the layout of the originals (same leading dimensions and batch strides)
@@ -627,7 +641,8 @@ int gemm_common(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* 
   if (lda < M || ldb < K || ldc < M) return fail(CTB_BAD_ARG, "%s: leading dimension too small", who);
   if (!is_pow2(tm) || !is_pow2(tn) || !is_pow2(tk))
     return fail(CTB_UNSUPPORTED_TILE, "%s: tile sizes must be powers of two (got %d,%d,%d)", who, tm, tn, tk);
-  if (dtype != CTB_F32 && dtype != CTB_F16) return fail(CTB_BAD_ARG, "%s: dtype must be CTB_F32 or CTB_F16", who);
+  if (dtype != CTB_F32 && dtype != CTB_F16 && dtype != CTB_BF16)
+    return fail(CTB_BAD_ARG, "%s: dtype must be CTB_F32, CTB_F16 or CTB_BF16", who);
   CTB_CHECK_DEV(A); CTB_CHECK_DEV(B); CTB_CHECK_DEV(C);
   const int es = dtype == CTB_F32 ? 4 : 2;
   if ((lda * es) % 16 || (ldb * es) % 16 || (sA * es) % 16 || (sB * es) % 16 || (uintptr_t)A % 16 || (uintptr_t)B % 16)
@@ -636,6 +651,9 @@ int gemm_common(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* 
   if (dtype == CTB_F32)
     return launch<float>(ctx, st, (const float*)A, (const float*)B, (float*)C, (int)M, (int)N, (int)K, (int)batch, lda,
                          ldb, ldc, sA, sB, sC);
+  if (dtype == CTB_BF16)
+    return launch<__nv_bfloat16>(ctx, st, (const __nv_bfloat16*)A, (const __nv_bfloat16*)B, (__nv_bfloat16*)C, (int)M, (int)N,
+                                 (int)K, (int)batch, lda, ldb, ldc, sA, sB, sC);
   return launch<__half>(ctx, st, (const __half*)A, (const __half*)B, (__half*)C, (int)M, (int)N, (int)K, (int)batch,
                         lda, ldb, ldc, sA, sB, sC);
 }

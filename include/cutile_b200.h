@@ -145,7 +145,7 @@ int ctb_layernorm_bwd_dwdb(ctb_ctx* ctx, void* stream, const float* DW, const fl
 /* matmul_kernel(A, B, C, tm, tn, tk)                 examples/matmul.jl:28-60
  * C(M,N) = A(M,K) * B(K,N), column-major with leading dimensions lda/ldb/ldc.
  * dtype CTB_F32: TF32 tensor-core operands (low 13 mantissa bits ignored), f32
- * accumulate, f32 result.  dtype CTB_F16: f16 operands, f32 accumulate, f16 result.
+ * accumulate, f32 result.  dtype CTB_F16 / CTB_BF16: 16-bit operands, f32 accumulate, result in the operands' type.
  * A and B need 16-byte aligned bases and leading dimensions (TMA). */
 int ctb_gemm(ctb_ctx* ctx, void* stream, const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
              int64_t lda, int64_t ldb, int64_t ldc, int dtype, int tm, int tn, int tk);

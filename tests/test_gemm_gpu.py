@@ -126,3 +126,23 @@ def test_gemm_tf32_round_to_nearest_even_option(cuda, M, N, K, batch):
     assert ref.rel_fro(C, rounded) <= 2e-5
     assert ref.rel_fro(C, exact) < trunc_err
     assert lib.lib.ctb_set_tf32_rounding(lib.context(0), 2) == lib.BAD_ARG
+
+
+@pytest.mark.parametrize("M,K,N,batch", [(256, 128, 256, 1), (136, 40, 264, 2), (2048, 512, 2048, 1), (1024, 2048, 512, 8)])
+def test_gemm_bf16(cuda, M, K, N, batch):
+    """bfloat16 operands and result, f32 accumulation (the element type is a parameter of the reference's batched example,
+    examples/batchmatmul.jl:166): against the oracle on the bf16-rounded inputs, tolerance 1e-2 (8 mantissa bits in the
+    result); single-CTA, split-K and CTA-pair kernels."""
+    import torch
+    d = inputs.batched_gemm(M, K, N, batch, seed=7, dtype=np.float32)
+    A, B = (torch.from_numpy(d[k]).cuda().to(torch.bfloat16) for k in ("A", "B"))
+    C = torch.full((batch, N, M), float("nan"), device="cuda", dtype=torch.bfloat16)
+    cuda.batchmatmul.batch_matmul_kernel(A, B, C, 128, 128, 64)
+    torch.cuda.synchronize()
+    back = lambda t: t.float().cpu().numpy()
+    want = ref.batched_gemm(back(A), back(B))
+    assert ref.rel_fro(back(C), want) <= 1e-2
+    if batch == 1:
+        C2 = torch.empty(N, M, device="cuda", dtype=torch.bfloat16)
+        cuda.matmul.matmul_kernel(A[0], B[0], C2, 64, 64, 64)
+        assert torch.equal(C2, C[0])
