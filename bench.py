@@ -539,6 +539,82 @@ class Fft(Workload):
         return ref.rel_fro(np.stack([y.real, y.imag]), np.stack([want.real, want.imag]))
 
 
+class TiledFused(Workload):
+    name = "tiled_fused"
+    metric = "tiled_broadcast_gbps"
+    unit = "GB/s"
+    kernel = "tiled_broadcast_kernel"
+    n = 1 << 26
+
+    def describe(self):
+        return "ct.Tiled(C) .= A .+ A .* sin.(A) as one kernel, f32, 2^26 elements ~ U(-1,1) seed 8 (test/host/broadcast.jl:13-19)"
+
+    def work(self):
+        return 2 * self.n * 4
+
+    def host_inputs(self):
+        import numpy as np
+        g = np.random.default_rng(8)
+        return dict(a=(g.random(self.n, dtype=np.float32) * 2 - 1))
+
+    def to_device(self, host, torch):
+        a = torch.from_numpy(host["a"]).cuda()
+        return dict(a=a, c=torch.empty_like(a))
+
+    def step(self, ctb, st):
+        T = ctb.tiled
+        A = T.Tiled(st["a"])
+        T.assign(st["c"], A + A * T.sin(A))
+
+    def e2e_io(self, st):
+        return [("a",)], [("c",)]
+
+    def cpu_step(self, host, ref, np):
+        a = host["a"][: 1 << 22]
+        return (lambda: ref.tiled_broadcast(("add", a, ("mul", a, ("sin", a))), dtype=np.float32)), (1 << 22) / self.n, \
+            "2^22 of 2^26 elements, numpy float32"
+
+    def check(self, host, st, ref, np):
+        a = host["a"][: 1 << 20]
+        want = ref.tiled_broadcast(("add", a, ("mul", a, ("sin", a))))
+        return float(np.max(np.abs(st["c"][: 1 << 20].cpu().numpy() - want)))
+
+
+class TiledSum(Workload):
+    name = "tiled_sum"
+    metric = "tiled_mapreduce_gbps"
+    unit = "GB/s"
+    kernel = "tiled_reduce_kernel"
+    m = n = 8192
+
+    def describe(self):
+        return "sum(ct.Tiled(A); dims=1), f32 8192x8192 ~ U(0,1) seed 9 (test/host/mapreduce.jl:16-21)"
+
+    def work(self):
+        return self.m * self.n * 4 + self.n * 4
+
+    def host_inputs(self):
+        import numpy as np
+        return dict(a=np.random.default_rng(9).random((self.n, self.m), dtype=np.float32))
+
+    def to_device(self, host, torch):
+        return dict(a=torch.from_numpy(host["a"]).cuda(), out=torch.empty(self.n, 1, device="cuda"))
+
+    def step(self, ctb, st):
+        ctb.tiled.tsum(ctb.tiled.Tiled(st["a"]), dims=1, out=st["out"])
+
+    def e2e_io(self, st):
+        return [("a",)], [("out",)]
+
+    def cpu_step(self, host, ref, np):
+        a = host["a"]
+        return (lambda: ref.tiled_mapreduce("identity", "add", a, (1,), dtype=np.float32)), 1.0, "full 8192x8192, numpy float32"
+
+    def check(self, host, st, ref, np):
+        want = ref.tiled_mapreduce("identity", "add", host["a"], (1,))
+        return ref.rel_fro(st["out"].cpu().numpy(), want)
+
+
 class Moe(Workload):
     name = "moe_256"
     metric = "moe_ffn_tflops"
@@ -604,7 +680,7 @@ class Moe4096(Moe):
 
 def registry():
     w = [Fmha(), FmhaB64(), Moe(), Moe4096(), Gemm(), BatchedGemm(), LayerNormFwd(), LayerNormBwd(), Softmax(0), Softmax(1),
-         SoftmaxOnline(), VecAdd(), Transpose(), Fft()]
+         SoftmaxOnline(), VecAdd(), Transpose(), Fft(), TiledFused(), TiledSum()]
     return {x.name: x for x in w}
 
 

@@ -1,0 +1,523 @@
+// Host-level array operations: the counterparts of cuTile.jl's `ct.Tiled` broadcast (src/broadcast.jl: a whole
+// broadcast expression fused into one kernel) and mapreduce (src/mapreduce.jl: sum / prod / maximum / minimum / a
+// mapped reduction over any set of dimensions).  The reference compiles the Julia expression; a prebuilt library
+// cannot, so the expression arrives as a short postfix program (push input, push constant, unary function, binary
+// operator) that every thread evaluates on a register stack for four neighbouring elements at a time: still one pass
+// over memory, one kernel, whatever the expression.  Arrays have up to three dimensions, column-major, first
+// dimension contiguous; an operand with extent 1 along a dimension is expanded along it (stride 0).  Arithmetic is
+// f32 whatever the element type.  Both are bound by HBM bandwidth: bytes of the operands read once plus the result.
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include <algorithm>
+
+#include "ctx.h"
+
+using namespace ctb_internal;
+
+namespace {
+
+constexpr int kMaxOps = CTB_TILED_MAX_OPS;
+constexpr int kMaxInputs = CTB_TILED_MAX_INPUTS;
+constexpr int kMaxConsts = CTB_TILED_MAX_CONSTS;
+constexpr int kStack = 4;
+
+struct Program {
+  int n_ops;
+  short op[kMaxOps];
+  short arg[kMaxOps];
+  float consts[kMaxConsts];
+};
+
+struct Operands {
+  const void* ptr[kMaxInputs];
+  long long stride[kMaxInputs][3];
+};
+
+__device__ __forceinline__ float unary(int op, float x) {
+  switch (op) {
+    case CTB_TILED_NEG: return -x;
+    case CTB_TILED_ABS: return fabsf(x);
+    case CTB_TILED_SQRT: return sqrtf(x);
+    case CTB_TILED_EXP: return expf(x);
+    case CTB_TILED_EXP2: return exp2f(x);
+    case CTB_TILED_LOG: return logf(x);
+    case CTB_TILED_LOG2: return log2f(x);
+    case CTB_TILED_SIN: return sinf(x);
+    case CTB_TILED_COS: return cosf(x);
+    case CTB_TILED_TANH: return tanhf(x);
+    case CTB_TILED_INV: return 1.0f / x;
+    case CTB_TILED_ABS2: return x * x;
+    default: return x;  // CTB_TILED_IDENTITY
+  }
+}
+__device__ __forceinline__ float binary(int op, float a, float b) {
+  switch (op) {
+    case CTB_TILED_ADD: return a + b;
+    case CTB_TILED_SUB: return a - b;
+    case CTB_TILED_MUL: return a * b;
+    case CTB_TILED_DIV: return a / b;
+    case CTB_TILED_MAX: return fmaxf(a, b);
+    case CTB_TILED_MIN: return fminf(a, b);
+    default: return powf(a, b);  // CTB_TILED_POW
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float load1(const void* p, long long i) {
+  if constexpr (sizeof(T) == 4) return static_cast<const float*>(p)[i];
+  else return __half2float(static_cast<const __half*>(p)[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store1(void* p, long long i, float v) {
+  if constexpr (sizeof(T) == 4) static_cast<float*>(p)[i] = v;
+  else static_cast<__half*>(p)[i] = __float2half_rn(v);
+}
+
+// V = 8 or 4: that many neighbouring elements of the first dimension per thread and trip (the host checks that every
+// operand is either contiguous or expanded along it and that rows start on 16-byte boundaries; the cost of decoding
+// an operation is shared by the V elements); V = 1: anything else.
+// DENSE: every operand either has the destination's shape (dense) or is a single element: one linear index, no
+// division.  Otherwise the element index is split into its three coordinates (32-bit arithmetic; the host checks
+// that the element count fits).  The operands are read once per element into registers; pushes are register moves.
+template <typename T, int V, bool DENSE>
+__global__ void __launch_bounds__(256)
+    tiled_broadcast_kernel(void* __restrict__ dest, const Operands in, const Program prog, int n_inputs, long long d0,
+                           long long d1, long long d2) {
+  const long long n0 = d0 / V, total = n0 * d1 * d2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    long long o;          // element offset in the destination
+    long long off[kMaxInputs];
+    long long st0[kMaxInputs];
+    if (DENSE) {
+      o = i * V;
+#pragma unroll
+      for (int a = 0; a < kMaxInputs; ++a) {
+        st0[a] = in.stride[a][0];
+        off[a] = st0[a] ? o : 0;
+      }
+    } else {
+      const unsigned u = (unsigned)i, un0 = (unsigned)n0, ud1 = (unsigned)d1;
+      const unsigned r = u / un0, i0 = (u - r * un0) * V, i2 = r / ud1, i1 = r - i2 * ud1;
+      o = i0 + d0 * (i1 + d1 * (long long)i2);
+#pragma unroll
+      for (int a = 0; a < kMaxInputs; ++a) {
+        st0[a] = in.stride[a][0];
+        off[a] = i0 * st0[a] + i1 * in.stride[a][1] + i2 * in.stride[a][2];
+      }
+    }
+    float x[kMaxInputs][V];
+#pragma unroll
+    for (int a = 0; a < kMaxInputs; ++a) {
+      if (a < n_inputs) {
+        if (V >= 4 && st0[a] == 1) {
+#pragma unroll
+          for (int g = 0; g < V / 4; ++g) {
+            if constexpr (sizeof(T) == 4) {
+              const float4 q = __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(in.ptr[a]) + off[a]) + g);
+              x[a][(4 * g) % V] = q.x; x[a][(4 * g + 1) % V] = q.y; x[a][(4 * g + 2) % V] = q.z; x[a][(4 * g + 3) % V] = q.w;
+            } else {
+              const uint2 q = __ldcs(reinterpret_cast<const uint2*>(static_cast<const __half*>(in.ptr[a]) + off[a]) + g);
+              const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+              const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
+              x[a][(4 * g) % V] = lo.x; x[a][(4 * g + 1) % V] = lo.y; x[a][(4 * g + 2) % V] = hi.x; x[a][(4 * g + 3) % V] = hi.y;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < V; ++v) x[a][v] = load1<T>(in.ptr[a], off[a] + v * st0[a]);
+        }
+      } else {
+#pragma unroll
+        for (int v = 0; v < V; ++v) x[a][v] = 0.f;
+      }
+    }
+    float s0[V], s1[V], s2[V], s3[V];  // the stack, top first
+#pragma unroll
+    for (int v = 0; v < V; ++v) s0[v] = s1[v] = s2[v] = s3[v] = 0.f;
+    for (int k = 0; k < prog.n_ops; ++k) {
+      const int op = prog.op[k], arg = prog.arg[k];
+      if (op <= CTB_TILED_CONST) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          s3[v] = s2[v]; s2[v] = s1[v]; s1[v] = s0[v];
+        }
+        if (op == CTB_TILED_CONST) {
+          const float c = prog.consts[arg & (kMaxConsts - 1)];
+#pragma unroll
+          for (int v = 0; v < V; ++v) s0[v] = c;
+        } else {
+          switch (arg) {
+            case 0:
+#pragma unroll
+              for (int v = 0; v < V; ++v) s0[v] = x[0][v];
+              break;
+            case 1:
+#pragma unroll
+              for (int v = 0; v < V; ++v) s0[v] = x[1][v];
+              break;
+            case 2:
+#pragma unroll
+              for (int v = 0; v < V; ++v) s0[v] = x[2][v];
+              break;
+            default:
+#pragma unroll
+              for (int v = 0; v < V; ++v) s0[v] = x[3][v];
+              break;
+          }
+        }
+      } else if (op < CTB_TILED_ADD) {
+        // one dispatch per operation and thread, not per element
+#define CTB_U(CODE, EXPR)               \
+  case CODE:                            \
+    _Pragma("unroll") for (int v = 0; v < V; ++v) { const float t = s0[v]; s0[v] = (EXPR); } \
+    break;
+        switch (op) {
+          CTB_U(CTB_TILED_NEG, -t)
+          CTB_U(CTB_TILED_ABS, fabsf(t))
+          CTB_U(CTB_TILED_SQRT, sqrtf(t))
+          CTB_U(CTB_TILED_EXP, expf(t))
+          CTB_U(CTB_TILED_EXP2, exp2f(t))
+          CTB_U(CTB_TILED_LOG, logf(t))
+          CTB_U(CTB_TILED_LOG2, log2f(t))
+          CTB_U(CTB_TILED_SIN, sinf(t))
+          CTB_U(CTB_TILED_COS, cosf(t))
+          CTB_U(CTB_TILED_TANH, tanhf(t))
+          CTB_U(CTB_TILED_INV, 1.0f / t)
+          CTB_U(CTB_TILED_ABS2, t * t)
+          default: break;  // CTB_TILED_IDENTITY
+        }
+#undef CTB_U
+      } else {
+#define CTB_B(CODE, EXPR)               \
+  case CODE:                            \
+    _Pragma("unroll") for (int v = 0; v < V; ++v) { const float a = s1[v], b = s0[v]; s0[v] = (EXPR); } \
+    break;
+        switch (op) {
+          CTB_B(CTB_TILED_ADD, a + b)
+          CTB_B(CTB_TILED_SUB, a - b)
+          CTB_B(CTB_TILED_MUL, a * b)
+          CTB_B(CTB_TILED_DIV, a / b)
+          CTB_B(CTB_TILED_MAX, fmaxf(a, b))
+          CTB_B(CTB_TILED_MIN, fminf(a, b))
+          default:
+#pragma unroll
+            for (int v = 0; v < V; ++v) s0[v] = powf(s1[v], s0[v]);
+            break;
+        }
+#undef CTB_B
+#pragma unroll
+        for (int v = 0; v < V; ++v) {
+          s1[v] = s2[v];
+          s2[v] = s3[v];
+        }
+      }
+    }
+    if (V >= 4) {
+#pragma unroll
+      for (int g = 0; g < V / 4; ++g) {
+        if constexpr (sizeof(T) == 4) {
+          __stcs(reinterpret_cast<float4*>(static_cast<float*>(dest) + o) + g,
+                 make_float4(s0[(4 * g) % V], s0[(4 * g + 1) % V], s0[(4 * g + 2) % V], s0[(4 * g + 3) % V]));
+        } else {
+          uint2 q;
+          *reinterpret_cast<__half2*>(&q.x) = __floats2half2_rn(s0[(4 * g) % V], s0[(4 * g + 1) % V]);
+          *reinterpret_cast<__half2*>(&q.y) = __floats2half2_rn(s0[(4 * g + 2) % V], s0[(4 * g + 3) % V]);
+          __stcs(reinterpret_cast<uint2*>(static_cast<__half*>(dest) + o) + g, q);
+        }
+      }
+    } else {
+      store1<T>(dest, o, s0[0]);
+    }
+  }
+}
+
+// ---- mapreduce ----------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float neutral(int op) {
+  return op == CTB_TILED_ADD ? 0.f : op == CTB_TILED_MUL ? 1.f : op == CTB_TILED_MAX ? -INFINITY : INFINITY;
+}
+
+struct ReduceShape {
+  long long d[3];        // extents
+  long long keep_n[3];   // extent of each dimension in the output index space (1 when reduced)
+  long long red_n[3];    // extent of each dimension in the reduced index space (1 when kept)
+  long long outputs, red_len, parts, chunk;
+};
+
+// Mode A (the first dimension is reduced): one CTA per (output, part).  The reduced index space is the first
+// dimension (contiguous) times the other reduced dimensions ("rows"); a part is a range [lo, hi) of it.  The CTA walks
+// its rows one after the other, inside a row 16 bytes per thread and trip where the row starts on a 16-byte boundary,
+// and combines in a fixed order (thread partials, lanes, then warps in order).
+// Mode B (the first dimension is kept): one thread per output, outputs along the first dimension in neighbouring
+// threads (coalesced), the part's share of the reduced index space walked in order with running coordinates.
+// OP is a compile-time constant and so is "f is the identity": a dispatch per element would cost more than the element.
+template <typename T, bool MODE_A, int OP, bool MAPPED>
+__global__ void __launch_bounds__(256)
+    tiled_reduce_kernel(const void* __restrict__ src, float* __restrict__ partial, void* __restrict__ dest, const ReduceShape s,
+                        int f_code) {
+  constexpr int op = OP;
+  auto fmap = [&](float v) { return MAPPED ? unary(f_code, v) : v; };
+  __shared__ float wsum[8];
+  const long long part = blockIdx.y;
+  const long long lo = part * s.chunk, hi = min(s.red_len, lo + s.chunk);
+  const long long st1 = s.d[0], st2 = s.d[0] * s.d[1];  // element strides of dimensions 1 and 2
+  if (MODE_A) {
+    // output coordinates: the first dimension is reduced, so the output index runs over dimensions 1 and 2
+    const long long o = blockIdx.x;
+    const long long k1 = o % s.keep_n[1], k2 = o / s.keep_n[1];
+    const long long base = k1 * st1 + k2 * st2;
+    const long long d0 = s.d[0];
+    constexpr int V = 16 / sizeof(T);
+    float acc = neutral(op);
+    for (long long row = lo / d0; row * d0 < hi; ++row) {  // rows of the reduced index space that this part touches
+      const long long r1 = row % s.red_n[1], r2 = row / s.red_n[1];
+      const long long rbase = base + r1 * st1 + r2 * st2;
+      const long long c_lo = max(lo - row * d0, 0ll), c_hi = min(hi - row * d0, d0);
+      const bool vec = ((rbase + c_lo) * (long long)sizeof(T) + (long long)(uintptr_t)src) % 16 == 0;
+      const long long c_vec = vec ? c_lo + (c_hi - c_lo) / V * V : c_lo;
+      for (long long c = c_lo + (long long)threadIdx.x * V; c < c_vec; c += 256 * V) {
+        if constexpr (sizeof(T) == 4) {
+          const float4 q = __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(src) + rbase + c));
+          acc = binary(op, acc, fmap(q.x));
+          acc = binary(op, acc, fmap(q.y));
+          acc = binary(op, acc, fmap(q.z));
+          acc = binary(op, acc, fmap(q.w));
+        } else {
+          const uint4 q = __ldcs(reinterpret_cast<const uint4*>(static_cast<const __half*>(src) + rbase + c));
+          const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 v = __half22float2(h[j]);
+            acc = binary(op, acc, fmap(v.x));
+            acc = binary(op, acc, fmap(v.y));
+          }
+        }
+      }
+      for (long long c = c_vec + threadIdx.x; c < c_hi; c += 256) acc = binary(op, acc, fmap(load1<T>(src, rbase + c)));
+    }
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) acc = binary(op, acc, __shfl_xor_sync(0xffffffffu, acc, sh));
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = wsum[0];
+      for (int w = 1; w < (int)(blockDim.x >> 5); ++w) t = binary(op, t, wsum[w]);
+      if (s.parts > 1) partial[o * s.parts + part] = t;
+      else store1<T>(dest, o, t);
+    }
+  } else {
+    const long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= s.outputs) return;
+    // output coordinates over the kept dimensions (the first one is kept), reduced coordinates over dimensions 1 and 2
+    const long long k0 = o % s.keep_n[0], q = o / s.keep_n[0], k1 = q % s.keep_n[1], k2 = q / s.keep_n[1];
+    const long long base = k0 + k1 * st1 + k2 * st2;
+    long long r1 = lo % s.red_n[1], r2 = lo / s.red_n[1];
+    long long off = base + r1 * st1 + r2 * st2;
+    auto advance = [&]() {  // to the next reduced coordinate, dimension 1 fastest
+      off += st1;
+      if (++r1 == s.red_n[1]) {
+        r1 = 0;
+        ++r2;
+        off = base + r2 * st2;
+      }
+    };
+    float acc = neutral(op);
+    long long r = lo;
+    for (; r + 4 <= hi; r += 4) {  // four loads in flight; combined in index order
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[j] = load1<T>(src, off);
+        advance();
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc = binary(op, acc, fmap(v[j]));
+    }
+    for (; r < hi; ++r) {
+      acc = binary(op, acc, fmap(load1<T>(src, off)));
+      advance();
+    }
+    if (s.parts > 1) partial[o * s.parts + part] = acc;
+    else store1<T>(dest, o, acc);
+  }
+}
+
+template <typename T, int OP>
+__global__ void tiled_reduce_final_kernel(const float* __restrict__ partial, void* __restrict__ dest, long long outputs,
+                                          long long parts) {
+  constexpr int op = OP;
+  const long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= outputs) return;
+  float acc = partial[o * parts];
+  for (long long p = 1; p < parts; ++p) acc = binary(op, acc, partial[o * parts + p]);  // ascending part order
+  store1<T>(dest, o, acc);
+}
+
+}  // namespace
+
+extern "C" {
+
+int ctb_tiled_broadcast(ctb_ctx* ctx, void* stream, void* dest, const int64_t* shape, const void* const* inputs,
+                        const int64_t* input_strides, int n_inputs, const int32_t* program, int n_ops, const float* constants,
+                        int n_constants, int dtype) {
+  CTB_CHECK_CTX(ctx);
+  if (!shape || !program) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: null shape or program");
+  if (dtype != CTB_F32 && dtype != CTB_F16) return fail(CTB_UNSUPPORTED, "ctb_tiled_broadcast: element type must be f32 or f16");
+  if (n_inputs < 0 || n_inputs > kMaxInputs || n_ops < 1 || n_ops > kMaxOps || n_constants < 0 || n_constants > kMaxConsts)
+    return fail(CTB_UNSUPPORTED, "ctb_tiled_broadcast: at most %d inputs, %d operations and %d constants", kMaxInputs, kMaxOps,
+                kMaxConsts);
+  if ((n_inputs && (!inputs || !input_strides)) || (n_constants && !constants))
+    return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: null operand table");
+  for (int k = 0; k < 3; ++k)
+    if (shape[k] < 0) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: negative extent");
+  Program prog;
+  prog.n_ops = n_ops;
+  int depth = 0;
+  for (int k = 0; k < n_ops; ++k) {
+    const int op = program[2 * k], arg = program[2 * k + 1];
+    if (op == CTB_TILED_INPUT) {
+      if (arg < 0 || arg >= n_inputs) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: operation %d names input %d", k, arg);
+      ++depth;
+    } else if (op == CTB_TILED_CONST) {
+      if (arg < 0 || arg >= n_constants) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: operation %d names constant %d", k, arg);
+      ++depth;
+    } else if (op >= CTB_TILED_IDENTITY && op <= CTB_TILED_ABS2) {
+      if (depth < 1) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: operation %d finds an empty stack", k);
+    } else if (op >= CTB_TILED_ADD && op <= CTB_TILED_POW) {
+      if (depth < 2) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: operation %d needs two values on the stack", k);
+      --depth;
+    } else {
+      return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: unknown operation code %d", op);
+    }
+    if (depth > kStack) return fail(CTB_UNSUPPORTED, "ctb_tiled_broadcast: the expression needs more than %d stack entries", kStack);
+    prog.op[k] = (short)op;
+    prog.arg[k] = (short)arg;
+  }
+  if (depth != 1) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: the program leaves %d values on the stack", depth);
+  for (int k = 0; k < n_constants; ++k) prog.consts[k] = constants[k];
+  const long long d0 = shape[0], d1 = shape[1], d2 = shape[2];
+  if (d0 == 0 || d1 == 0 || d2 == 0) return CTB_OK;  // empty arrays: nothing to launch
+  CTB_CHECK_DEV(dest);
+  const int es = dtype == CTB_F32 ? 4 : 2;
+  Operands in = {};
+  bool vec = d0 % 4 == 0 && (uintptr_t)dest % 16 == 0;
+  for (int a = 0; a < n_inputs; ++a) {
+    CTB_CHECK_DEV(inputs[a]);
+    in.ptr[a] = inputs[a];
+    for (int k = 0; k < 3; ++k) {
+      in.stride[a][k] = input_strides[3 * a + k];
+      if (in.stride[a][k] < 0) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: negative stride");
+    }
+    const long long s0 = in.stride[a][0];
+    if (s0 == 1) {  // vector loads need aligned rows
+      if ((uintptr_t)inputs[a] % (4 * es) || (in.stride[a][1] * es) % (4 * es) || (in.stride[a][2] * es) % (4 * es)) vec = false;
+    } else if (s0 != 0) {
+      vec = false;
+    }
+  }
+  // dense: every operand is laid out like the destination or is a single element
+  bool dense = true;
+  for (int a = 0; a < n_inputs; ++a) {
+    const bool like_dest = in.stride[a][0] == 1 && (d1 == 1 || in.stride[a][1] == d0) && (d2 == 1 || in.stride[a][2] == d0 * d1);
+    const bool single = in.stride[a][0] == 0 && (d1 == 1 || in.stride[a][1] == 0) && (d2 == 1 || in.stride[a][2] == 0);
+    if (!like_dest && !single) dense = false;
+  }
+  const bool vec8 = false;  // eight elements per thread measured slower than four (registers)
+  const long long units = (vec8 ? d0 / 8 : vec ? d0 / 4 : d0) * d1 * d2;
+  if (!dense && units > 0x7fffffffLL) return fail(CTB_UNSUPPORTED, "ctb_tiled_broadcast: too many elements for an expanded operand");
+  const int grid = (int)std::max<long long>(1, std::min<long long>((units + 255) / 256, (long long)ctx->sm_count * 16));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define CTB_TILED_LAUNCH(T, V, D) tiled_broadcast_kernel<T, V, D><<<grid, 256, 0, st>>>(dest, in, prog, n_inputs, d0, d1, d2)
+#define CTB_TILED_PICK(T)                                  \
+  do {                                                     \
+    if (vec8) CTB_TILED_LAUNCH(T, 8, true);                \
+    else if (vec && dense) CTB_TILED_LAUNCH(T, 4, true);   \
+    else if (vec) CTB_TILED_LAUNCH(T, 4, false);           \
+    else if (dense) CTB_TILED_LAUNCH(T, 1, true);          \
+    else CTB_TILED_LAUNCH(T, 1, false);                    \
+  } while (0)
+  if (dtype == CTB_F32) CTB_TILED_PICK(float);
+  else CTB_TILED_PICK(__half);
+#undef CTB_TILED_PICK
+#undef CTB_TILED_LAUNCH
+  CTB_CHECK_LAUNCH("ctb_tiled_broadcast launch");
+  return CTB_OK;
+}
+
+int ctb_tiled_mapreduce(ctb_ctx* ctx, void* stream, void* dest, const void* src, const int64_t* shape, int reduce_mask, int f,
+                        int op, int dtype) {
+  CTB_CHECK_CTX(ctx);
+  if (!shape) return fail(CTB_BAD_ARG, "ctb_tiled_mapreduce: null shape");
+  if (dtype != CTB_F32 && dtype != CTB_F16) return fail(CTB_UNSUPPORTED, "ctb_tiled_mapreduce: element type must be f32 or f16");
+  if (f < CTB_TILED_IDENTITY || f > CTB_TILED_ABS2) return fail(CTB_BAD_ARG, "ctb_tiled_mapreduce: f must be a unary function code");
+  if (op != CTB_TILED_ADD && op != CTB_TILED_MUL && op != CTB_TILED_MAX && op != CTB_TILED_MIN)
+    return fail(CTB_UNSUPPORTED, "ctb_tiled_mapreduce: the reduction must be +, *, max or min");
+  if (reduce_mask < 0 || reduce_mask > 7) return fail(CTB_BAD_ARG, "ctb_tiled_mapreduce: reduce_mask has bits for three dimensions");
+  ReduceShape s;
+  s.outputs = 1;
+  s.red_len = 1;
+  for (int k = 0; k < 3; ++k) {
+    if (shape[k] < 0) return fail(CTB_BAD_ARG, "ctb_tiled_mapreduce: negative extent");
+    s.d[k] = shape[k];
+    const bool red = (reduce_mask >> k) & 1;
+    s.keep_n[k] = red ? 1 : shape[k];
+    s.red_n[k] = red ? shape[k] : 1;
+    s.outputs *= s.keep_n[k];
+    s.red_len *= s.red_n[k];
+  }
+  if (s.outputs == 0) return CTB_OK;  // no output elements
+  CTB_CHECK_DEV(dest);
+  if (s.red_len > 0) CTB_CHECK_DEV(src);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool mode_a = (reduce_mask & 1) != 0 && s.red_len > 0;
+  // enough (output, part) pairs to fill the GPU; a part is at least 4096 reduced elements for a CTA, 32 for a thread
+  const long long want = mode_a ? (long long)ctx->sm_count * 8 : (long long)ctx->sm_count * 8 * 256;
+  const long long min_part = mode_a ? 4096 : 32;
+  s.parts = std::max<long long>(1, std::min<long long>({want / std::max<long long>(1, s.outputs),
+                                                        (s.red_len + min_part - 1) / min_part, (long long)1024}));
+  s.chunk = (std::max<long long>(1, s.red_len) + s.parts - 1) / s.parts;
+  if (mode_a) s.chunk = (s.chunk + 1023) / 1024 * 1024;  // parts start on 16-byte boundaries of an aligned row
+  s.parts = (std::max<long long>(1, s.red_len) + s.chunk - 1) / s.chunk;
+  float* partial = nullptr;
+  if (s.parts > 1) {
+    void* ws = nullptr;
+    int r = workspace(ctx, (size_t)s.outputs * s.parts * sizeof(float), &ws, st);
+    if (r) return r;
+    partial = static_cast<float*>(ws);
+  }
+  if (mode_a && s.outputs > 0x7fffffffLL) return fail(CTB_UNSUPPORTED, "ctb_tiled_mapreduce: too many output elements");
+  const dim3 grid(mode_a ? (unsigned)s.outputs : (unsigned)((s.outputs + 255) / 256), (unsigned)s.parts);
+  const unsigned fgrid = (unsigned)((s.outputs + 255) / 256);
+  const bool mapped = f != CTB_TILED_IDENTITY;
+#define CTB_RED_LAUNCH(T, A, OP, M)                                                                \
+  do {                                                                                             \
+    tiled_reduce_kernel<T, A, OP, M><<<grid, 256, 0, st>>>(src, partial, dest, s, f);             \
+    if (s.parts > 1) tiled_reduce_final_kernel<T, OP><<<fgrid, 256, 0, st>>>(partial, dest, s.outputs, s.parts); \
+  } while (0)
+#define CTB_RED_MAPPED(T, A, OP)              \
+  do {                                        \
+    if (mapped) CTB_RED_LAUNCH(T, A, OP, true); \
+    else CTB_RED_LAUNCH(T, A, OP, false);     \
+  } while (0)
+#define CTB_RED_OP(T, A)                                              \
+  do {                                                                \
+    if (op == CTB_TILED_ADD) CTB_RED_MAPPED(T, A, CTB_TILED_ADD);     \
+    else if (op == CTB_TILED_MUL) CTB_RED_MAPPED(T, A, CTB_TILED_MUL); \
+    else if (op == CTB_TILED_MAX) CTB_RED_MAPPED(T, A, CTB_TILED_MAX); \
+    else CTB_RED_MAPPED(T, A, CTB_TILED_MIN);                         \
+  } while (0)
+  if (dtype == CTB_F32) {
+    if (mode_a) CTB_RED_OP(float, true);
+    else CTB_RED_OP(float, false);
+  } else {
+    if (mode_a) CTB_RED_OP(__half, true);
+    else CTB_RED_OP(__half, false);
+  }
+#undef CTB_RED_OP
+#undef CTB_RED_MAPPED
+#undef CTB_RED_LAUNCH
+  CTB_CHECK_LAUNCH("ctb_tiled_mapreduce launch");
+  return CTB_OK;
+}
+
+}  // extern "C"

@@ -8,4 +8,4 @@ CUDA library; nothing here computes on the host.
 """
 from . import _lib  # noqa: F401  (fails loudly when the shared library is missing)
 from ._lib import CtbError, version_info, check_device_status  # noqa: F401
-from . import softmax, layernorm, matmul, batchmatmul, fmha, moe, multi, vadd, transpose, fft  # noqa: F401
+from . import softmax, layernorm, matmul, batchmatmul, fmha, moe, multi, vadd, transpose, fft, tiled  # noqa: F401

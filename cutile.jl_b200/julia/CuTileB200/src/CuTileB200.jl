@@ -387,4 +387,115 @@ moe_workspace_bytes(T, H, I, E, topk, tile_m) =
 reserve_workspace(bytes) =
     check(ccall((:ctb_reserve_workspace, LIB), Cint, (Ptr{Cvoid}, Ptr{Cvoid}, Csize_t), context(), stream(), bytes))
 
+# ---- ct.Tiled: host-level broadcast and mapreduce (src/broadcast.jl, src/mapreduce.jl) -------------------------
+# `Tiled(A) .= f.(Tiled(B), ...)` flattens the Broadcasted tree into a postfix program that the library evaluates in one
+# kernel; `sum(Tiled(A); dims)`, `prod`, `maximum`, `minimum` and `mapreduce(f, op, Tiled(A); dims)` go to
+# ctb_tiled_mapreduce.  Arrays of up to three dimensions, Float32 or Float16.
+import Base.Broadcast: BroadcastStyle, Broadcasted
+
+struct Tiled{A<:CuArray}
+    parent::A
+end
+Base.parent(t::Tiled) = t.parent
+Base.size(t::Tiled) = size(t.parent)
+Base.axes(t::Tiled) = axes(t.parent)
+Base.ndims(::Type{<:Tiled{A}}) where {A} = ndims(A)
+Base.eltype(::Type{<:Tiled{A}}) where {A} = eltype(A)
+Base.Broadcast.broadcastable(t::Tiled) = t
+
+struct TiledStyle{N} <: BroadcastStyle end
+TiledStyle{M}(::Val{N}) where {N,M} = TiledStyle{N}()
+BroadcastStyle(::Type{<:Tiled{A}}) where {A} = TiledStyle{ndims(A)}()
+BroadcastStyle(::TiledStyle{N}, ::Base.Broadcast.DefaultArrayStyle{M}) where {N,M} = TiledStyle{max(N, M)}()
+BroadcastStyle(::TiledStyle{N}, ::TiledStyle{M}) where {N,M} = TiledStyle{max(N, M)}()
+
+const TILED_UNARY = Dict{Any,Cint}(identity => 16, (-) => 17, abs => 18, sqrt => 19, exp => 20, exp2 => 21, log => 22,
+                                   log2 => 23, sin => 24, cos => 25, tanh => 26, inv => 27, abs2 => 28)
+const TILED_BINARY = Dict{Any,Cint}((+) => 64, (-) => 65, (*) => 66, (/) => 67, max => 68, min => 69, (^) => 70)
+
+function tiled_compile!(prog::Vector{Int32}, inputs::Vector{Any}, consts::Vector{Float32}, x)
+    if x isa Tiled
+        i = findfirst(a -> a === parent(x), inputs)
+        i === nothing && (push!(inputs, parent(x)); i = length(inputs))
+        append!(prog, (0, i - 1))
+    elseif x isa Number
+        v = Float32(x)
+        i = findfirst(==(v), consts)
+        i === nothing && (push!(consts, v); i = length(consts))
+        append!(prog, (1, i - 1))
+    elseif x isa Base.RefValue
+        tiled_compile!(prog, inputs, consts, x[])
+    elseif x isa Broadcasted
+        foreach(a -> tiled_compile!(prog, inputs, consts, a), x.args)
+        table = length(x.args) == 1 ? TILED_UNARY : TILED_BINARY
+        haskey(table, x.f) || throw(ArgumentError("Tiled broadcast: no device code for $(x.f) with $(length(x.args)) argument(s)"))
+        append!(prog, (table[x.f], 0))
+    elseif x isa AbstractArray
+        throw(ArgumentError("Tiled broadcast: host-side array leaf of type $(typeof(x))"))
+    else
+        throw(TypeError(:Tiled, "broadcast leaf", Union{Tiled,Number}, x))
+    end
+end
+
+shape3(a) = Int64[size(a, 1), size(a, 2), size(a, 3)]
+
+function tiled_broadcast!(dest::CuArray{T}, bc) where {T}
+    ndims(dest) <= 3 || throw(ArgumentError("Tiled: at most three dimensions"))
+    axes(dest) == axes(bc) || all(d -> size(dest, d) == get(map(length, axes(bc)), d, 1) || get(map(length, axes(bc)), d, 1) == 1, 1:3) ||
+        throw(DimensionMismatch("destination $(size(dest)) and broadcast expression $(map(length, axes(bc)))"))
+    isempty(dest) && return dest
+    prog, inputs, consts = Int32[], Any[], Float32[]
+    tiled_compile!(prog, inputs, consts, bc)
+    strides = Int64[]
+    for a in inputs
+        eltype(a) == T || throw(ArgumentError("Tiled: operands and destination must share one element type"))
+        run = 1
+        for d in 1:3
+            push!(strides, size(a, d) == 1 ? 0 : run)
+            run *= size(a, d)
+        end
+    end
+    check(ccall((:ctb_tiled_broadcast, LIB), Cint,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Int64}, Ptr{Ptr{Cvoid}}, Ptr{Int64}, Cint, Ptr{Int32}, Cint, Ptr{Float32}, Cint, Cint),
+        context(), stream(), dptr(dest), shape3(dest), Ptr{Cvoid}[dptr(a) for a in inputs], strides, length(inputs), prog,
+        length(prog) ÷ 2, consts, length(consts), dtype(T)))
+    return dest
+end
+
+Base.Broadcast.materialize!(dest::Tiled, bc::Broadcasted) = tiled_broadcast!(parent(dest), bc)
+Base.Broadcast.materialize!(dest::Tiled, x::Number) = tiled_broadcast!(parent(dest), Broadcasted(identity, (x,)))
+function Base.copy(bc::Broadcasted{TiledStyle{N}}) where {N}
+    find(t::Tiled) = parent(t)
+    find(x) = nothing
+    find(b::Broadcasted) = (for a in b.args; r = find(a); r === nothing || return r; end; nothing)
+    arr = find(bc)
+    arr === nothing && error("tiled broadcast requires at least one Tiled() argument")
+    return tiled_broadcast!(similar(arr, eltype(arr), axes(bc)), bc)
+end
+
+function tiled_mapreduce(f, op, t::Tiled; dims=:)
+    A = parent(t)
+    T = eltype(A)
+    ds = dims === Colon() ? (1:ndims(A)) : dims
+    mask = 0
+    for d in ds
+        d isa Integer || throw(ArgumentError("dims must be integers"))
+        d >= 1 || throw(ArgumentError("reduced dimension(s) must be >= 1"))
+        d <= ndims(A) && (mask |= 1 << (d - 1))
+    end
+    R = similar(A, T, ntuple(d -> (mask >> (d - 1)) & 1 == 1 ? 1 : size(A, d), ndims(A)))
+    haskey(TILED_UNARY, f) || throw(ArgumentError("Tiled mapreduce: no device code for $f"))
+    code = op === (+) || op === Base.add_sum ? 64 : op === (*) || op === Base.mul_prod ? 66 : op === max ? 68 : op === min ? 69 :
+           throw(ArgumentError("Tiled mapreduce: the reduction must be +, *, max or min"))
+    check(ccall((:ctb_tiled_mapreduce, LIB), Cint,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Int64}, Cint, Cint, Cint, Cint),
+        context(), stream(), dptr(R), dptr(A), shape3(A), mask, TILED_UNARY[f], code, dtype(T)))
+    return dims === Colon() ? Array(R)[1] : R
+end
+Base.mapreduce(f, op, t::Tiled; dims=:) = tiled_mapreduce(f, op, t; dims)
+Base.sum(t::Tiled; dims=:) = tiled_mapreduce(identity, +, t; dims)
+Base.prod(t::Tiled; dims=:) = tiled_mapreduce(identity, *, t; dims)
+Base.maximum(t::Tiled; dims=:) = tiled_mapreduce(identity, max, t; dims)
+Base.minimum(t::Tiled; dims=:) = tiled_mapreduce(identity, min, t; dims)
+
 end # module

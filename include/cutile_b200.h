@@ -120,6 +120,33 @@ int ctb_transpose(ctb_ctx* ctx, void* stream, const void* x, void* y, int64_t m,
 int ctb_fft(ctb_ctx* ctx, void* stream, const void* x, void* y, const void* W0, const void* W1, const void* W2, const void* T0,
             const void* T1, int64_t N, int F0, int F1, int F2, int64_t batch, int BS, int D);
 
+/* ---- Host-level array operations (ct.Tiled) ---------------------------------- */
+/* ct.Tiled(C) .= f.(ct.Tiled(A), ...)                 src/broadcast.jl:19-23,92-165 (one fused kernel per expression)
+ * sum / prod / maximum / minimum / mapreduce(f, op, ct.Tiled(A); dims)     src/mapreduce.jl:66-203
+ * Arrays have up to three dimensions (shape[3], unused trailing extents = 1), column-major and dense; f32 or f16,
+ * arithmetic in f32.  The broadcast expression is a postfix program of (code, argument) pairs evaluated per element
+ * on a stack of at most four values: CTB_TILED_INPUT pushes inputs[argument] (its three strides in elements, 0 along
+ * a dimension where the operand has extent 1 and is expanded), CTB_TILED_CONST pushes constants[argument], a unary
+ * code replaces the top, a binary code replaces the two top values (second-from-top OP top).  The program must leave
+ * exactly one value.  Empty arrays launch nothing. */
+enum {
+  CTB_TILED_INPUT = 0, CTB_TILED_CONST = 1,
+  CTB_TILED_IDENTITY = 16, CTB_TILED_NEG, CTB_TILED_ABS, CTB_TILED_SQRT, CTB_TILED_EXP, CTB_TILED_EXP2, CTB_TILED_LOG,
+  CTB_TILED_LOG2, CTB_TILED_SIN, CTB_TILED_COS, CTB_TILED_TANH, CTB_TILED_INV, CTB_TILED_ABS2,
+  CTB_TILED_ADD = 64, CTB_TILED_SUB, CTB_TILED_MUL, CTB_TILED_DIV, CTB_TILED_MAX, CTB_TILED_MIN, CTB_TILED_POW
+};
+#define CTB_TILED_MAX_OPS 32
+#define CTB_TILED_MAX_INPUTS 4
+#define CTB_TILED_MAX_CONSTS 8
+int ctb_tiled_broadcast(ctb_ctx* ctx, void* stream, void* dest, const int64_t* shape, const void* const* inputs,
+                        const int64_t* input_strides, int n_inputs, const int32_t* program, int n_ops, const float* constants,
+                        int n_constants, int dtype);
+/* dest = reduction with `op` (CTB_TILED_ADD, _MUL, _MAX or _MIN) of f(src) (a unary code, CTB_TILED_IDENTITY for none)
+ * over the dimensions whose bit is set in reduce_mask (bit 0 = first dimension); dest is dense with extent 1 along
+ * the reduced dimensions.  Fixed summation order (bitwise repeatable); an empty reduction gives the neutral element. */
+int ctb_tiled_mapreduce(ctb_ctx* ctx, void* stream, void* dest, const void* src, const int64_t* shape, int reduce_mask, int f,
+                        int op, int dtype);
+
 /* ---- LayerNorm ---------------------------------------------------------- */
 /* layer_norm_fwd(X, W, B, Y, Mean, Rstd, eps, TILE_N)   examples/layernorm.jl:27-68
  * X, Y (N, M) f32; W, B (N); Mean, Rstd (M). */

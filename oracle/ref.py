@@ -285,6 +285,42 @@ def fft(x):
     return np.fft.fft(np.asarray(x, dtype=np.complex128), axis=-1)
 
 
+# ---------------------------------------------------------------------- ct.Tiled host operations
+TILED_UNARY = {"identity": lambda x: x, "neg": lambda x: -x, "abs": np.abs, "sqrt": np.sqrt, "exp": np.exp, "exp2": np.exp2,
+               "log": np.log, "log2": np.log2, "sin": np.sin, "cos": np.cos, "tanh": np.tanh, "inv": lambda x: 1.0 / x,
+               "abs2": lambda x: x * x}
+TILED_BINARY = {"add": np.add, "sub": np.subtract, "mul": np.multiply, "div": np.divide, "max": np.maximum,
+                "min": np.minimum, "pow": np.power}
+
+
+def tiled_broadcast(expr, dtype=np.float64):
+    """Value of a broadcast expression tree (``src/broadcast.jl:19-23``: ``ct.Tiled(C) .= f.(args...)`` means the plain
+    Julia broadcast of the same expression).  expr: a numpy array, a Python scalar, or a tuple (name, arg) /
+    (name, lhs, rhs).  numpy arrays hold the Julia arrays with the dimensions reversed, so numpy's alignment of
+    TRAILING dimensions is Julia's alignment of LEADING dimensions: plain numpy broadcasting gives Julia's result."""
+    if isinstance(expr, tuple):
+        if len(expr) == 2:
+            return TILED_UNARY[expr[0]](tiled_broadcast(expr[1], dtype))
+        return TILED_BINARY[expr[0]](tiled_broadcast(expr[1], dtype), tiled_broadcast(expr[2], dtype))
+    return np.asarray(expr, dtype=dtype)
+
+
+def tiled_mapreduce(f, op, x, julia_dims, dtype=np.float64):
+    """``mapreduce(f, op, ct.Tiled(A); dims)`` (``src/mapreduce.jl:66-203``; sum / prod / maximum / minimum are the
+    cases f = identity).  x: numpy array whose axes are the Julia dimensions reversed; julia_dims: 1-based Julia
+    dimensions to reduce (dimensions beyond ndims are ignored like in Julia).  Keeps the reduced dimensions with
+    extent 1."""
+    y = TILED_UNARY[f](np.asarray(x, dtype=dtype))
+    axes = tuple(x.ndim - d for d in julia_dims if 1 <= d <= x.ndim)
+    red = {"add": np.sum, "mul": np.prod, "max": np.max, "min": np.min}[op]
+    if not axes:
+        return y
+    if op in ("max", "min") and any(y.shape[a] == 0 for a in axes):
+        shape = [1 if i in axes else n for i, n in enumerate(y.shape)]
+        return np.full(shape, -np.inf if op == "max" else np.inf, dtype=dtype)
+    return red(y, axis=axes, keepdims=True)
+
+
 def rel_fro(out, ref):
     """||out-ref||_F / ||ref||_F, the norm-wise measure Julia's ``isapprox`` uses
     on arrays (``examples/matmul.jl:100``)."""
