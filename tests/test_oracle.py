@@ -142,3 +142,19 @@ def test_fft_three_stage_restatement_is_the_dft(batch, factors):
     for t in tabs:
         assert np.allclose(np.hypot(t[..., 0], t[..., 1]), 1.0, atol=1e-6)
         assert np.array_equal(t[0, :, 0], np.ones(t.shape[1], np.float32)) and not t[0, :, 1].any()
+
+
+def test_tiled_restatements_follow_julia_dimension_order():
+    """numpy arrays hold the Julia arrays with the dimensions reversed: Julia dims=1 is numpy's LAST axis, and Julia's
+    broadcast of A(N) with B(N, M) is numpy's broadcast of a[N] with b[M, N]."""
+    a = np.arange(24, dtype=np.float64).reshape(2, 3, 4)          # Julia (4, 3, 2)
+    r = ref.tiled_mapreduce("identity", "add", a, (1,))
+    assert r.shape == (2, 3, 1) and np.array_equal(r[..., 0], a.sum(axis=2))
+    r = ref.tiled_mapreduce("abs2", "add", a, (1, 3))
+    assert r.shape == (1, 3, 1) and np.array_equal(r[0, :, 0], (a * a).sum(axis=(0, 2)))
+    assert np.array_equal(ref.tiled_mapreduce("identity", "max", a, (2, 7)), a.max(axis=1, keepdims=True))  # dims > ndims ignored
+    assert np.array_equal(ref.tiled_mapreduce("identity", "mul", a, ()), a)
+    v, m = np.arange(4.0), np.ones((3, 4))
+    out = ref.tiled_broadcast(("add", v, ("mul", m, ("sin", v))))
+    want = np.array([[v[j] + np.sin(v[j]) for j in range(4)] for _ in range(3)])
+    assert out.shape == (3, 4) and np.allclose(out, want, rtol=0, atol=1e-15)
