@@ -24,6 +24,8 @@
 #include <cooperative_groups.h>
 #include <math.h>
 
+#include <type_traits>
+
 #include "ctx.h"
 #include "ptx.cuh"
 
@@ -44,10 +46,10 @@ namespace {
 // coalesced 16-byte access; W_r (64 KB at 32 experts x 1024) stays in L1/L2.
 constexpr int kRouterEPL = 256 / 32;
 // Top-k selection and gate weights of one token from its logits (lane l holds experts l, l+32, ...).
-__device__ __forceinline__ void route_one(float (&mine)[kRouterEPL], int t, int* __restrict__ ids,
+template <int EPL>  // experts per lane: E <= 32 * EPL
+__device__ __forceinline__ void route_one(float (&mine)[EPL], int t, int* __restrict__ ids,
                                           __half* __restrict__ gates, float* __restrict__ logits_out, int T, int E,
                                           int topk, int lane) {
-  constexpr int EPL = kRouterEPL;
   if (logits_out) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
@@ -186,15 +188,42 @@ __global__ void __launch_bounds__(kRouterThreads)
               for (int u = 0; u < TT; ++u) acc[u][e] = fmaf(xf[u][j], wf[j], acc[u][e]);
           }
         }
+        // The 32 partial sums of each of the TT * TE logits meet in the butterfly v += v[lane ^ o], o = 16, 8, 4, 2, 1.
+        // Every lane of a pair computes the same sum (a + b = b + a), so at each level a lane keeps half of its
+        // logits and hands the other half to its partner: the same additions in the same order for the logit a
+        // lane ends up holding, a quarter of the shuffles.
+        constexpr int NV = TT * TE;
+        float v[NV];
 #pragma unroll
         for (int u = 0; u < TT; ++u)
 #pragma unroll
-          for (int e = 0; e < TE; ++e) {
-            float v = acc[u][e];
+          for (int e = 0; e < TE; ++e) v[u * TE + e] = acc[u][e];
+        int held = 0;  // index of the logit this lane holds at the end
+        int cnt = NV;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && e0 + e < ge) sl[(size_t)(wt * TT + u) * E + g0 + e0 + e] = v;
+        for (int o = 16; o > 0; o >>= 1) {
+          if (cnt > 1) {
+            const int half = cnt / 2;
+            const bool upper = (lane & o) != 0;
+#pragma unroll
+            for (int j = 0; j < NV / 2; ++j) {
+              if (j < half) {
+                const float send = upper ? v[j] : v[j + half];
+                const float keep = upper ? v[j + half] : v[j];
+                v[j] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+              }
+            }
+            if (upper) held += half;
+            cnt = half;
+          } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
           }
+        }
+        static_assert(NV <= 16, "the last butterfly level must be a plain exchange");
+        {
+          const int u = held / TE, e = held - u * TE;
+          if ((lane & ((32 / NV) - 1)) == 0 && e0 + e < ge) sl[(size_t)(wt * TT + u) * E + g0 + e0 + e] = v[0];
+        }
       }
     }
     __syncthreads();
@@ -202,10 +231,17 @@ __global__ void __launch_bounds__(kRouterThreads)
     for (int tl = warp; tl < G; tl += kRouterWarps) {
       const int t = tbase + tl;
       if (t >= T) break;
-      float lg[EPL];
+      auto route = [&](auto epl) {  // as few experts per lane as E needs: the selection loops run over all of them
+        constexpr int N = decltype(epl)::value;
+        float lg[N];
 #pragma unroll
-      for (int i = 0; i < EPL; ++i) lg[i] = lane + 32 * i < E ? sl[(size_t)tl * E + lane + 32 * i] : -INFINITY;
-      route_one(lg, t, ids, gates, logits_out, T, E, topk, lane);
+        for (int i = 0; i < N; ++i) lg[i] = lane + 32 * i < E ? sl[(size_t)tl * E + lane + 32 * i] : -INFINITY;
+        route_one<N>(lg, t, ids, gates, logits_out, T, E, topk, lane);
+      };
+      if (E <= 32) route(std::integral_constant<int, 1>{});
+      else if (E <= 64) route(std::integral_constant<int, 2>{});
+      else if (E <= 128) route(std::integral_constant<int, 4>{});
+      else route(std::integral_constant<int, EPL>{});
     }
   }
   cp_async_wait_all();  // a CTA without any group still has its copy of W_r in flight
