@@ -2,10 +2,12 @@
 // broadcast expression fused into one kernel) and mapreduce (src/mapreduce.jl: sum / prod / maximum / minimum / a
 // mapped reduction over any set of dimensions).  The reference compiles the Julia expression; a prebuilt library
 // cannot, so the expression arrives as a short postfix program (push input, push constant, unary function, binary
-// operator) that every thread evaluates on a register stack for four neighbouring elements at a time: still one pass
-// over memory, one kernel, whatever the expression.  Arrays have up to three dimensions, column-major, first
-// dimension contiguous; an operand with extent 1 along a dimension is expanded along it (stride 0).  Arithmetic is
-// f32 whatever the element type.  Both are bound by HBM bandwidth: bytes of the operands read once plus the result.
+// operator).  The host turns it into instructions of an accumulator machine (compile_program below: a leaf operand
+// of a binary operator is read in place, only a binary operator between two computed values touches the stack),
+// and every thread runs those instructions on registers for four or eight elements at a time: still one pass over
+// memory, one kernel, whatever the expression.  Arrays have up to three dimensions, column-major, first dimension
+// contiguous; an operand with extent 1 along a dimension is expanded along it (stride 0).  Arithmetic is f32
+// whatever the element type.  Both are bound by HBM bandwidth: bytes of the operands read once plus the result.
 #include <cuda_fp16.h>
 #include <math.h>
 
@@ -22,10 +24,21 @@ constexpr int kMaxInputs = CTB_TILED_MAX_INPUTS;
 constexpr int kMaxConsts = CTB_TILED_MAX_CONSTS;
 constexpr int kStack = 4;
 
+// One instruction word of the accumulator machine.  The accumulator A is the top of a four-entry register stack.
+//   kind LOAD : push; A = operand
+//   kind UNARY: A = code(A)
+//   kind BIN  : A = A code operand, or operand code A when the REV bit is set; an operand from the stack is popped
+// operand source: the stack entry below A (BIN only), inputs[arg] or constants[arg].
+enum : unsigned { K_LOAD = 0, K_UNARY = 1, K_BIN = 2 };
+enum : unsigned { SRC_STACK = 0, SRC_INPUT = 1, SRC_CONST = 2 };
+constexpr unsigned kRevBit = 1u << 4;
+__host__ __device__ constexpr unsigned make_ins(unsigned kind, unsigned src, bool rev, unsigned code, unsigned arg) {
+  return kind | (src << 2) | (rev ? kRevBit : 0u) | (code << 8) | (arg << 16);
+}
+
 struct Program {
-  int n_ops;
-  short op[kMaxOps];
-  short arg[kMaxOps];
+  int n_ins;
+  unsigned ins[kMaxOps];
   float consts[kMaxConsts];
 };
 
@@ -33,6 +46,90 @@ struct Operands {
   const void* ptr[kMaxInputs];
   long long stride[kMaxInputs][3];
 };
+
+// ---- postfix program -> accumulator-machine instructions (host) ---------------------------------------------------
+struct Node {
+  int op, arg, left, right;  // left/right: node indices, -1 for none
+  int need;                  // stack entries the subtree needs when it is evaluated into A
+};
+inline bool is_leaf(const Node& n) { return n.op == CTB_TILED_INPUT || n.op == CTB_TILED_CONST; }
+inline unsigned leaf_src(const Node& n) { return n.op == CTB_TILED_INPUT ? SRC_INPUT : SRC_CONST; }
+
+struct Compiler {
+  Node nodes[kMaxOps];
+  int n_nodes = 0;
+  Program* out = nullptr;
+  void put(unsigned w) { out->ins[out->n_ins++] = w; }
+  void emit(int i) {
+    const Node& n = nodes[i];
+    if (is_leaf(n)) {
+      put(make_ins(K_LOAD, leaf_src(n), false, 0, (unsigned)n.arg));
+    } else if (n.right < 0) {
+      emit(n.left);
+      if (n.op != CTB_TILED_IDENTITY) put(make_ins(K_UNARY, 0, false, (unsigned)n.op, 0));
+    } else {
+      const Node &l = nodes[n.left], &r = nodes[n.right];
+      const bool commutes = n.op == CTB_TILED_ADD || n.op == CTB_TILED_MUL;  // a op b == b op a bit for bit
+      if (is_leaf(r)) {         // A = left; A = A op leaf
+        emit(n.left);
+        put(make_ins(K_BIN, leaf_src(r), false, (unsigned)n.op, (unsigned)r.arg));
+      } else if (is_leaf(l)) {  // A = right; A = leaf op A
+        emit(n.right);
+        put(make_ins(K_BIN, leaf_src(l), !commutes, (unsigned)n.op, (unsigned)l.arg));
+      } else if (l.need > r.need) {  // the deeper side first: A = right, below it left; A = below op A
+        emit(n.left);
+        emit(n.right);
+        put(make_ins(K_BIN, SRC_STACK, !commutes, (unsigned)n.op, 0));
+      } else {                  // A = left, below it right; A = A op below
+        emit(n.right);
+        emit(n.left);
+        put(make_ins(K_BIN, SRC_STACK, false, (unsigned)n.op, 0));
+      }
+    }
+  }
+};
+
+// Returns 0, or a negative number -(k+1) naming the offending postfix operation k with *why set; -1000 when the
+// expression needs more than kStack live values.  *need: the stack entries the instructions use (1 = the accumulator
+// alone).
+int compile_program(const int32_t* program, int n_ops, int n_inputs, int n_constants, Program* out, const char** why,
+                    int* need = nullptr) {
+  Compiler c;
+  c.out = out;
+  out->n_ins = 0;
+  int stack[kMaxOps], depth = 0;
+  for (int k = 0; k < n_ops; ++k) {
+    const int op = program[2 * k], arg = program[2 * k + 1];
+    Node n = {op, arg, -1, -1, 1};
+    if (op == CTB_TILED_INPUT) {
+      if (arg < 0 || arg >= n_inputs) { *why = "names an input that was not given"; return -(k + 1); }
+    } else if (op == CTB_TILED_CONST) {
+      if (arg < 0 || arg >= n_constants) { *why = "names a constant that was not given"; return -(k + 1); }
+    } else if (op >= CTB_TILED_IDENTITY && op <= CTB_TILED_ABS2) {
+      if (depth < 1) { *why = "finds an empty stack"; return -(k + 1); }
+      n.left = stack[--depth];
+      n.need = c.nodes[n.left].need;
+    } else if (op >= CTB_TILED_ADD && op <= CTB_TILED_POW) {
+      if (depth < 2) { *why = "needs two values on the stack"; return -(k + 1); }
+      n.right = stack[--depth];
+      n.left = stack[--depth];
+      const Node &l = c.nodes[n.left], &r = c.nodes[n.right];
+      if (is_leaf(r)) n.need = l.need;
+      else if (is_leaf(l)) n.need = r.need;
+      else n.need = std::max(std::max(l.need, r.need), std::min(l.need, r.need) + 1);
+    } else {
+      *why = "is not an operation code";
+      return -(k + 1);
+    }
+    c.nodes[c.n_nodes] = n;
+    stack[depth++] = c.n_nodes++;
+  }
+  if (depth != 1) { *why = "the program must leave exactly one value"; return -(n_ops + 1); }
+  if (c.nodes[stack[0]].need > kStack) return -1000;
+  if (need) *need = c.nodes[stack[0]].need;
+  c.emit(stack[0]);
+  return 0;
+}
 
 __device__ __forceinline__ float unary(int op, float x) {
   switch (op) {
@@ -74,105 +171,90 @@ __device__ __forceinline__ void store1(void* p, long long i, float v) {
   else static_cast<__half*>(p)[i] = __float2half_rn(v);
 }
 
-// V = 8 or 4: that many neighbouring elements of the first dimension per thread and trip (the host checks that every
-// operand is either contiguous or expanded along it and that rows start on 16-byte boundaries; the cost of decoding
-// an operation is shared by the V elements); V = 1: anything else.
+// V = 4: four neighbouring elements of the first dimension per group (the host checks that every operand is either
+// contiguous or expanded along it and that rows start on 16-byte boundaries); V = 1: anything else.  G groups per
+// thread and trip, a whole grid apart (neighbouring threads touch neighbouring groups): G loads per operand are in
+// flight per thread, which is what hides the latency of HBM, and the cost of decoding an instruction is shared by
+// V * G elements.  NIN: operands held in registers (1, 2 or 4); DEEP: the program has an operator between two
+// computed values, so the three stack entries below the accumulator exist.  Registers not spent on absent operands
+// and on an unused stack go to more groups per thread.
 // DENSE: every operand either has the destination's shape (dense) or is a single element: one linear index, no
-// division.  Otherwise the element index is split into its three coordinates (32-bit arithmetic; the host checks
-// that the element count fits).  The operands are read once per element into registers; pushes are register moves.
-template <typename T, int V, bool DENSE>
+// division.  Otherwise the group index is split into its three coordinates (32-bit arithmetic; the host checks
+// that the element count fits).  The operands are read once per element into registers.
+template <typename T, int V, int G, bool DENSE, int NIN, bool DEEP>
 __global__ void __launch_bounds__(256)
     tiled_broadcast_kernel(void* __restrict__ dest, const Operands in, const Program prog, int n_inputs, long long d0,
                            long long d1, long long d2) {
+  constexpr int E = V * G;
+  constexpr int ES = DEEP ? E : 1;  // extent of the stack entries below the accumulator
   const long long n0 = d0 / V, total = n0 * d1 * d2;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    long long o;          // element offset in the destination
-    long long off[kMaxInputs];
-    long long st0[kMaxInputs];
-    if (DENSE) {
-      o = i * V;
+  const long long grid_stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += grid_stride * G) {
+    long long o[G];  // element offset of each group in the destination
+    bool live[G];
+    float x[NIN][E];
 #pragma unroll
-      for (int a = 0; a < kMaxInputs; ++a) {
-        st0[a] = in.stride[a][0];
-        off[a] = st0[a] ? o : 0;
-      }
-    } else {
-      const unsigned u = (unsigned)i, un0 = (unsigned)n0, ud1 = (unsigned)d1;
-      const unsigned r = u / un0, i0 = (u - r * un0) * V, i2 = r / ud1, i1 = r - i2 * ud1;
-      o = i0 + d0 * (i1 + d1 * (long long)i2);
+    for (int g = 0; g < G; ++g) {
+      const long long ig = i + g * grid_stride;
+      live[g] = ig < total;
+      long long off[NIN];
+      long long st0[NIN];
+      if (DENSE) {
+        o[g] = ig * V;
 #pragma unroll
-      for (int a = 0; a < kMaxInputs; ++a) {
-        st0[a] = in.stride[a][0];
-        off[a] = i0 * st0[a] + i1 * in.stride[a][1] + i2 * in.stride[a][2];
-      }
-    }
-    float x[kMaxInputs][V];
-#pragma unroll
-    for (int a = 0; a < kMaxInputs; ++a) {
-      if (a < n_inputs) {
-        if (V >= 4 && st0[a] == 1) {
-#pragma unroll
-          for (int g = 0; g < V / 4; ++g) {
-            if constexpr (sizeof(T) == 4) {
-              const float4 q = __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(in.ptr[a]) + off[a]) + g);
-              x[a][(4 * g) % V] = q.x; x[a][(4 * g + 1) % V] = q.y; x[a][(4 * g + 2) % V] = q.z; x[a][(4 * g + 3) % V] = q.w;
-            } else {
-              const uint2 q = __ldcs(reinterpret_cast<const uint2*>(static_cast<const __half*>(in.ptr[a]) + off[a]) + g);
-              const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
-              const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
-              x[a][(4 * g) % V] = lo.x; x[a][(4 * g + 1) % V] = lo.y; x[a][(4 * g + 2) % V] = hi.x; x[a][(4 * g + 3) % V] = hi.y;
-            }
-          }
-        } else {
-#pragma unroll
-          for (int v = 0; v < V; ++v) x[a][v] = load1<T>(in.ptr[a], off[a] + v * st0[a]);
+        for (int a = 0; a < NIN; ++a) {
+          st0[a] = in.stride[a][0];
+          off[a] = st0[a] ? o[g] : 0;
         }
       } else {
+        const unsigned u = (unsigned)ig, un0 = (unsigned)n0, ud1 = (unsigned)d1;
+        const unsigned r = u / un0, i0 = (u - r * un0) * V, i2 = r / ud1, i1 = r - i2 * ud1;
+        o[g] = i0 + d0 * (i1 + d1 * (long long)i2);
 #pragma unroll
-        for (int v = 0; v < V; ++v) x[a][v] = 0.f;
+        for (int a = 0; a < NIN; ++a) {
+          st0[a] = in.stride[a][0];
+          off[a] = i0 * st0[a] + i1 * in.stride[a][1] + i2 * in.stride[a][2];
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        float* xa = &x[a][g * V];
+        if (a < n_inputs && live[g]) {
+          if (V == 4 && st0[a] == 1) {
+            if constexpr (sizeof(T) == 4) {
+              const float4 q = __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(in.ptr[a]) + off[a]));
+              xa[0] = q.x; xa[1 % V] = q.y; xa[2 % V] = q.z; xa[3 % V] = q.w;
+            } else {
+              const uint2 q = __ldcs(reinterpret_cast<const uint2*>(static_cast<const __half*>(in.ptr[a]) + off[a]));
+              const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+              const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
+              xa[0] = lo.x; xa[1 % V] = lo.y; xa[2 % V] = hi.x; xa[3 % V] = hi.y;
+            }
+          } else {
+#pragma unroll
+            for (int v = 0; v < V; ++v) xa[v] = load1<T>(in.ptr[a], off[a] + v * st0[a]);
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < V; ++v) xa[v] = 0.f;
+        }
       }
     }
-    float s0[V], s1[V], s2[V], s3[V];  // the stack, top first
+    float s0[E], s1[ES], s2[ES], s3[ES];  // the stack, top (the accumulator) first
 #pragma unroll
-    for (int v = 0; v < V; ++v) s0[v] = s1[v] = s2[v] = s3[v] = 0.f;
-    for (int k = 0; k < prog.n_ops; ++k) {
-      const int op = prog.op[k], arg = prog.arg[k];
-      if (op <= CTB_TILED_CONST) {
+    for (int v = 0; v < E; ++v) s0[v] = 0.f;
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-          s3[v] = s2[v]; s2[v] = s1[v]; s1[v] = s0[v];
-        }
-        if (op == CTB_TILED_CONST) {
-          const float c = prog.consts[arg & (kMaxConsts - 1)];
-#pragma unroll
-          for (int v = 0; v < V; ++v) s0[v] = c;
-        } else {
-          switch (arg) {
-            case 0:
-#pragma unroll
-              for (int v = 0; v < V; ++v) s0[v] = x[0][v];
-              break;
-            case 1:
-#pragma unroll
-              for (int v = 0; v < V; ++v) s0[v] = x[1][v];
-              break;
-            case 2:
-#pragma unroll
-              for (int v = 0; v < V; ++v) s0[v] = x[2][v];
-              break;
-            default:
-#pragma unroll
-              for (int v = 0; v < V; ++v) s0[v] = x[3][v];
-              break;
-          }
-        }
-      } else if (op < CTB_TILED_ADD) {
-        // one dispatch per operation and thread, not per element
+    for (int v = 0; v < ES; ++v) s1[v] = s2[v] = s3[v] = 0.f;
+    for (int k = 0; k < prog.n_ins; ++k) {
+      const unsigned w = prog.ins[k];
+      const unsigned kind = w & 3u, src = (w >> 2) & 3u, code = (w >> 8) & 0xffu, arg = w >> 16;
+      if (kind == K_UNARY) {
+        // one dispatch per instruction and thread, not per element
 #define CTB_U(CODE, EXPR)               \
   case CODE:                            \
-    _Pragma("unroll") for (int v = 0; v < V; ++v) { const float t = s0[v]; s0[v] = (EXPR); } \
+    _Pragma("unroll") for (int v = 0; v < E; ++v) { const float t = s0[v]; s0[v] = (EXPR); } \
     break;
-        switch (op) {
+        switch (code) {
           CTB_U(CTB_TILED_NEG, -t)
           CTB_U(CTB_TILED_ABS, fabsf(t))
           CTB_U(CTB_TILED_SQRT, sqrtf(t))
@@ -185,51 +267,294 @@ __global__ void __launch_bounds__(256)
           CTB_U(CTB_TILED_TANH, tanhf(t))
           CTB_U(CTB_TILED_INV, 1.0f / t)
           CTB_U(CTB_TILED_ABS2, t * t)
-          default: break;  // CTB_TILED_IDENTITY
+          default: break;
         }
 #undef CTB_U
-      } else {
+        continue;
+      }
+      float t[E];  // the operand
+      if (src == SRC_INPUT) {
+        const unsigned which = NIN == 1 ? 0u : NIN == 2 ? (arg & 1u) : (arg & 3u);
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) {
+          if (which == (unsigned)a) {
+#pragma unroll
+            for (int v = 0; v < E; ++v) t[v] = x[a][v];
+          }
+        }
+      } else if (src == SRC_CONST) {
+        const float c = prog.consts[arg & (kMaxConsts - 1)];
+#pragma unroll
+        for (int v = 0; v < E; ++v) t[v] = c;
+      } else {  // the entry below the accumulator, popped (DEEP programs only)
+#pragma unroll
+        for (int v = 0; v < E; ++v) {
+          t[v] = s1[v % ES];
+          if (DEEP) { s1[v % ES] = s2[v % ES]; s2[v % ES] = s3[v % ES]; }
+        }
+      }
+      if (kind == K_LOAD) {
+#pragma unroll
+        for (int v = 0; v < E; ++v) {
+          if (DEEP) { s3[v % ES] = s2[v % ES]; s2[v % ES] = s1[v % ES]; s1[v % ES] = s0[v]; }
+          s0[v] = t[v];
+        }
+        continue;
+      }
+      if (w & kRevBit) {
+#pragma unroll
+        for (int v = 0; v < E; ++v) {
+          const float q = s0[v]; s0[v] = t[v]; t[v] = q;
+        }
+      }
 #define CTB_B(CODE, EXPR)               \
   case CODE:                            \
-    _Pragma("unroll") for (int v = 0; v < V; ++v) { const float a = s1[v], b = s0[v]; s0[v] = (EXPR); } \
+    _Pragma("unroll") for (int v = 0; v < E; ++v) { const float a = s0[v], b = t[v]; s0[v] = (EXPR); } \
     break;
-        switch (op) {
-          CTB_B(CTB_TILED_ADD, a + b)
-          CTB_B(CTB_TILED_SUB, a - b)
-          CTB_B(CTB_TILED_MUL, a * b)
-          CTB_B(CTB_TILED_DIV, a / b)
-          CTB_B(CTB_TILED_MAX, fmaxf(a, b))
-          CTB_B(CTB_TILED_MIN, fminf(a, b))
-          default:
+      switch (code) {
+        CTB_B(CTB_TILED_ADD, a + b)
+        CTB_B(CTB_TILED_SUB, a - b)
+        CTB_B(CTB_TILED_MUL, a * b)
+        CTB_B(CTB_TILED_DIV, a / b)
+        CTB_B(CTB_TILED_MAX, fmaxf(a, b))
+        CTB_B(CTB_TILED_MIN, fminf(a, b))
+        default:
 #pragma unroll
-            for (int v = 0; v < V; ++v) s0[v] = powf(s1[v], s0[v]);
-            break;
-        }
-#undef CTB_B
-#pragma unroll
-        for (int v = 0; v < V; ++v) {
-          s1[v] = s2[v];
-          s2[v] = s3[v];
-        }
+          for (int v = 0; v < E; ++v) s0[v] = powf(s0[v], t[v]);
+          break;
       }
+#undef CTB_B
     }
-    if (V >= 4) {
 #pragma unroll
-      for (int g = 0; g < V / 4; ++g) {
+    for (int g = 0; g < G; ++g) {
+      if (!live[g]) continue;
+      const float* r = &s0[g * V];
+      if (V == 4) {
         if constexpr (sizeof(T) == 4) {
-          __stcs(reinterpret_cast<float4*>(static_cast<float*>(dest) + o) + g,
-                 make_float4(s0[(4 * g) % V], s0[(4 * g + 1) % V], s0[(4 * g + 2) % V], s0[(4 * g + 3) % V]));
+          __stcs(reinterpret_cast<float4*>(static_cast<float*>(dest) + o[g]), make_float4(r[0], r[1 % V], r[2 % V], r[3 % V]));
         } else {
           uint2 q;
-          *reinterpret_cast<__half2*>(&q.x) = __floats2half2_rn(s0[(4 * g) % V], s0[(4 * g + 1) % V]);
-          *reinterpret_cast<__half2*>(&q.y) = __floats2half2_rn(s0[(4 * g + 2) % V], s0[(4 * g + 3) % V]);
-          __stcs(reinterpret_cast<uint2*>(static_cast<__half*>(dest) + o) + g, q);
+          *reinterpret_cast<__half2*>(&q.x) = __floats2half2_rn(r[0], r[1 % V]);
+          *reinterpret_cast<__half2*>(&q.y) = __floats2half2_rn(r[2 % V], r[3 % V]);
+          __stcs(reinterpret_cast<uint2*>(static_cast<__half*>(dest) + o[g]), q);
         }
+      } else {
+        store1<T>(dest, o[g], r[0]);
       }
-    } else {
-      store1<T>(dest, o, s0[0]);
     }
   }
+}
+
+// ---- the vector path: operands staged in shared memory by cp.async, two trips deep ----------------------------------
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+// 16 or 8 bytes global -> shared, asynchronous; src_bytes = 0 writes zeros and reads nothing
+template <int BYTES>
+__device__ __forceinline__ void cp_async_group(unsigned dst, const void* src, unsigned src_bytes) {
+  if constexpr (BYTES == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Every operand is contiguous along the first dimension with 16-byte aligned rows, or expanded along it (the host
+// checks).  A group is four neighbouring elements; a thread owns G groups per trip, a whole grid apart.  The
+// operands of the NEXT trip are copied global -> shared by cp.async (no registers, nothing waits on them) while the
+// instructions run on the current trip's copies, so the latency of HBM is off the critical path whatever the
+// occupancy; registers hold only the accumulator, the current operand and, for DEEP programs, the three stack
+// entries.  A thread reads only the shared memory it filled itself: no CTA barrier anywhere.
+// Shared memory: [2 buffers][n_inputs][G][256 threads] groups of 4 * sizeof(T) bytes.
+template <typename T, int G, bool DENSE, bool DEEP>
+__global__ void __launch_bounds__(256)
+    tiled_broadcast_pipe_kernel(void* __restrict__ dest, const Operands in, const Program prog, int n_inputs, long long d0,
+                                long long d1, long long d2) {
+  constexpr int V = 4, E = V * G, VB = V * (int)sizeof(T);
+  constexpr int ES = DEEP ? E : 1;
+  extern __shared__ __align__(16) unsigned char tiled_smem[];
+  const long long n0 = d0 / V, total = n0 * d1 * d2;
+  const long long grid_stride = (long long)gridDim.x * blockDim.x;
+  const unsigned tid = threadIdx.x;
+  const unsigned buf_bytes = (unsigned)n_inputs * G * 256 * VB;
+  const unsigned smem0 = smem_addr(tiled_smem) + tid * VB;
+  auto slot = [&](unsigned buf, unsigned a, unsigned g) { return smem0 + buf * buf_bytes + (a * G + g) * (256 * VB); };
+
+  // destination offset and operand offsets of group index ig
+  auto locate = [&](long long ig, long long& o, long long (&off)[kMaxInputs]) {
+    if (DENSE) {
+      o = ig * V;
+#pragma unroll
+      for (int a = 0; a < kMaxInputs; ++a) off[a] = in.stride[a][0] ? o : 0;
+    } else {
+      const unsigned u = (unsigned)ig, un0 = (unsigned)n0, ud1 = (unsigned)d1;
+      const unsigned r = u / un0, i0 = (u - r * un0) * V, i2 = r / ud1, i1 = r - i2 * ud1;
+      o = i0 + d0 * (i1 + d1 * (long long)i2);
+#pragma unroll
+      for (int a = 0; a < kMaxInputs; ++a) off[a] = i0 * in.stride[a][0] + i1 * in.stride[a][1] + i2 * in.stride[a][2];
+    }
+  };
+  auto issue = [&](long long i, unsigned buf) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const long long ig = i + g * grid_stride;
+      const bool live = ig < total;
+      long long o, off[kMaxInputs];
+      locate(live ? ig : 0, o, off);
+#pragma unroll
+      for (int a = 0; a < kMaxInputs; ++a) {
+        if (a < n_inputs) {
+          const T* src = static_cast<const T*>(in.ptr[a]) + off[a];
+          if (in.stride[a][0] == 1) {
+            cp_async_group<VB>(slot(buf, a, g), src, live ? VB : 0);
+          } else if (live) {  // expanded along the first dimension: one element, four copies
+            const T v = *src;
+            T* dst = reinterpret_cast<T*>(tiled_smem + (slot(buf, a, g) - smem_addr(tiled_smem)));
+            dst[0] = v; dst[1] = v; dst[2] = v; dst[3] = v;
+          }
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  long long i = (long long)blockIdx.x * blockDim.x + tid;
+  if (i < total) issue(i, 0);
+  for (unsigned buf = 0; i < total; i += grid_stride * G, buf ^= 1u) {
+    const long long next = i + grid_stride * G;
+    if (next < total) issue(next, buf ^ 1u);
+    else cp_async_commit();  // an empty group keeps the count below uniform
+    cp_async_wait<1>();      // everything but the newest group has landed: this trip's operands
+
+    float s0[E], s1[ES], s2[ES], s3[ES];  // the stack, top (the accumulator) first
+#pragma unroll
+    for (int v = 0; v < E; ++v) s0[v] = 0.f;
+#pragma unroll
+    for (int v = 0; v < ES; ++v) s1[v] = s2[v] = s3[v] = 0.f;
+    for (int k = 0; k < prog.n_ins; ++k) {
+      const unsigned w = prog.ins[k];
+      const unsigned kind = w & 3u, src = (w >> 2) & 3u, code = (w >> 8) & 0xffu, arg = w >> 16;
+      if (kind == K_UNARY) {
+#define CTB_U(CODE, EXPR)               \
+  case CODE:                            \
+    _Pragma("unroll") for (int v = 0; v < E; ++v) { const float t = s0[v]; s0[v] = (EXPR); } \
+    break;
+        switch (code) {
+          CTB_U(CTB_TILED_NEG, -t)
+          CTB_U(CTB_TILED_ABS, fabsf(t))
+          CTB_U(CTB_TILED_SQRT, sqrtf(t))
+          CTB_U(CTB_TILED_EXP, expf(t))
+          CTB_U(CTB_TILED_EXP2, exp2f(t))
+          CTB_U(CTB_TILED_LOG, logf(t))
+          CTB_U(CTB_TILED_LOG2, log2f(t))
+          CTB_U(CTB_TILED_SIN, sinf(t))
+          CTB_U(CTB_TILED_COS, cosf(t))
+          CTB_U(CTB_TILED_TANH, tanhf(t))
+          CTB_U(CTB_TILED_INV, 1.0f / t)
+          CTB_U(CTB_TILED_ABS2, t * t)
+          default: break;
+        }
+#undef CTB_U
+        continue;
+      }
+      float t[E];  // the operand
+      if (src == SRC_INPUT) {
+        const unsigned base = slot(buf, arg & (kMaxInputs - 1), 0);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          if constexpr (sizeof(T) == 4) {
+            float4 q;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w) : "r"(base + g * (256 * VB)));
+            t[4 * g] = q.x; t[4 * g + 1] = q.y; t[4 * g + 2] = q.z; t[4 * g + 3] = q.w;
+          } else {
+            uint2 q;
+            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(base + g * (256 * VB)));
+            const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+            const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
+            t[4 * g] = lo.x; t[4 * g + 1] = lo.y; t[4 * g + 2] = hi.x; t[4 * g + 3] = hi.y;
+          }
+        }
+      } else if (src == SRC_CONST) {
+        const float c = prog.consts[arg & (kMaxConsts - 1)];
+#pragma unroll
+        for (int v = 0; v < E; ++v) t[v] = c;
+      } else {  // the entry below the accumulator, popped (DEEP programs only)
+#pragma unroll
+        for (int v = 0; v < E; ++v) {
+          t[v] = s1[v % ES];
+          if (DEEP) { s1[v % ES] = s2[v % ES]; s2[v % ES] = s3[v % ES]; }
+        }
+      }
+      if (kind == K_LOAD) {
+#pragma unroll
+        for (int v = 0; v < E; ++v) {
+          if (DEEP) { s3[v % ES] = s2[v % ES]; s2[v % ES] = s1[v % ES]; s1[v % ES] = s0[v]; }
+          s0[v] = t[v];
+        }
+        continue;
+      }
+      if (w & kRevBit) {
+#pragma unroll
+        for (int v = 0; v < E; ++v) {
+          const float q = s0[v]; s0[v] = t[v]; t[v] = q;
+        }
+      }
+#define CTB_B(CODE, EXPR)               \
+  case CODE:                            \
+    _Pragma("unroll") for (int v = 0; v < E; ++v) { const float a = s0[v], b = t[v]; s0[v] = (EXPR); } \
+    break;
+      switch (code) {
+        CTB_B(CTB_TILED_ADD, a + b)
+        CTB_B(CTB_TILED_SUB, a - b)
+        CTB_B(CTB_TILED_MUL, a * b)
+        CTB_B(CTB_TILED_DIV, a / b)
+        CTB_B(CTB_TILED_MAX, fmaxf(a, b))
+        CTB_B(CTB_TILED_MIN, fminf(a, b))
+        default:
+#pragma unroll
+          for (int v = 0; v < E; ++v) s0[v] = powf(s0[v], t[v]);
+          break;
+      }
+#undef CTB_B
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const long long ig = i + g * grid_stride;
+      if (ig >= total) continue;
+      long long o, off[kMaxInputs];
+      locate(ig, o, off);
+      const float* r = &s0[g * V];
+      if constexpr (sizeof(T) == 4) {
+        __stcs(reinterpret_cast<float4*>(static_cast<float*>(dest) + o), make_float4(r[0], r[1], r[2], r[3]));
+      } else {
+        uint2 q;
+        *reinterpret_cast<__half2*>(&q.x) = __floats2half2_rn(r[0], r[1]);
+        *reinterpret_cast<__half2*>(&q.y) = __floats2half2_rn(r[2], r[3]);
+        __stcs(reinterpret_cast<uint2*>(static_cast<__half*>(dest) + o), q);
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
+template <typename T, int G, bool DENSE, bool DEEP>
+int launch_pipe(ctb_ctx* ctx, cudaStream_t st, void* dest, const Operands& in, const Program& prog, int n_inputs, long long d0,
+                long long d1, long long d2, long long units) {
+  auto kernel = tiled_broadcast_pipe_kernel<T, G, DENSE, DEEP>;
+  const int smem = std::max(1, n_inputs) * 2 * G * 256 * 4 * (int)sizeof(T);
+  if (smem > 48 * 1024 &&  // per device, so on every launch that needs it: a host-side table write
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return fail(CTB_CUDA_ERROR, "ctb_tiled_broadcast: shared memory attribute: %s", cudaGetErrorString(cudaGetLastError()));
+  // Several waves of CTAs, not one wave of resident ones: CTAs that all start together stay in step (all loading,
+  // then all storing) and measured 10 % slower than CTAs that start at different times.
+  const long long ctas = (units + 256ll * G - 1) / (256ll * G);
+  int per_sm = 16;
+#ifdef CTB_TILED_TUNE
+  if (const char* e = getenv("CTB_TW")) per_sm = atoi(e);
+#endif
+  const int grid = (int)std::max<long long>(1, std::min<long long>(ctas, (long long)ctx->sm_count * per_sm));
+  kernel<<<grid, 256, smem, st>>>(dest, in, prog, n_inputs, d0, d1, d2);
+  return CTB_OK;
 }
 
 // ---- mapreduce ----------------------------------------------------------------------------------------------------
@@ -371,29 +696,12 @@ int ctb_tiled_broadcast(ctb_ctx* ctx, void* stream, void* dest, const int64_t* s
   for (int k = 0; k < 3; ++k)
     if (shape[k] < 0) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: negative extent");
   Program prog;
-  prog.n_ops = n_ops;
-  int depth = 0;
-  for (int k = 0; k < n_ops; ++k) {
-    const int op = program[2 * k], arg = program[2 * k + 1];
-    if (op == CTB_TILED_INPUT) {
-      if (arg < 0 || arg >= n_inputs) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: operation %d names input %d", k, arg);
-      ++depth;
-    } else if (op == CTB_TILED_CONST) {
-      if (arg < 0 || arg >= n_constants) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: operation %d names constant %d", k, arg);
-      ++depth;
-    } else if (op >= CTB_TILED_IDENTITY && op <= CTB_TILED_ABS2) {
-      if (depth < 1) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: operation %d finds an empty stack", k);
-    } else if (op >= CTB_TILED_ADD && op <= CTB_TILED_POW) {
-      if (depth < 2) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: operation %d needs two values on the stack", k);
-      --depth;
-    } else {
-      return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: unknown operation code %d", op);
-    }
-    if (depth > kStack) return fail(CTB_UNSUPPORTED, "ctb_tiled_broadcast: the expression needs more than %d stack entries", kStack);
-    prog.op[k] = (short)op;
-    prog.arg[k] = (short)arg;
-  }
-  if (depth != 1) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: the program leaves %d values on the stack", depth);
+  const char* why = "";
+  int need = 1;
+  const int bad = compile_program(program, n_ops, n_inputs, n_constants, &prog, &why, &need);
+  if (bad == -1000)
+    return fail(CTB_UNSUPPORTED, "ctb_tiled_broadcast: the expression needs more than %d intermediate values at once", kStack);
+  if (bad) return fail(CTB_BAD_ARG, "ctb_tiled_broadcast: operation %d %s", -bad - 1, why);
   for (int k = 0; k < n_constants; ++k) prog.consts[k] = constants[k];
   const long long d0 = shape[0], d1 = shape[1], d2 = shape[2];
   if (d0 == 0 || d1 == 0 || d2 == 0) return CTB_OK;  // empty arrays: nothing to launch
@@ -422,25 +730,60 @@ int ctb_tiled_broadcast(ctb_ctx* ctx, void* stream, void* dest, const int64_t* s
     const bool single = in.stride[a][0] == 0 && (d1 == 1 || in.stride[a][1] == 0) && (d2 == 1 || in.stride[a][2] == 0);
     if (!like_dest && !single) dense = false;
   }
-  const bool vec8 = false;  // eight elements per thread measured slower than four (registers)
-  const long long units = (vec8 ? d0 / 8 : vec ? d0 / 4 : d0) * d1 * d2;
+  const long long units = (vec ? d0 / 4 : d0) * d1 * d2;
   if (!dense && units > 0x7fffffffLL) return fail(CTB_UNSUPPORTED, "ctb_tiled_broadcast: too many elements for an expanded operand");
-  const int grid = (int)std::max<long long>(1, std::min<long long>((units + 255) / 256, (long long)ctx->sm_count * 16));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define CTB_TILED_LAUNCH(T, V, D) tiled_broadcast_kernel<T, V, D><<<grid, 256, 0, st>>>(dest, in, prog, n_inputs, d0, d1, d2)
-#define CTB_TILED_PICK(T)                                  \
-  do {                                                     \
-    if (vec8) CTB_TILED_LAUNCH(T, 8, true);                \
-    else if (vec && dense) CTB_TILED_LAUNCH(T, 4, true);   \
-    else if (vec) CTB_TILED_LAUNCH(T, 4, false);           \
-    else if (dense) CTB_TILED_LAUNCH(T, 1, true);          \
-    else CTB_TILED_LAUNCH(T, 1, false);                    \
+  const bool deep = need > 1;
+  int rc = CTB_OK;
+  int tune_g = 0;
+#ifdef CTB_TILED_TUNE
+  if (const char* e = getenv("CTB_TG")) tune_g = atoi(e);
+#endif
+  // groups per thread: as many as registers (the stack of a deep program) and shared memory (the operands) allow
+#define CTB_TILED_VEC(T, D)                                                                                          \
+  do {                                                                                                               \
+    if (tune_g == 2 && !deep) rc = launch_pipe<T, 2, D, false>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units); \
+    else if (tune_g == 4 && !deep) rc = launch_pipe<T, 4, D, false>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units); \
+    else if (deep) rc = launch_pipe<T, 2, D, true>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units);            \
+    else if (n_inputs <= 3) rc = launch_pipe<T, 4, D, false>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units);  \
+    else rc = launch_pipe<T, 2, D, false>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units);                     \
+  } while (0)
+#define CTB_TILED_SCALAR(T, D)                                                                                       \
+  do {                                                                                                               \
+    const int grid = (int)std::max<long long>(1, std::min<long long>((units + 255) / 256, (long long)ctx->sm_count * 16)); \
+    tiled_broadcast_kernel<T, 1, 1, D, kMaxInputs, true><<<grid, 256, 0, st>>>(dest, in, prog, n_inputs, d0, d1, d2); \
+  } while (0)
+#define CTB_TILED_PICK(T)                                                     \
+  do {                                                                        \
+    if (vec && dense) CTB_TILED_VEC(T, true);                                 \
+    else if (vec) CTB_TILED_VEC(T, false);                                    \
+    else if (dense) CTB_TILED_SCALAR(T, true);                                \
+    else CTB_TILED_SCALAR(T, false);                                          \
   } while (0)
   if (dtype == CTB_F32) CTB_TILED_PICK(float);
   else CTB_TILED_PICK(__half);
 #undef CTB_TILED_PICK
-#undef CTB_TILED_LAUNCH
+#undef CTB_TILED_SCALAR
+#undef CTB_TILED_VEC
+  if (rc) return rc;
   CTB_CHECK_LAUNCH("ctb_tiled_broadcast launch");
+  return CTB_OK;
+}
+
+int ctb_tiled_compile(const int32_t* program, int n_ops, int n_inputs, int n_constants, uint32_t* instructions,
+                      int* n_instructions) {
+  if (!program || !instructions || !n_instructions) return fail(CTB_BAD_ARG, "ctb_tiled_compile: null argument");
+  if (n_inputs < 0 || n_inputs > kMaxInputs || n_ops < 1 || n_ops > kMaxOps || n_constants < 0 || n_constants > kMaxConsts)
+    return fail(CTB_UNSUPPORTED, "ctb_tiled_compile: at most %d inputs, %d operations and %d constants", kMaxInputs, kMaxOps,
+                kMaxConsts);
+  Program prog;
+  const char* why = "";
+  const int bad = compile_program(program, n_ops, n_inputs, n_constants, &prog, &why);
+  if (bad == -1000)
+    return fail(CTB_UNSUPPORTED, "ctb_tiled_compile: the expression needs more than %d intermediate values at once", kStack);
+  if (bad) return fail(CTB_BAD_ARG, "ctb_tiled_compile: operation %d %s", -bad - 1, why);
+  for (int k = 0; k < prog.n_ins; ++k) instructions[k] = prog.ins[k];
+  *n_instructions = prog.n_ins;
   return CTB_OK;
 }
 

@@ -60,6 +60,7 @@ SIGNATURES = {
     "ctb_transpose": [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _i, _i, _i],
     "ctb_tiled_broadcast": [_p, _p, _p, C.POINTER(_i64), C.POINTER(_p), C.POINTER(_i64), _i, C.POINTER(C.c_int32), _i,
                             C.POINTER(C.c_float), _i, _i],
+    "ctb_tiled_compile": [C.POINTER(C.c_int32), _i, _i, _i, C.POINTER(C.c_uint32), C.POINTER(_i)],
     "ctb_tiled_mapreduce": [_p, _p, _p, _p, C.POINTER(_i64), _i, _i, _i, _i],
     "ctb_fft": [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _i, _i],
     "ctb_layernorm_fwd": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i],

@@ -124,11 +124,14 @@ int ctb_fft(ctb_ctx* ctx, void* stream, const void* x, void* y, const void* W0, 
 /* ct.Tiled(C) .= f.(ct.Tiled(A), ...)                 src/broadcast.jl:19-23,92-165 (one fused kernel per expression)
  * sum / prod / maximum / minimum / mapreduce(f, op, ct.Tiled(A); dims)     src/mapreduce.jl:66-203
  * Arrays have up to three dimensions (shape[3], unused trailing extents = 1), column-major and dense; f32 or f16,
- * arithmetic in f32.  The broadcast expression is a postfix program of (code, argument) pairs evaluated per element
- * on a stack of at most four values: CTB_TILED_INPUT pushes inputs[argument] (its three strides in elements, 0 along
- * a dimension where the operand has extent 1 and is expanded), CTB_TILED_CONST pushes constants[argument], a unary
- * code replaces the top, a binary code replaces the two top values (second-from-top OP top).  The program must leave
- * exactly one value.  Empty arrays launch nothing. */
+ * arithmetic in f32.  The broadcast expression is a postfix program of (code, argument) pairs with the meaning of a
+ * stack machine: CTB_TILED_INPUT pushes inputs[argument] (its three strides in elements, 0 along a dimension where
+ * the operand has extent 1 and is expanded), CTB_TILED_CONST pushes constants[argument], a unary code replaces the
+ * top, a binary code replaces the two top values (second-from-top OP top).  The program must leave exactly one value.
+ * The library re-orders the evaluation (an input or constant operand of a binary operator is read in place, the
+ * deeper side of an operator between two computed values goes first; a + b and a * b may be evaluated as b + a and
+ * b * a); it then holds at most four intermediate values at once, which every program of CTB_TILED_MAX_OPS
+ * operations fits.  Empty arrays launch nothing. */
 enum {
   CTB_TILED_INPUT = 0, CTB_TILED_CONST = 1,
   CTB_TILED_IDENTITY = 16, CTB_TILED_NEG, CTB_TILED_ABS, CTB_TILED_SQRT, CTB_TILED_EXP, CTB_TILED_EXP2, CTB_TILED_LOG,
@@ -141,6 +144,12 @@ enum {
 int ctb_tiled_broadcast(ctb_ctx* ctx, void* stream, void* dest, const int64_t* shape, const void* const* inputs,
                         const int64_t* input_strides, int n_inputs, const int32_t* program, int n_ops, const float* constants,
                         int n_constants, int dtype);
+/* Diagnostic: the instruction words ctb_tiled_broadcast would run for this program (no GPU needed).  A word is
+ * kind | source << 2 | reversed << 4 | code << 8 | argument << 16 with kind 0 = push the operand, 1 = top = code(top),
+ * 2 = top = top code operand (operand code top when reversed); source 0 = the value below the top (popped), 1 =
+ * inputs[argument], 2 = constants[argument].  instructions has room for CTB_TILED_MAX_OPS words. */
+int ctb_tiled_compile(const int32_t* program, int n_ops, int n_inputs, int n_constants, uint32_t* instructions,
+                      int* n_instructions);
 /* dest = reduction with `op` (CTB_TILED_ADD, _MUL, _MAX or _MIN) of f(src) (a unary code, CTB_TILED_IDENTITY for none)
  * over the dimensions whose bit is set in reduce_mask (bit 0 = first dimension); dest is dense with extent 1 along
  * the reduced dimensions.  Fixed summation order (bitwise repeatable); an empty reduction gives the neutral element. */

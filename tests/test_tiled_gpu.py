@@ -81,6 +81,75 @@ def test_broadcast_size_one_expansion_and_rank_expansion(cuda):
     assert np.array_equal(out.cpu().numpy(), want)
 
 
+def _tree_to_expr(T, tree, leaves):
+    """(name, ...) trees with integer leaves (operand index) and float leaves (constants) -> a Tiled expression."""
+    if isinstance(tree, int):
+        return T.Tiled(leaves[tree])
+    if isinstance(tree, float):
+        return tree
+    args = [_tree_to_expr(T, c, leaves) for c in tree[1:]]
+    if len(args) == 1:
+        return {"neg": lambda x: -x, "abs": abs}.get(tree[0], getattr(T, tree[0], None))(T.Expr.wrap(args[0]))
+    a, b = T.Expr.wrap(args[0]), T.Expr.wrap(args[1])
+    return {"add": lambda: a + b, "sub": lambda: a - b, "mul": lambda: a * b, "div": lambda: a / b, "pow": lambda: a ** b,
+            "max": lambda: T.tmax(a, b), "min": lambda: T.tmin(a, b)}[tree[0]]()
+
+
+def _tree_to_oracle(tree, arrays):
+    if isinstance(tree, int):
+        return arrays[tree]
+    if isinstance(tree, float):
+        return tree
+    return (tree[0],) + tuple(_tree_to_oracle(c, arrays) for c in tree[1:])
+
+
+# one tree per kernel variant: operands held (1, 2, 3-4), accumulator only or with the stack, reversed operators
+VARIANT_TREES = [
+    ("sub", 2.0, ("exp", 0)),                                             # 1 operand, constant on the left (reversed)
+    ("div", 0, ("add", ("abs2", 0), 1.5)),                                # 1 operand, input on the left (reversed)
+    ("mul", ("sin", 0), ("cos", 0)),                                      # 1 operand, two computed sides (stack)
+    ("min", ("max", 0, 1), ("mul", 1, 0.5)),                              # 2 operands, stack
+    ("sub", ("mul", 0, 1), 1),                                            # 2 operands, accumulator only
+    ("add", ("mul", 0, 1), ("sub", 2, 3)),                                # 4 operands, stack
+    ("sub", 3, ("div", 2, ("add", ("abs", 1), ("exp", 0)))),              # 4 operands, accumulator only, reversed twice
+    ("sub", ("sub", ("sin", 0), ("cos", 1)), ("sub", ("tanh", 2), ("mul", ("exp", 0), ("abs", 1)))),   # 3 live values
+    ("pow", 1.5, ("abs", 0)),                                             # reversed pow
+]
+
+
+@pytest.mark.parametrize("n", [4 * 256 * 4 * 3 + 4, 1000, 1 << 20, (1 << 20) + 12])
+@pytest.mark.parametrize("k", range(len(VARIANT_TREES)))
+def test_broadcast_every_kernel_variant(cuda, n, k):
+    """Sizes around the group structure (G groups of four elements per thread and trip, a grid apart): ragged last
+    trips, fewer groups than threads, unaligned n (scalar path: n = 1000 is a multiple of four, 1 << 20 + 12 too;
+    the odd case is in the shapes test)."""
+    import torch
+    T = cuda.tiled
+    tree = VARIANT_TREES[k]
+    arrays = [rnd((n,), 40 + j) for j in range(4)]
+    leaves = [torch.from_numpy(a).cuda() for a in arrays]
+    out = torch.full((n,), float("nan"), device="cuda")
+    T.assign(out, _tree_to_expr(T, tree, leaves))
+    close(out.cpu().numpy(), ref.tiled_broadcast(_tree_to_oracle(tree, arrays)), 2e-6)
+
+
+def test_broadcast_variants_f16_and_expanded(cuda):
+    import torch
+    T = cuda.tiled
+    # Julia (64, 48) with a column operand (64, 1) and a row operand (1, 48): the non-dense vector path, two operands
+    a, col, row = rnd((48, 64), 50), rnd((1, 64), 51), rnd((48, 1), 52)
+    A, Cc, R = (torch.from_numpy(v).cuda() for v in (a, col, row))
+    out = T.materialize((T.Tiled(A) - T.Tiled(Cc)) * T.Tiled(R) + T.sin(T.Tiled(A)) * T.cos(T.Tiled(Cc)))
+    close(out.cpu().numpy(), (a - col) * row + np.sin(a.astype(np.float64)) * np.cos(col.astype(np.float64)), 2e-6)
+    for tree in VARIANT_TREES[:6]:
+        arrays = [rnd((4099 * 4,), 60 + j, dtype=np.float16) for j in range(4)]
+        leaves = [torch.from_numpy(v).cuda() for v in arrays]
+        out = torch.empty(4099 * 4, device="cuda", dtype=torch.float16)
+        T.assign(out, _tree_to_expr(T, tree, leaves))
+        want = ref.tiled_broadcast(_tree_to_oracle(tree, [v.astype(np.float64) for v in arrays]))
+        close(out.cpu().numpy(), want, 1.5e-3)                                # one f16 rounding of the f32 result
+
+
 def test_broadcast_empty_zero_dim_and_rejections(cuda):
     import torch
     T = cuda.tiled
@@ -90,7 +159,7 @@ def test_broadcast_empty_zero_dim_and_rejections(cuda):
     T.assign(Z, 1.0)                                                                   # 0-dim arrays
     assert Z.item() == 1.0
     A = torch.ones(16, device="cuda")
-    C = torch.empty(32, device="cuda")
+    C = torch.arange(32, device="cuda", dtype=torch.float32)
     with pytest.raises(ValueError, match="DimensionMismatch"):
         T.assign(C, T.Tiled(A))
     with pytest.raises(ValueError, match="DimensionMismatch"):
@@ -102,8 +171,15 @@ def test_broadcast_empty_zero_dim_and_rejections(cuda):
     with pytest.raises(ValueError, match="device memory"):
         T.assign(torch.ones(32), 0)                                                    # CPU destination
     lib = cuda._lib
+    # six pushes deep as a postfix program, one live value after the library re-orders it
+    D = torch.empty_like(C)
+    T.assign(D, T.Tiled(C) + (T.Tiled(C) + (T.Tiled(C) + (T.Tiled(C) + (T.Tiled(C) + T.Tiled(C))))))
+    np.testing.assert_array_equal(D.cpu().numpy(), 6 * C.cpu().numpy())
+    long = T.Tiled(C)
+    for _ in range(17):                                                                # 35 operations: over the limit
+        long = long + T.Tiled(C)
     with pytest.raises(cuda.CtbError) as e:
-        T.assign(C, T.Tiled(C) + (T.Tiled(C) + (T.Tiled(C) + (T.Tiled(C) + (T.Tiled(C) + T.Tiled(C))))))
+        T.assign(D, long)
     assert e.value.status == lib.UNSUPPORTED
 
 
