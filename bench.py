@@ -543,7 +543,7 @@ class TiledFused(Workload):
     name = "tiled_fused"
     metric = "tiled_broadcast_gbps"
     unit = "GB/s"
-    kernel = "tiled_broadcast_kernel"
+    kernel = "tiled_broadcast_pipe_kernel"
     n = 1 << 26
 
     def describe(self):

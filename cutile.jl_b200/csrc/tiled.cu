@@ -12,6 +12,7 @@
 #include <math.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "ctx.h"
 
@@ -32,8 +33,20 @@ constexpr int kStack = 4;
 enum : unsigned { K_LOAD = 0, K_UNARY = 1, K_BIN = 2 };
 enum : unsigned { SRC_STACK = 0, SRC_INPUT = 1, SRC_CONST = 2 };
 constexpr unsigned kRevBit = 1u << 4;
+// Bits 24..31: the index the vector kernel switches on, dense so that the switch is one jump through a table:
+// 0, 1 = push an input / a constant; 2..13 = the unary codes NEG..ABS2; then the seven binary codes for each of the six
+// (operand source, reversed) pairs.
+constexpr unsigned kDispatchUnary = 2, kDispatchBinary = 14;
+__host__ __device__ constexpr unsigned bin_variant(unsigned src, bool rev) {
+  return (src == SRC_INPUT ? 0u : src == SRC_CONST ? 1u : 2u) * 2u + (rev ? 1u : 0u);
+}
+__host__ __device__ constexpr unsigned dispatch_index(unsigned kind, unsigned src, bool rev, unsigned code) {
+  return kind == K_LOAD ? (src == SRC_INPUT ? 0u : 1u)
+         : kind == K_UNARY ? kDispatchUnary + (code - CTB_TILED_NEG)
+                           : kDispatchBinary + 7u * bin_variant(src, rev) + (code - CTB_TILED_ADD);
+}
 __host__ __device__ constexpr unsigned make_ins(unsigned kind, unsigned src, bool rev, unsigned code, unsigned arg) {
-  return kind | (src << 2) | (rev ? kRevBit : 0u) | (code << 8) | (arg << 16);
+  return kind | (src << 2) | (rev ? kRevBit : 0u) | (code << 8) | (arg << 16) | (dispatch_index(kind, src, rev, code) << 24);
 }
 
 struct Program {
@@ -171,13 +184,11 @@ __device__ __forceinline__ void store1(void* p, long long i, float v) {
   else static_cast<__half*>(p)[i] = __float2half_rn(v);
 }
 
-// V = 4: four neighbouring elements of the first dimension per group (the host checks that every operand is either
-// contiguous or expanded along it and that rows start on 16-byte boundaries); V = 1: anything else.  G groups per
-// thread and trip, a whole grid apart (neighbouring threads touch neighbouring groups): G loads per operand are in
-// flight per thread, which is what hides the latency of HBM, and the cost of decoding an instruction is shared by
-// V * G elements.  NIN: operands held in registers (1, 2 or 4); DEEP: the program has an operator between two
-// computed values, so the three stack entries below the accumulator exist.  Registers not spent on absent operands
-// and on an unused stack go to more groups per thread.
+// The general path, for arrays the vector path below cannot take (a first extent that is not a multiple of four, rows
+// that do not start on 16-byte boundaries): instantiated with V = 1, G = 1, NIN = 4, DEEP = true, one element per
+// thread and trip, operands and stack in registers.  (V = 4 groups of four neighbouring elements, G groups per thread
+// and NIN operands held are the knobs of the register-only vector kernel this one was before the operands moved to
+// shared memory; they still compile.)
 // DENSE: every operand either has the destination's shape (dense) or is a single element: one linear index, no
 // division.  Otherwise the group index is split into its three coordinates (32-bit arithmetic; the host checks
 // that the element count fits).  The operands are read once per element into registers.
@@ -247,7 +258,7 @@ __global__ void __launch_bounds__(256)
     for (int v = 0; v < ES; ++v) s1[v] = s2[v] = s3[v] = 0.f;
     for (int k = 0; k < prog.n_ins; ++k) {
       const unsigned w = prog.ins[k];
-      const unsigned kind = w & 3u, src = (w >> 2) & 3u, code = (w >> 8) & 0xffu, arg = w >> 16;
+      const unsigned kind = w & 3u, src = (w >> 2) & 3u, code = (w >> 8) & 0xffu, arg = (w >> 16) & 0xffu;
       if (kind == K_UNARY) {
         // one dispatch per instruction and thread, not per element
 #define CTB_U(CODE, EXPR)               \
@@ -345,6 +356,59 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// ---- sine and cosine for the vector path ---------------------------------------------------------------------------
+// The library's sinf / cosf test every element for a huge argument and branch; for a thread's 4 * G elements that
+// is most of the instructions of a short expression.  Here the test is made once for all of a thread's elements and
+// the common case runs without a branch:  j = round(|x| * 2/pi) by the magic-number addition, r = |x| - j * pi/2 with
+// pi/2 split in three f32 parts (every step one FMA; for |x| <= 105615 the first difference is exact), then
+// sin(r) = r + r s (S0 + S1 s + S2 s^2) or cos(r) = 1 - s/2 + s^2 (C0 + C1 s + C2 s^2) with s = r^2, picked by the
+// parity of j, the sign by bit 1 of j (and by the sign of x for the sine, which keeps sin(-0) = -0).  The
+// coefficients are a weighted minimax fit on |r| <= pi/4 (fit errors 3.6e-9 relative and 9.6e-11).  The same
+// arithmetic evaluated on a CPU for every f32 in [0, 105615] differs from the exact value by at most 1.54 ulp
+// (0.02 % of the arguments by more than 1 ulp).  Anything larger, infinite or NaN takes sinf / cosf.
+constexpr float kSinCosLimit = 105615.0f;
+template <bool COS>
+__device__ __forceinline__ float sincos_reduced(float x) {
+  constexpr float kTwoOverPi = 0.636619772367581343f, kMagic = 12582912.0f;  // 1.5 * 2^23
+  constexpr float P1 = 0x1.921fb6p+0f, P2 = -0x1.777a5cp-25f, P3 = -0x1.ee59dap-50f;  // sum = pi/2 to 2^-74
+  constexpr float S0 = -0.16666655242443085f, S1 = 0.008332176133990288f, S2 = -0.00019516977772582322f;
+  constexpr float C0 = 0.04166664555668831f, C1 = -0.0013887364184483886f, C2 = 2.443809171381872e-05f;
+  const float ax = fabsf(x);
+  float jf = __fmaf_rn(ax, kTwoOverPi, kMagic);
+  unsigned q = __float_as_uint(jf);  // the low bits of the mantissa hold j
+  jf = __fadd_rn(jf, -kMagic);
+  float r = __fmaf_rn(jf, -P1, ax);
+  r = __fmaf_rn(jf, -P2, r);
+  r = __fmaf_rn(jf, -P3, r);
+  if (COS) q += 1u;  // cos(x) = sin(x + pi/2)
+  const float s = __fmul_rn(r, r);
+  // both polynomials, one select: selects and bit operations issue at half the rate of FMAs
+  float ps = __fmaf_rn(s, S2, S1);
+  ps = __fmaf_rn(s, ps, S0);
+  ps = __fmaf_rn(__fmul_rn(s, r), ps, r);
+  float pc = __fmaf_rn(s, C2, C1);
+  pc = __fmaf_rn(s, pc, C0);
+  pc = __fmaf_rn(s, pc, -0.5f);
+  pc = __fmaf_rn(s, pc, 1.0f);
+  const float res = (q & 1u) ? pc : ps;
+  unsigned sign = (q & 2u) << 30;
+  if (!COS) sign ^= __float_as_uint(x) & 0x80000000u;
+  return __uint_as_float(__float_as_uint(res) ^ sign);
+}
+template <bool COS, int E>
+__device__ __forceinline__ void sincos_all(float (&a)[E]) {
+  bool in_range = true;
+#pragma unroll
+  for (int v = 0; v < E; ++v) in_range = in_range && (fabsf(a[v]) <= kSinCosLimit);  // false for NaN
+  if (in_range) {
+#pragma unroll
+    for (int v = 0; v < E; ++v) a[v] = sincos_reduced<COS>(a[v]);
+  } else {
+#pragma unroll
+    for (int v = 0; v < E; ++v) a[v] = COS ? cosf(a[v]) : sinf(a[v]);
+  }
+}
+
 // ---- the vector path: operands staged in shared memory by cp.async, two trips deep ----------------------------------
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 // 16 or 8 bytes global -> shared, asynchronous; src_bytes = 0 writes zeros and reads nothing
@@ -359,6 +423,57 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// The element-wise part of one instruction, for all of a thread's elements.  The operation, its direction and the
+// kind of operand are template parameters and every instruction has its own straight-line code in the kernel's one
+// switch: tests on them inside the element loops came out as two to five predicated moves per element and
+// instruction, and a chain of compares per instruction, more than the arithmetic itself.
+template <int CODE, bool REV>
+__device__ __forceinline__ float binary_op(float p, float q) {
+  const float a = REV ? q : p, b = REV ? p : q;
+  if constexpr (CODE == CTB_TILED_ADD) return a + b;
+  else if constexpr (CODE == CTB_TILED_SUB) return a - b;
+  else if constexpr (CODE == CTB_TILED_MUL) return a * b;
+  else if constexpr (CODE == CTB_TILED_DIV) return a / b;
+  else if constexpr (CODE == CTB_TILED_MAX) return fmaxf(a, b);
+  else if constexpr (CODE == CTB_TILED_MIN) return fminf(a, b);
+  else return powf(a, b);
+}
+template <int CODE, bool REV, int E>
+__device__ __forceinline__ void apply_binary(float (&s0)[E], const float (&t)[E]) {
+#pragma unroll
+  for (int v = 0; v < E; ++v) s0[v] = binary_op<CODE, REV>(s0[v], t[v]);
+}
+template <int CODE, bool REV, int E>
+__device__ __forceinline__ void apply_binary(float (&s0)[E], float c) {
+#pragma unroll
+  for (int v = 0; v < E; ++v) s0[v] = binary_op<CODE, REV>(s0[v], c);
+}
+template <int CODE, int E>
+__device__ __forceinline__ void apply_unary(float (&s0)[E]) {
+  if constexpr (CODE == CTB_TILED_SIN) {
+    sincos_all<false>(s0);
+  } else if constexpr (CODE == CTB_TILED_COS) {
+    sincos_all<true>(s0);
+  } else {
+#pragma unroll
+    for (int v = 0; v < E; ++v) s0[v] = unary(CODE, s0[v]);  // CODE is a constant: the switch inside folds
+  }
+}
+
+// Calls f(integral_constant<IDX>) for the run-time idx in [LO, HI) through a balanced tree of compares: six uniform
+// branches for the 56 instructions.  (A switch over the same cases was compiled to a chain of compares, one per case.)
+template <unsigned LO, unsigned HI, typename F>
+__device__ __forceinline__ void tree_dispatch(unsigned idx, F&& f) {
+  if constexpr (HI - LO == 1) {
+    f(std::integral_constant<unsigned, LO>());
+  } else {
+    constexpr unsigned MID = (LO + HI) / 2;
+    if (idx < MID) tree_dispatch<LO, MID>(idx, f);
+    else tree_dispatch<MID, HI>(idx, f);
+  }
+}
+constexpr unsigned kDispatchCount = kDispatchBinary + 7 * 6;
+
 // Every operand is contiguous along the first dimension with 16-byte aligned rows, or expanded along it (the host
 // checks).  A group is four neighbouring elements; a thread owns G groups per trip, a whole grid apart.  The
 // operands of the NEXT trip are copied global -> shared by cp.async (no registers, nothing waits on them) while the
@@ -366,6 +481,8 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 // occupancy; registers hold only the accumulator, the current operand and, for DEEP programs, the three stack
 // entries.  A thread reads only the shared memory it filled itself: no CTA barrier anywhere.
 // Shared memory: [2 buffers][n_inputs][G][256 threads] groups of 4 * sizeof(T) bytes.
+// Addresses: with DENSE operands a thread keeps one running pointer per array and adds a trip's bytes to it; a trip
+// whose G groups all exist (all but a thread's last) runs without a bounds test.
 template <typename T, int G, bool DENSE, bool DEEP>
 __global__ void __launch_bounds__(256)
     tiled_broadcast_pipe_kernel(void* __restrict__ dest, const Operands in, const Program prog, int n_inputs, long long d0,
@@ -375,164 +492,159 @@ __global__ void __launch_bounds__(256)
   extern __shared__ __align__(16) unsigned char tiled_smem[];
   const long long n0 = d0 / V, total = n0 * d1 * d2;
   const long long grid_stride = (long long)gridDim.x * blockDim.x;
+  const long long group_bytes = grid_stride * VB;  // from one of a thread's groups to the next, in a dense array
   const unsigned tid = threadIdx.x;
   const unsigned buf_bytes = (unsigned)n_inputs * G * 256 * VB;
   const unsigned smem0 = smem_addr(tiled_smem) + tid * VB;
   auto slot = [&](unsigned buf, unsigned a, unsigned g) { return smem0 + buf * buf_bytes + (a * G + g) * (256 * VB); };
 
-  // destination offset and operand offsets of group index ig
-  auto locate = [&](long long ig, long long& o, long long (&off)[kMaxInputs]) {
-    if (DENSE) {
-      o = ig * V;
+  long long i = (long long)blockIdx.x * blockDim.x + tid;
+  // running pointers (DENSE): this thread's first group of the trip to copy next / to store next
+  const char* src_p[kMaxInputs];
 #pragma unroll
-      for (int a = 0; a < kMaxInputs; ++a) off[a] = in.stride[a][0] ? o : 0;
-    } else {
-      const unsigned u = (unsigned)ig, un0 = (unsigned)n0, ud1 = (unsigned)d1;
-      const unsigned r = u / un0, i0 = (u - r * un0) * V, i2 = r / ud1, i1 = r - i2 * ud1;
-      o = i0 + d0 * (i1 + d1 * (long long)i2);
-#pragma unroll
-      for (int a = 0; a < kMaxInputs; ++a) off[a] = i0 * in.stride[a][0] + i1 * in.stride[a][1] + i2 * in.stride[a][2];
-    }
+  for (int a = 0; a < kMaxInputs; ++a) src_p[a] = static_cast<const char*>(in.ptr[a]) + i * VB;
+  char* dst_p = static_cast<char*>(dest) + i * VB;
+
+  // element offset of group ig in the destination (the general case)
+  auto dest_offset = [&](long long ig) -> long long {
+    const unsigned u = (unsigned)ig, un0 = (unsigned)n0, ud1 = (unsigned)d1;
+    const unsigned r = u / un0, i0 = (u - r * un0) * V, i2 = r / ud1, i1 = r - i2 * ud1;
+    return i0 + d0 * (i1 + d1 * (long long)i2);
   };
-  auto issue = [&](long long i, unsigned buf) {
+  auto issue = [&](long long at, unsigned buf, auto full_tag) {
+    constexpr bool FULL = decltype(full_tag)::value;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      const long long ig = i + g * grid_stride;
-      const bool live = ig < total;
-      long long o, off[kMaxInputs];
-      locate(live ? ig : 0, o, off);
+      const long long ig = at + g * grid_stride;
+      const bool live = FULL || ig < total;
+      unsigned i0 = 0, i1 = 0, i2 = 0;
+      if (!DENSE) {
+        const unsigned u = live ? (unsigned)ig : 0u, un0 = (unsigned)n0, ud1 = (unsigned)d1;
+        const unsigned r = u / un0;
+        i0 = (u - r * un0) * V, i2 = r / ud1, i1 = r - i2 * ud1;
+      }
 #pragma unroll
       for (int a = 0; a < kMaxInputs; ++a) {
-        if (a < n_inputs) {
-          const T* src = static_cast<const T*>(in.ptr[a]) + off[a];
-          if (in.stride[a][0] == 1) {
-            cp_async_group<VB>(slot(buf, a, g), src, live ? VB : 0);
+        if (a < n_inputs) {  // uniform
+          const bool contiguous = in.stride[a][0] == 1;
+          const char* src;
+          if (DENSE) {
+            src = contiguous ? src_p[a] + g * group_bytes : static_cast<const char*>(in.ptr[a]);
+          } else {
+            src = static_cast<const char*>(in.ptr[a]) +
+                  (i0 * in.stride[a][0] + i1 * in.stride[a][1] + i2 * in.stride[a][2]) * (long long)sizeof(T);
+          }
+          if (contiguous) {
+            if (FULL) cp_async_group<VB>(slot(buf, a, g), src, VB);
+            else cp_async_group<VB>(slot(buf, a, g), live ? src : static_cast<const char*>(in.ptr[a]), live ? VB : 0);
           } else if (live) {  // expanded along the first dimension: one element, four copies
-            const T v = *src;
+            const T v = *reinterpret_cast<const T*>(src);
             T* dst = reinterpret_cast<T*>(tiled_smem + (slot(buf, a, g) - smem_addr(tiled_smem)));
             dst[0] = v; dst[1] = v; dst[2] = v; dst[3] = v;
           }
         }
       }
     }
+    if (DENSE) {
+#pragma unroll
+      for (int a = 0; a < kMaxInputs; ++a) src_p[a] += group_bytes * G;
+    }
     cp_async_commit();
   };
-
-  long long i = (long long)blockIdx.x * blockDim.x + tid;
-  if (i < total) issue(i, 0);
-  for (unsigned buf = 0; i < total; i += grid_stride * G, buf ^= 1u) {
-    const long long next = i + grid_stride * G;
-    if (next < total) issue(next, buf ^ 1u);
-    else cp_async_commit();  // an empty group keeps the count below uniform
-    cp_async_wait<1>();      // everything but the newest group has landed: this trip's operands
-
-    float s0[E], s1[ES], s2[ES], s3[ES];  // the stack, top (the accumulator) first
-#pragma unroll
-    for (int v = 0; v < E; ++v) s0[v] = 0.f;
-#pragma unroll
-    for (int v = 0; v < ES; ++v) s1[v] = s2[v] = s3[v] = 0.f;
-    for (int k = 0; k < prog.n_ins; ++k) {
-      const unsigned w = prog.ins[k];
-      const unsigned kind = w & 3u, src = (w >> 2) & 3u, code = (w >> 8) & 0xffu, arg = w >> 16;
-      if (kind == K_UNARY) {
-#define CTB_U(CODE, EXPR)               \
-  case CODE:                            \
-    _Pragma("unroll") for (int v = 0; v < E; ++v) { const float t = s0[v]; s0[v] = (EXPR); } \
-    break;
-        switch (code) {
-          CTB_U(CTB_TILED_NEG, -t)
-          CTB_U(CTB_TILED_ABS, fabsf(t))
-          CTB_U(CTB_TILED_SQRT, sqrtf(t))
-          CTB_U(CTB_TILED_EXP, expf(t))
-          CTB_U(CTB_TILED_EXP2, exp2f(t))
-          CTB_U(CTB_TILED_LOG, logf(t))
-          CTB_U(CTB_TILED_LOG2, log2f(t))
-          CTB_U(CTB_TILED_SIN, sinf(t))
-          CTB_U(CTB_TILED_COS, cosf(t))
-          CTB_U(CTB_TILED_TANH, tanhf(t))
-          CTB_U(CTB_TILED_INV, 1.0f / t)
-          CTB_U(CTB_TILED_ABS2, t * t)
-          default: break;
-        }
-#undef CTB_U
-        continue;
-      }
-      float t[E];  // the operand
-      if (src == SRC_INPUT) {
-        const unsigned base = slot(buf, arg & (kMaxInputs - 1), 0);
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          if constexpr (sizeof(T) == 4) {
-            float4 q;
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w) : "r"(base + g * (256 * VB)));
-            t[4 * g] = q.x; t[4 * g + 1] = q.y; t[4 * g + 2] = q.z; t[4 * g + 3] = q.w;
-          } else {
-            uint2 q;
-            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(base + g * (256 * VB)));
-            const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
-            const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
-            t[4 * g] = lo.x; t[4 * g + 1] = lo.y; t[4 * g + 2] = hi.x; t[4 * g + 3] = hi.y;
-          }
-        }
-      } else if (src == SRC_CONST) {
-        const float c = prog.consts[arg & (kMaxConsts - 1)];
-#pragma unroll
-        for (int v = 0; v < E; ++v) t[v] = c;
-      } else {  // the entry below the accumulator, popped (DEEP programs only)
-#pragma unroll
-        for (int v = 0; v < E; ++v) {
-          t[v] = s1[v % ES];
-          if (DEEP) { s1[v % ES] = s2[v % ES]; s2[v % ES] = s3[v % ES]; }
-        }
-      }
-      if (kind == K_LOAD) {
-#pragma unroll
-        for (int v = 0; v < E; ++v) {
-          if (DEEP) { s3[v % ES] = s2[v % ES]; s2[v % ES] = s1[v % ES]; s1[v % ES] = s0[v]; }
-          s0[v] = t[v];
-        }
-        continue;
-      }
-      if (w & kRevBit) {
-#pragma unroll
-        for (int v = 0; v < E; ++v) {
-          const float q = s0[v]; s0[v] = t[v]; t[v] = q;
-        }
-      }
-#define CTB_B(CODE, EXPR)               \
-  case CODE:                            \
-    _Pragma("unroll") for (int v = 0; v < E; ++v) { const float a = s0[v], b = t[v]; s0[v] = (EXPR); } \
-    break;
-      switch (code) {
-        CTB_B(CTB_TILED_ADD, a + b)
-        CTB_B(CTB_TILED_SUB, a - b)
-        CTB_B(CTB_TILED_MUL, a * b)
-        CTB_B(CTB_TILED_DIV, a / b)
-        CTB_B(CTB_TILED_MAX, fmaxf(a, b))
-        CTB_B(CTB_TILED_MIN, fminf(a, b))
-        default:
-#pragma unroll
-          for (int v = 0; v < E; ++v) s0[v] = powf(s0[v], t[v]);
-          break;
-      }
-#undef CTB_B
-    }
+  // the four elements of every group of operand `a`, from shared memory
+  auto fetch = [&](unsigned buf, unsigned a, float (&t)[E]) {
+    const unsigned base = slot(buf, a & (kMaxInputs - 1), 0);
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      const long long ig = i + g * grid_stride;
-      if (ig >= total) continue;
-      long long o, off[kMaxInputs];
-      locate(ig, o, off);
+      if constexpr (sizeof(T) == 4) {
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(t[4 * g]), "=f"(t[4 * g + 1]), "=f"(t[4 * g + 2]), "=f"(t[4 * g + 3])
+                     : "r"(base + g * (256 * VB)));
+      } else {
+        uint2 q;
+        asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(q.x), "=r"(q.y) : "r"(base + g * (256 * VB)));
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&q.x));
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&q.y));
+        t[4 * g] = lo.x; t[4 * g + 1] = lo.y; t[4 * g + 2] = hi.x; t[4 * g + 3] = hi.y;
+      }
+    }
+  };
+  auto start_next = [&](long long at, unsigned buf) {
+    if (at + (G - 1) * grid_stride < total) issue(at, buf, std::true_type());
+    else if (at < total) issue(at, buf, std::false_type());
+    else cp_async_commit();  // an empty group keeps the count in the wait below uniform
+  };
+
+  start_next(i, 0);
+  for (unsigned buf = 0; i < total; i += grid_stride * G, buf ^= 1u) {
+    start_next(i + grid_stride * G, buf ^ 1u);
+    cp_async_wait<1>();  // everything but the newest group has landed: this trip's operands
+
+    float s0[E], s1[ES], s2[ES], s3[ES];  // the stack, top (the accumulator) first; every program starts with a push
+#pragma unroll
+    for (int v = 0; v < ES; ++v) s1[v] = s2[v] = s3[v] = 0.f;
+    auto push = [&]() {
+      if (DEEP) {
+#pragma unroll
+        for (int v = 0; v < ES; ++v) { s3[v] = s2[v]; s2[v] = s1[v]; s1[v] = s0[v % E]; }
+      }
+    };
+    auto pop = [&](float (&t)[E]) {  // DEEP programs only
+#pragma unroll
+      for (int v = 0; v < E; ++v) {
+        t[v] = s1[v % ES];
+        if (DEEP) { s1[v % ES] = s2[v % ES]; s2[v % ES] = s3[v % ES]; }
+      }
+    };
+    for (int k = 0; k < prog.n_ins; ++k) {
+      const unsigned w = prog.ins[k];
+      const unsigned arg = (w >> 16) & 0xffu;
+      tree_dispatch<0, 64>(w >> 24, [&](auto tag) {
+        constexpr unsigned IDX = decltype(tag)::value;
+        if constexpr (IDX == 0) {
+          push();
+          fetch(buf, arg, s0);
+        } else if constexpr (IDX == 1) {
+          push();
+          const float c = prog.consts[arg & (kMaxConsts - 1)];
+#pragma unroll
+          for (int v = 0; v < E; ++v) s0[v] = c;
+        } else if constexpr (IDX < kDispatchBinary) {
+          apply_unary<(int)(CTB_TILED_NEG + IDX - kDispatchUnary)>(s0);
+        } else if constexpr (IDX < kDispatchCount) {
+          constexpr unsigned VARIANT = (IDX - kDispatchBinary) / 7;
+          constexpr int CODE = (int)(CTB_TILED_ADD + (IDX - kDispatchBinary) % 7);
+          constexpr bool REV = VARIANT & 1u;
+          if constexpr (VARIANT / 2 == 0) {  // an input
+            float t[E];
+            fetch(buf, arg, t);
+            apply_binary<CODE, REV>(s0, t);
+          } else if constexpr (VARIANT / 2 == 1) {  // a constant
+            apply_binary<CODE, REV>(s0, prog.consts[arg & (kMaxConsts - 1)]);
+          } else if constexpr (DEEP) {  // the entry below the accumulator
+            float t[E];
+            pop(t);
+            apply_binary<CODE, REV>(s0, t);
+          }
+        }
+      });
+    }
+    const bool full = i + (G - 1) * grid_stride < total;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (!full && i + g * grid_stride >= total) continue;
+      char* out = DENSE ? dst_p + g * group_bytes : static_cast<char*>(dest) + dest_offset(i + g * grid_stride) * (long long)sizeof(T);
       const float* r = &s0[g * V];
       if constexpr (sizeof(T) == 4) {
-        __stcs(reinterpret_cast<float4*>(static_cast<float*>(dest) + o), make_float4(r[0], r[1], r[2], r[3]));
+        __stcs(reinterpret_cast<float4*>(out), make_float4(r[0], r[1], r[2], r[3]));
       } else {
         uint2 q;
         *reinterpret_cast<__half2*>(&q.x) = __floats2half2_rn(r[0], r[1]);
         *reinterpret_cast<__half2*>(&q.y) = __floats2half2_rn(r[2], r[3]);
-        __stcs(reinterpret_cast<uint2*>(static_cast<__half*>(dest) + o), q);
+        __stcs(reinterpret_cast<uint2*>(out), q);
       }
     }
+    dst_p += group_bytes * G;
   }
   cp_async_wait<0>();
 }
@@ -548,11 +660,7 @@ int launch_pipe(ctb_ctx* ctx, cudaStream_t st, void* dest, const Operands& in, c
   // Several waves of CTAs, not one wave of resident ones: CTAs that all start together stay in step (all loading,
   // then all storing) and measured 10 % slower than CTAs that start at different times.
   const long long ctas = (units + 256ll * G - 1) / (256ll * G);
-  int per_sm = 16;
-#ifdef CTB_TILED_TUNE
-  if (const char* e = getenv("CTB_TW")) per_sm = atoi(e);
-#endif
-  const int grid = (int)std::max<long long>(1, std::min<long long>(ctas, (long long)ctx->sm_count * per_sm));
+  const int grid = (int)std::max<long long>(1, std::min<long long>(ctas, (long long)ctx->sm_count * 16));
   kernel<<<grid, 256, smem, st>>>(dest, in, prog, n_inputs, d0, d1, d2);
   return CTB_OK;
 }
@@ -735,16 +843,11 @@ int ctb_tiled_broadcast(ctb_ctx* ctx, void* stream, void* dest, const int64_t* s
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool deep = need > 1;
   int rc = CTB_OK;
-  int tune_g = 0;
-#ifdef CTB_TILED_TUNE
-  if (const char* e = getenv("CTB_TG")) tune_g = atoi(e);
-#endif
-  // groups per thread: as many as registers (the stack of a deep program) and shared memory (the operands) allow
+  // groups per thread: as many as registers (the stack of a deep program) and shared memory (the operands) allow;
+  // eight groups for a single operand measured slower than four (128 registers, two CTAs per SM)
 #define CTB_TILED_VEC(T, D)                                                                                          \
   do {                                                                                                               \
-    if (tune_g == 2 && !deep) rc = launch_pipe<T, 2, D, false>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units); \
-    else if (tune_g == 4 && !deep) rc = launch_pipe<T, 4, D, false>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units); \
-    else if (deep) rc = launch_pipe<T, 2, D, true>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units);            \
+    if (deep) rc = launch_pipe<T, 2, D, true>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units);                 \
     else if (n_inputs <= 3) rc = launch_pipe<T, 4, D, false>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units);  \
     else rc = launch_pipe<T, 2, D, false>(ctx, st, dest, in, prog, n_inputs, d0, d1, d2, units);                     \
   } while (0)

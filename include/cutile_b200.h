@@ -147,7 +147,8 @@ int ctb_tiled_broadcast(ctb_ctx* ctx, void* stream, void* dest, const int64_t* s
 /* Diagnostic: the instruction words ctb_tiled_broadcast would run for this program (no GPU needed).  A word is
  * kind | source << 2 | reversed << 4 | code << 8 | argument << 16 with kind 0 = push the operand, 1 = top = code(top),
  * 2 = top = top code operand (operand code top when reversed); source 0 = the value below the top (popped), 1 =
- * inputs[argument], 2 = constants[argument].  instructions has room for CTB_TILED_MAX_OPS words. */
+ * inputs[argument], 2 = constants[argument]; the argument has eight bits, bits 24-31 repeat kind, source, reversed and
+ * code as one dense index for the kernel's jump table.  instructions has room for CTB_TILED_MAX_OPS words. */
 int ctb_tiled_compile(const int32_t* program, int n_ops, int n_inputs, int n_constants, uint32_t* instructions,
                       int* n_instructions);
 /* dest = reduction with `op` (CTB_TILED_ADD, _MUL, _MAX or _MIN) of f(src) (a unary code, CTB_TILED_IDENTITY for none)

@@ -48,7 +48,7 @@ def run_words(words, inputs, consts):
     """The machine of the header comment; also checks the stack never holds more than four values."""
     stack = []
     for w in words:
-        kind, src, rev, code, arg = w & 3, (w >> 2) & 3, (w >> 4) & 1, (w >> 8) & 0xFF, w >> 16
+        kind, src, rev, code, arg = w & 3, (w >> 2) & 3, (w >> 4) & 1, (w >> 8) & 0xFF, (w >> 16) & 0xFF
         if kind == 1:
             stack[-1] = ref.TILED_UNARY[NAMES[code]](stack[-1])
             continue
