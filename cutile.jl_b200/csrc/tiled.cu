@@ -684,7 +684,7 @@ struct ReduceShape {
 // Mode B (the first dimension is kept): one thread per output, outputs along the first dimension in neighbouring
 // threads (coalesced), the part's share of the reduced index space walked in order with running coordinates.
 // OP is a compile-time constant and so is "f is the identity": a dispatch per element would cost more than the element.
-template <typename T, bool MODE_A, int OP, bool MAPPED>
+template <typename T, bool MODE_A, int OP, bool MAPPED, int VB = 1>
 __global__ void __launch_bounds__(256)
     tiled_reduce_kernel(const void* __restrict__ src, float* __restrict__ partial, void* __restrict__ dest, const ReduceShape s,
                         int f_code) {
@@ -739,7 +739,11 @@ __global__ void __launch_bounds__(256)
       else store1<T>(dest, o, t);
     }
   } else {
-    const long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    // VB neighbouring outputs per thread (VB = 4: the first extent is a multiple of four and the rows start on
+    // aligned boundaries, so the four outputs share their other coordinates and one 16-byte / 8-byte load fetches an
+    // element of each); eight loads in flight per thread, combined in index order: the order of summation of every
+    // output is the same as with one output per thread.
+    const long long o = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VB;
     if (o >= s.outputs) return;
     // output coordinates over the kept dimensions (the first one is kept), reduced coordinates over dimensions 1 and 2
     const long long k0 = o % s.keep_n[0], q = o / s.keep_n[0], k1 = q % s.keep_n[1], k2 = q / s.keep_n[1];
@@ -754,24 +758,48 @@ __global__ void __launch_bounds__(256)
         off = base + r2 * st2;
       }
     };
-    float acc = neutral(op);
-    long long r = lo;
-    for (; r + 4 <= hi; r += 4) {  // four loads in flight; combined in index order
-      float v[4];
+    auto load = [&](long long at, float (&v)[VB]) {
+      if constexpr (VB == 1) {
+        v[0] = load1<T>(src, at);
+      } else if constexpr (sizeof(T) == 4) {
+        const float4 x = __ldcs(reinterpret_cast<const float4*>(static_cast<const float*>(src) + at));
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+      } else {
+        const uint2 x = __ldcs(reinterpret_cast<const uint2*>(static_cast<const __half*>(src) + at));
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&x.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&x.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+      }
+    };
+    constexpr int kFlight = VB == 1 ? 4 : 8;
+    float acc[VB];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        v[j] = load1<T>(src, off);
+    for (int e = 0; e < VB; ++e) acc[e] = neutral(op);
+    long long r = lo;
+    for (; r + kFlight <= hi; r += kFlight) {
+      float v[kFlight][VB];
+#pragma unroll
+      for (int j = 0; j < kFlight; ++j) {
+        load(off, v[j]);
         advance();
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc = binary(op, acc, fmap(v[j]));
+      for (int j = 0; j < kFlight; ++j)
+#pragma unroll
+        for (int e = 0; e < VB; ++e) acc[e] = binary(op, acc[e], fmap(v[j][e]));
     }
     for (; r < hi; ++r) {
-      acc = binary(op, acc, fmap(load1<T>(src, off)));
+      float v[VB];
+      load(off, v);
       advance();
+#pragma unroll
+      for (int e = 0; e < VB; ++e) acc[e] = binary(op, acc[e], fmap(v[e]));
     }
-    if (s.parts > 1) partial[o * s.parts + part] = acc;
-    else store1<T>(dest, o, acc);
+#pragma unroll
+    for (int e = 0; e < VB; ++e) {
+      if (s.parts > 1) partial[(o + e) * s.parts + part] = acc[e];
+      else store1<T>(dest, o + e, acc[e]);
+    }
   }
 }
 
@@ -919,7 +947,11 @@ int ctb_tiled_mapreduce(ctb_ctx* ctx, void* stream, void* dest, const void* src,
   // enough (output, part) pairs to fill the GPU; a part is at least 4096 reduced elements for a CTA, 32 for a thread
   const long long want = mode_a ? (long long)ctx->sm_count * 8 : (long long)ctx->sm_count * 8 * 256;
   const long long min_part = mode_a ? 4096 : 32;
-  s.parts = std::max<long long>(1, std::min<long long>({want / std::max<long long>(1, s.outputs),
+  // first dimension kept: four neighbouring outputs per thread where 16-byte (f16: 8-byte) loads are aligned
+  const int es = dtype == CTB_F32 ? 4 : 2;
+  const int vb = (!mode_a && (reduce_mask & 1) == 0 && s.d[0] % 4 == 0 && (uintptr_t)src % (4 * es) == 0) ? 4 : 1;
+  const long long work_items = mode_a ? s.outputs : s.outputs / vb;
+  s.parts = std::max<long long>(1, std::min<long long>({want / std::max<long long>(1, work_items),
                                                         (s.red_len + min_part - 1) / min_part, (long long)1024}));
   s.chunk = (std::max<long long>(1, s.red_len) + s.parts - 1) / s.parts;
   if (mode_a) s.chunk = (s.chunk + 1023) / 1024 * 1024;  // parts start on 16-byte boundaries of an aligned row
@@ -932,12 +964,13 @@ int ctb_tiled_mapreduce(ctb_ctx* ctx, void* stream, void* dest, const void* src,
     partial = static_cast<float*>(ws);
   }
   if (mode_a && s.outputs > 0x7fffffffLL) return fail(CTB_UNSUPPORTED, "ctb_tiled_mapreduce: too many output elements");
-  const dim3 grid(mode_a ? (unsigned)s.outputs : (unsigned)((s.outputs + 255) / 256), (unsigned)s.parts);
+  const dim3 grid(mode_a ? (unsigned)s.outputs : (unsigned)((work_items + 255) / 256), (unsigned)s.parts);
   const unsigned fgrid = (unsigned)((s.outputs + 255) / 256);
   const bool mapped = f != CTB_TILED_IDENTITY;
 #define CTB_RED_LAUNCH(T, A, OP, M)                                                                \
   do {                                                                                             \
-    tiled_reduce_kernel<T, A, OP, M><<<grid, 256, 0, st>>>(src, partial, dest, s, f);             \
+    if (!A && vb == 4) tiled_reduce_kernel<T, false, OP, M, 4><<<grid, 256, 0, st>>>(src, partial, dest, s, f); \
+    else tiled_reduce_kernel<T, A, OP, M><<<grid, 256, 0, st>>>(src, partial, dest, s, f);        \
     if (s.parts > 1) tiled_reduce_final_kernel<T, OP><<<fgrid, 256, 0, st>>>(partial, dest, s.outputs, s.parts); \
   } while (0)
 #define CTB_RED_MAPPED(T, A, OP)              \

@@ -186,7 +186,8 @@ def test_broadcast_empty_zero_dim_and_rejections(cuda):
 @pytest.mark.parametrize("shape,dims", [((1000,), None), ((1000,), 1), ((64, 32), 1), ((64, 32), 2), ((8, 16, 32), (1, 2)),
                                         ((8, 16, 32), (1, 3)), ((8, 16, 32), (2, 3)), ((8, 16, 32), (1, 2, 3)),
                                         ((33, 1001), 2), ((33, 1001), 1), ((7, 5, 3), None), ((64, 32), (2, 3)),
-                                        ((4096, 4096), None), ((3, 2_000_003), 1), ((2_000_003, 3), 1)])
+                                        ((4096, 4096), None), ((3, 2_000_003), 1), ((2_000_003, 3), 1),
+                                        ((1000, 260), 2), ((37, 11, 64), (2, 3)), ((5000, 8), 2), ((2048, 2048), 2)])
 def test_mapreduce_sum(cuda, shape, dims):
     import torch
     T = cuda.tiled
@@ -222,6 +223,18 @@ def test_mapreduce_prod_max_min_mapped_and_edge_cases(cuda):
     want = h.astype(np.float32).sum(axis=1, keepdims=True)
     close(got.cpu().numpy(), want, 2e-3)
     assert got.dtype == torch.float16
+    # first dimension kept and a multiple of four: four outputs per thread, f32 and f16, every reduction
+    c = rnd((333, 40), 25, lo=0.9, hi=1.1)
+    Cc = torch.from_numpy(c).cuda()
+    close(T.tprod(T.Tiled(Cc), dims=2).cpu().numpy(), ref.tiled_mapreduce("identity", "mul", c, (2,)), 1e-5)
+    assert np.array_equal(T.tmaximum(T.Tiled(Cc), dims=2).cpu().numpy(), c.max(axis=0, keepdims=True))
+    assert np.array_equal(T.tminimum(T.Tiled(Cc), dims=2).cpu().numpy(), c.min(axis=0, keepdims=True))
+    close(T.tmapreduce("abs2", "add", T.Tiled(Cc), dims=2).cpu().numpy(), ref.tiled_mapreduce("abs2", "add", c, (2,)), 1e-5)
+    h2 = rnd((301, 64), 26, np.float16)
+    got = T.tsum(T.Tiled(torch.from_numpy(h2).cuda()), dims=2)
+    close(got.cpu().numpy(), h2.astype(np.float32).sum(axis=0, keepdims=True), 2e-3)
+    view = torch.from_numpy(rnd((64, 36), 27)).cuda()[:, 1:33].contiguous()            # aligned copy ...
+    close(T.tsum(T.Tiled(view), dims=2).cpu().numpy(), view.cpu().numpy().sum(axis=0, keepdims=True), 1e-5)
     with pytest.raises(ValueError, match="ArgumentError"):
         T.tsum(T.Tiled(A), dims=0)
     with pytest.raises(TypeError):
