@@ -185,8 +185,9 @@ __global__ void __launch_bounds__(kThreads) softmax_staged_kernel(T* __restrict_
 // Rows too long for the registers of a CTA but not for its shared memory (up to about 200 KB): one CTA per SM keeps
 // the whole row on chip, so HBM is still read once and written once.  The row arrives as kRowChunks bulk copies, each
 // with its own mbarrier; the threads look for the maximum of a chunk as soon as it has landed, under the copies of
-// the chunks behind it.  Then one pass of exponentials (stored back) and sum, one pass that scales, and one bulk
-// store per chunk; a chunk's part of the buffer is refilled with the next row's chunk as soon as its store has read it.
+// the chunks behind it and sum the exponentials in the same pass (online, rescaling when the maximum grows).  A second
+// pass evaluates the exponentials again, scales and stores to global memory; a chunk's part of the buffer is refilled
+// with the next row's chunk as soon as it was read.
 constexpr int kRowThreads = 512;
 constexpr int kRowChunks = 8;
 template <typename T>
@@ -228,7 +229,10 @@ __global__ void __launch_bounds__(kRowThreads) softmax_row_smem_kernel(T* __rest
   bool alive = true;
   int it = 0;
   for (int row = blockIdx.x; row < M && alive; row += gridDim.x, ++it) {
-    float mx = -FLT_MAX;
+    // One pass over the chunks as they land: running maximum and sum of exponentials per thread, the sum rescaled
+    // when the maximum grows (the chunk loop of the reference, examples/softmax.jl:48-100), then combined over the CTA
+    // in a fixed order.
+    float m = -FLT_MAX, l = 0.f;
     for (int c = 0; c < kRowChunks; ++c) {
       const int p0 = c * per, p1 = min(npack, p0 + per);
       if (p1 <= p0) break;
@@ -236,27 +240,23 @@ __global__ void __launch_bounds__(kRowThreads) softmax_row_smem_kernel(T* __rest
       for (int p = p0 + tid; p < p1; p += kRowThreads) {
         float f[4];
         Pack<T>::unpack(buf[p], f);
-        mx = fmaxf(mx, fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])));
+        const float cm = fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3]));
+        if (cm > m) {
+          l *= exp_sub(m, cm);
+          m = cm;
+        }
+        l += (exp_sub(f[0], m) + exp_sub(f[1], m)) + (exp_sub(f[2], m) + exp_sub(f[3], m));
       }
     }
     alive = __syncthreads_and(alive);
     if (!alive) break;
-    mx = block_reduce(mx, true);
-    float s4[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int p = tid; p < npack; p += kRowThreads) {
-      float f[4];
-      Pack<T>::unpack(buf[p], f);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        f[k] = exp_sub(f[k], mx);
-        s4[k] += f[k];
-      }
-      if (sizeof(T) == 4) buf[p] = Pack<T>::pack(f);  // f32 rows keep the exponentials; f16 rows recompute them below
-    }
-    const float inv = 1.0f / block_reduce((s4[0] + s4[1]) + (s4[2] + s4[3]), false);
-    // Scale and store chunk by chunk; as soon as the store of a chunk has read its part of the buffer, the same
-    // part takes the next row's chunk, so that the next row streams in under the rest of this one.
+    const float mx = block_reduce(m, true);
+    const float inv = 1.0f / block_reduce(l * exp_sub(m, mx), false);
+    // Scale and store chunk by chunk, from registers straight to global memory (16 bytes per thread, neighbouring
+    // threads neighbouring addresses); as soon as every thread has read a chunk's part of the buffer, the same part
+    // takes the next row's chunk, so that the next row streams in under the rest of this one.
     const int next = row + gridDim.x;
+    P* dst = reinterpret_cast<P*>(out + (long long)row * ld_out);
     for (int c = 0; c < kRowChunks; ++c) {
       const int p0 = c * per, p1 = min(npack, p0 + per);
       if (p1 <= p0) break;
@@ -264,22 +264,15 @@ __global__ void __launch_bounds__(kRowThreads) softmax_row_smem_kernel(T* __rest
         float f[4];
         Pack<T>::unpack(buf[p], f);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) f[k] = (sizeof(T) == 4 ? f[k] : exp_sub(f[k], mx)) * inv;
-        buf[p] = Pack<T>::pack(f);
+        for (int k = 0; k < 4; ++k) f[k] = exp_sub(f[k], mx) * inv;
+        const P v = Pack<T>::pack(f);
+        if constexpr (sizeof(P) == 16) __stcs(reinterpret_cast<float4*>(dst + p), *reinterpret_cast<const float4*>(&v));
+        else __stcs(reinterpret_cast<uint2*>(dst + p), *reinterpret_cast<const uint2*>(&v));
       }
-      fence_proxy_async_smem();
-      __syncthreads();
-      if (tid == 0) {
-        bulk_s2g(out + (long long)row * ld_out + (long long)p0 * 4, buf + p0, (uint32_t)(p1 - p0) * 4 * sizeof(T));
-        bulk_commit();
-        if (next < M) {
-          bulk_wait_read<0>();
-          load_chunk(next, c);
-        }
-      }
+      __syncthreads();  // all reads of the chunk are done before the bulk copy overwrites it
+      if (tid == 0 && next < M) load_chunk(next, c);
     }
   }
-  if (tid == 0) bulk_wait<0>();
 }
 
 // ------------------------------------------------------------------ variant 1, any row
