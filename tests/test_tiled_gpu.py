@@ -133,6 +133,20 @@ def test_broadcast_every_kernel_variant(cuda, n, k):
     close(out.cpu().numpy(), ref.tiled_broadcast(_tree_to_oracle(tree, arrays)), 2e-6)
 
 
+def test_broadcast_in_place(cuda):
+    """The destination may be an operand: every thread reads the elements of a trip before it writes them, and reads
+    ahead only elements it has not written (several trips per thread at this size)."""
+    import torch
+    T = cuda.tiled
+    a, b = rnd((1 << 24,), 30), rnd((1 << 24,), 31)
+    A, B = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    T.assign(A, T.Tiled(A) * 2.0 + T.Tiled(B))
+    assert np.array_equal(A.cpu().numpy(), a * np.float32(2) + b)
+    T.assign(B, T.sin(T.Tiled(B)) * T.cos(T.Tiled(A)) + T.Tiled(B))                    # stack in use, two operands
+    want = np.sin(b.astype(np.float64)) * np.cos((a * np.float32(2) + b).astype(np.float64)) + b
+    close(B.cpu().numpy(), want, 2e-6)
+
+
 def test_broadcast_variants_f16_and_expanded(cuda):
     import torch
     T = cuda.tiled
