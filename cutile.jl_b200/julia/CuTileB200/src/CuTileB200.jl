@@ -381,6 +381,87 @@ function cutile_moe_ep(g::Group, hidden_states::Vector, w1::Vector, w2::Vector, 
     return out
 end
 
+# ---- one process per GPU ----------------------------------------------------
+# The library owns the NCCL communicator and the exchange buffers; the host program only carries two byte strings
+# between its processes by its own means (MPI.jl, Distributed, files): the NCCL unique id drawn by rank 0, and every
+# rank's buffer handle.  `exchange(bytes) -> Vector{Vector{UInt8}}` below is that means: it must return the byte
+# strings of all ranks, in rank order, on every rank (an all-gather).
+const UNIQUE_ID_BYTES = 128
+const EP_HANDLE_BYTES = 64
+
+"Rank 0 draws the NCCL unique id (ncclGetUniqueId) that `comm_init_rank` takes on every rank."
+function comm_unique_id()
+    id = zeros(UInt8, UNIQUE_ID_BYTES)
+    check(ccall((:ctb_comm_unique_id, LIB), Cint, (Ptr{UInt8},), id))
+    return id
+end
+"Attaches a communicator of `world` ranks to this process's context (collective: every rank calls it with the same id)."
+comm_init_rank(id::Vector{UInt8}, rank::Int, world::Int) =
+    check(ccall((:ctb_comm_init_rank, LIB), Cint, (Ptr{Cvoid}, Ptr{UInt8}, Cint, Cint), context(), id, rank, world))
+"Tears the communicator down without waiting for outstanding operations (after a host-side failure of another rank)."
+comm_abort() = check(ccall((:ctb_comm_abort, LIB), Cint, (Ptr{Cvoid},), context()))
+"(rank, world, NCCL version) of this context's communicator; world == 1 when there is none."
+function comm_info()
+    r, w, v = Ref{Cint}(0), Ref{Cint}(0), Ref{Cint}(0)
+    check(ccall((:ctb_comm_info, LIB), Cint, (Ptr{Cvoid}, Ref{Cint}, Ref{Cint}, Ref{Cint}), context(), r, w, v))
+    return (Int(r[]), Int(w[]), Int(v[]))
+end
+
+"One rank's exchange buffers for a fixed (T_local, H, topk), mapped into every rank through CUDA IPC handles."
+mutable struct EpRank
+    handle::Ptr{Cvoid}
+    rank::Int
+    world::Int
+    shape::NTuple{3,Int}
+end
+function EpRank(T_local::Int, H::Int, topk::Int, rank::Int, world::Int, exchange; with_nccl::Bool=true)
+    if with_nccl && world > 1 && comm_info()[2] == 1   # no communicator on the context yet
+        ids = exchange(rank == 0 ? comm_unique_id() : zeros(UInt8, UNIQUE_ID_BYTES))
+        comm_init_rank(ids[1], rank, world)
+    end
+    out = Ref{Ptr{Cvoid}}(C_NULL)
+    check(ccall((:ctb_ep_create, LIB), Cint, (Ptr{Cvoid}, Cint, Cint, Int64, Int64, Int64, Ref{Ptr{Cvoid}}),
+                context(), world, rank, T_local, H, topk, out))
+    mine = zeros(UInt8, EP_HANDLE_BYTES)
+    check(ccall((:ctb_ep_export, LIB), Cint, (Ptr{Cvoid}, Ptr{UInt8}), out[], mine))
+    for (q, h) in enumerate(exchange(mine))
+        q - 1 == rank || check(ccall((:ctb_ep_import, LIB), Cint, (Ptr{Cvoid}, Cint, Ptr{UInt8}), out[], q - 1, h))
+    end
+    CUDA.synchronize()
+    exchange(UInt8[])   # a barrier: every rank's flags are zero and mapped before anyone's first step
+    return EpRank(out[], rank, world, (T_local, H, topk))
+end
+function Base.close(e::EpRank)
+    e.handle == C_NULL || ccall((:ctb_ep_destroy, LIB), Cvoid, (Ptr{Cvoid},), e.handle)
+    e.handle = C_NULL
+end
+
+"This rank's call of the expert-parallel cutile_moe (every rank must make it): hidden_states (H, T_local), w1 (H, 2I, E/N),
+ w2 (I, H, E/N), topk_weights / topk_ids (T_local, topk) with global 1-based expert ids (Int32).  Returns (H, T_local) f16,
+ bit-identical to cutile_moe on the gathered problem."
+function cutile_moe_ep(e::EpRank, hidden_states::CuArray{Float16,2}, w1::CuArray{Float16,3}, w2::CuArray{Float16,3},
+                       topk_weights::CuArray{Float16,2}, topk_ids::CuArray{Int32,2}, num_experts::Int,
+                       tile_m::Int, tile_n::Int, tile_k::Int; a2a::Cint=A2A_PEER)
+    H, T_local = size(hidden_states); I = size(w2, 1); topk = size(topk_ids, 2)
+    (T_local, H, topk) == e.shape || throw(ArgumentError("cutile_moe_ep: shapes do not match the buffers"))
+    out = CuArray{Float16}(undef, H, T_local)
+    check(ccall((:ctb_moe_ffn_ep, LIB), Cint,
+        (Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Ptr{Cvoid}, Int64, Int64, Int64,
+         Int64, Int64, Cint, Cint, Cint, Cint),
+        e.handle, stream(), dptr(hidden_states), dptr(w1), dptr(w2), dptr(topk_weights), dptr(topk_ids), dptr(out),
+        T_local, H, I, num_experts, topk, tile_m, tile_n, tile_k, a2a))
+    return out
+end
+
+"Releases this process's contexts (and their communicators and scratch)."
+function destroy_contexts()
+    for ctx in values(CONTEXTS)
+        ccall((:ctb_destroy, LIB), Cvoid, (Ptr{Cvoid},), ctx)
+    end
+    empty!(CONTEXTS)
+end
+status_string(st::Integer) = unsafe_string(ccall((:ctb_status_string, LIB), Cstring, (Cint,), st))
+
 "Bytes of context scratch `cutile_moe` needs for this shape; `reserve_workspace` sizes it up front (before a graph capture)."
 moe_workspace_bytes(T, H, I, E, topk, tile_m) =
     ccall((:ctb_workspace_bytes, LIB), Csize_t, (Cint, Ptr{Int64}, Cint), 1, Int64[T, H, I, E, topk, tile_m], 6)
