@@ -9,11 +9,13 @@
 // variant 1 ("chunked", the counterpart of softmax_chunked_kernel, :48-100):
 //   rows that fit the registers of a CTA and are 16-byte aligned take the
 //   variant-0 kernel (one HBM read, one write; a chunk-by-chunk running
-//   (max, sum) over bulk-copied chunks was measured 1.5x slower because it
-//   evaluates two exponentials per element).  Longer rows that fit shared
-//   memory (up to 200 KB) are kept there whole, in chunks that are searched for
-//   the maximum as they land (still one HBM read, one write).  Anything else:
-//   a running (max, sum) per thread over chunks with 128-bit loads, re-read once.
+//   (max, sum) over bulk-copied chunks was measured 1.5x slower there because
+//   it evaluates two exponentials per element).  Longer rows that fit shared
+//   memory (up to 200 KB) are kept there whole: a running (max, sum) over the
+//   chunks as they land, then a second pass that scales and stores (still one
+//   HBM read, one write; for these rows the passes over shared memory cost
+//   more than the second exponential).  Anything else: a running (max, sum)
+//   per thread over chunks with 128-bit loads, re-read once.
 //
 // Both compute in f32 (examples/softmax.jl:32-35,92).  exp(x - max) is evaluated
 // as ex2.approx((x - max)*log2(e)) (relative error about 2^-22 plus the rounding
