@@ -424,9 +424,9 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // The element-wise part of one instruction, for all of a thread's elements.  The operation, its direction and the
-// kind of operand are template parameters and every instruction has its own straight-line code in the kernel's one
-// switch: tests on them inside the element loops came out as two to five predicated moves per element and
-// instruction, and a chain of compares per instruction, more than the arithmetic itself.
+// kind of operand are template parameters and every instruction has its own straight-line code under the kernel's
+// dispatch: with run-time tests on them around the element loops a multiplication by a constant executed 8.2
+// instructions per element (counted with ncu by differencing programs), with straight-line code 4.5.
 template <int CODE, bool REV>
 __device__ __forceinline__ float binary_op(float p, float q) {
   const float a = REV ? q : p, b = REV ? p : q;
@@ -461,7 +461,7 @@ __device__ __forceinline__ void apply_unary(float (&s0)[E]) {
 }
 
 // Calls f(integral_constant<IDX>) for the run-time idx in [LO, HI) through a balanced tree of compares: six uniform
-// branches for the 56 instructions.  (A switch over the same cases was compiled to a chain of compares, one per case.)
+// branches for the 56 instructions (measured 4 % faster on a four-instruction program than a switch over the same cases).
 template <unsigned LO, unsigned HI, typename F>
 __device__ __forceinline__ void tree_dispatch(unsigned idx, F&& f) {
   if constexpr (HI - LO == 1) {
