@@ -3,7 +3,7 @@
  *
  * Each entry point replaces one `@cuda backend=cuTile ... kernel(args...)`
  * launch (reference: src/launch.jl:788-814, the TileKernel call) or one host
- * wrapper of examples/*.jl; the comment above each declaration names it.
+ * wrapper of the examples' .jl files; the comment above each declaration names it.
  *
  * Conventions
  *  - Arrays are Julia column-major: the first listed dimension is contiguous.

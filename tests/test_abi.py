@@ -26,6 +26,16 @@ def test_library_exports_every_declared_symbol():
     assert sorted(_lib.SIGNATURES) == names, "ctypes signatures and header disagree"
 
 
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 on its own, without warnings."""
+    import subprocess
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "cutile_b200.h"\nint main(void) { return CTB_OK; }\n')
+    r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-I",
+                        os.path.dirname(HEADER), str(src)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 def test_version_and_status_strings():
     import cutile_b200
     assert "sm_100a" in cutile_b200.version_info()
